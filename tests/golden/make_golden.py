@@ -1,0 +1,169 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own Python.
+
+Run in a container that has the reference checkout (pass its ``src`` directory as
+argv[1]); the GPU box does not have it, which is why the outputs are committed.
+
+    python tests/golden/make_golden.py <reference>/src
+
+The reference package cannot be imported whole under transformers 5.x (its model
+files import a class that was removed), so an empty ``trimkv`` package whose
+``__path__`` points at the checkout is registered first and only
+``trimkv.cache_utils`` / ``trimkv.attn.eager_attn`` are imported.  The flat cache
+classes call a CUDA-only Triton append; on CPU it is rebound to a per-head
+concatenation with the same semantics (src/trimkv/triton/db_cache_utils.py:97-117).
+"""
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+import torch.nn.functional as F
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def import_reference(src_dir):
+    pkg = types.ModuleType("trimkv")
+    pkg.__path__ = [os.path.join(src_dir, "trimkv")]
+    sys.modules["trimkv"] = pkg
+    import trimkv.cache_utils as cu
+    attn_pkg = types.ModuleType("trimkv.attn")
+    attn_pkg.__path__ = [os.path.join(src_dir, "trimkv", "attn")]
+    sys.modules["trimkv.attn"] = attn_pkg
+    import trimkv.attn.eager_attn as ea
+
+    def cat_append(cache, state, headlens, cu_headlens):
+        _, h_, s_, _ = state.shape
+        parts = []
+        for h in range(h_):
+            a = int(cu_headlens[h]); n = int(headlens[h])
+            parts += [cache[a:a + n], state[0, h]]
+        return torch.cat(parts, 0)
+
+    cu.update_flatten_view_triton = cat_append
+    return cu, ea
+
+
+def config1(cu):
+    """BASELINE config 1: batch 1, 8 KV heads, D 128, fp32, M 512, B 128, 4096 prefill + 256 steps."""
+    torch.manual_seed(0)
+    H, D, S, M, B, T = 8, 128, 4096, 512, 128, 256
+    cache = cu.TrimKVCache(device="cpu")
+    logb = F.logsigmoid(torch.randn(1, H, S + T) * 1.5 + 3.0)
+    kept, lens, evict_steps = [], [], []
+
+    def step(lo, hi, tag):
+        n = hi - lo
+        # K/V content does not influence selection; small deterministic rows keep this fast.
+        k = torch.arange(lo, hi, dtype=torch.float32)[None, None, :, None].expand(1, H, n, D).contiguous()
+        cache.update(k, k.clone(), logb[:, :, lo:hi].contiguous(), torch.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(memory_size=M, buffer_size=B)
+        after = cache.get_cache_length(0)
+        lens.append(after)
+        if after != before:
+            kept.append(cache.kv_positions[0][0].numpy().astype(np.int32).copy())
+            evict_steps.append(tag)
+
+    step(0, S, 0)
+    for t in range(T):
+        step(S + t, S + t + 1, t + 1)
+    np.savez_compressed(
+        os.path.join(HERE, "config1_lockstep.npz"),
+        log_beta=logb[0].numpy(), kept_positions=np.stack(kept), lens=np.asarray(lens, np.int32),
+        evict_steps=np.asarray(evict_steps, np.int32), M=M, B=B, S=S, T=T)
+    print("config1: evictions at", evict_steps, "final len", lens[-1])
+
+
+def ties_bf16(cu):
+    """bf16-stored log beta makes equal scores common; pin the kept-score multiset and the lengths."""
+    torch.manual_seed(1)
+    Bt, H, D, S, M, B, T = 2, 4, 16, 700, 256, 64, 200
+    cache = cu.TrimKVCache(device="cpu")
+    logb = F.logsigmoid(torch.randn(Bt, H, S + T) * 1.5 + 3.0).to(torch.bfloat16)
+    out_scores, out_pos_ref, steps = [], [], []
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        n = hi - lo
+        k = torch.zeros(Bt, H, n, D, dtype=torch.bfloat16)
+        cache.update(k, k.clone(), logb[:, :, lo:hi].contiguous(), torch.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        q_idx = cache.get_seq_length(0) + 1
+        cache.compress(memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            rw = cache.retention_weights[0].to(torch.float32)
+            sc = rw * (q_idx - cache.kv_positions[0])
+            out_scores.append(np.sort(sc.numpy().reshape(Bt * H, M), axis=-1))
+            out_pos_ref.append(cache.kv_positions[0].numpy().reshape(Bt * H, M).astype(np.int32))
+            steps.append(t)
+    np.savez_compressed(
+        os.path.join(HERE, "ties_bf16.npz"),
+        log_beta_bits=logb.view(torch.int16).numpy(), kept_scores_sorted=np.stack(out_scores),
+        kept_positions_reference=np.stack(out_pos_ref), evict_steps=np.asarray(steps, np.int32),
+        M=M, B=B, S=S, T=T)
+    print("ties_bf16: evictions at", steps)
+
+
+def ties_single_shot(cu):
+    """Independent evictions whose boundary falls inside a class of equal scores."""
+    torch.manual_seed(4)
+    R, n, M = 64, 300, 200
+    vals = torch.tensor([-0.5, -0.25, -0.125, -0.0625])
+    logb = vals[torch.randint(0, 4, (1, R, n))]
+    cache = cu.TrimKVCache(device="cpu")
+    k = torch.zeros(1, R, n, 2)
+    cache.update(k, k.clone(), logb, torch.arange(n), 0)
+    q_idx = cache.get_seq_length(0) + 1
+    cache.compress(memory_size=M, buffer_size=n - M)
+    pos = cache.kv_positions[0][0]
+    sc = cache.retention_weights[0][0] * (q_idx - pos)
+    np.savez_compressed(
+        os.path.join(HERE, "ties_single_shot.npz"), log_beta=logb[0].numpy(),
+        kept_positions_reference=pos.numpy().astype(np.int32),
+        kept_scores_sorted=np.sort(sc.numpy(), axis=-1), M=M)
+    print("ties_single_shot: ok")
+
+
+def flat_layout(cu):
+    """Flat varlen layout of BatchedDynamicBudgetTrimKVCache after a prefill and three appends."""
+    torch.manual_seed(2)
+    Bt, H, D, S = 2, 3, 8, 5
+    cache = cu.BatchedDynamicBudgetTrimKVCache(device="cpu")
+    k = torch.randn(Bt, H, S + 4, D)
+    b = F.logsigmoid(torch.randn(Bt, H, S + 4))
+    cache.update(k[:, :, :S], k[:, :, :S] * 2, b[:, :, :S], torch.arange(S), 0)
+    for t in range(3):
+        lo, hi = (S + t, S + t + 1) if t < 2 else (S + 2, S + 4)
+        _, _, _, _, kw = cache.update(k[:, :, lo:hi], k[:, :, lo:hi] * 2, b[:, :, lo:hi], torch.arange(lo, hi), 0)
+    np.savez_compressed(
+        os.path.join(HERE, "flat_layout.npz"),
+        k=k.numpy(), log_beta=b.numpy(), key_flat=cache.key_cache[0].numpy(),
+        value_flat=cache.value_cache[0].numpy(), rw_flat=cache.retention_weights[0].numpy(),
+        pos_flat=cache.kv_positions[0].numpy(), head_lens=kw["head_lens"].numpy(),
+        cu_seqlens_k=kw["cu_seqlens_k"].numpy(), S=S)
+    print("flat_layout: head_lens", kw["head_lens"].tolist())
+
+
+def eager_attention(ea):
+    """Dense GQA attention from the reference's eager function (fp32), Q=1 and Q=3."""
+    torch.manual_seed(3)
+    Bt, Hq, Hkv, D, n = 2, 8, 2, 128, 37
+    out = {}
+    for ql in (1, 3):
+        q = torch.randn(Bt, Hq, ql, D); k = torch.randn(Bt, Hkv, n, D); v = torch.randn(Bt, Hkv, n, D)
+        mask = torch.full((ql, n), float("-inf")).triu(n - ql + 1)[None, None]
+        mod = types.SimpleNamespace(num_key_value_groups=Hq // Hkv, training=False)
+        o, _, _ = ea.eager_attention_forward(mod, q, k, v, mask, scaling=D ** -0.5)
+        out[f"q{ql}"] = q.numpy(); out[f"k{ql}"] = k.numpy(); out[f"v{ql}"] = v.numpy(); out[f"o{ql}"] = o.numpy()
+    np.savez_compressed(os.path.join(HERE, "eager_attention.npz"), **out)
+    print("eager_attention: ok")
+
+
+if __name__ == "__main__":
+    cu_, ea_ = import_reference(sys.argv[1])
+    config1(cu_)
+    ties_bf16(cu_)
+    ties_single_shot(cu_)
+    flat_layout(cu_)
+    eager_attention(ea_)

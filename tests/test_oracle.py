@@ -1,0 +1,127 @@
+"""The oracle against the golden vectors produced by the reference's own Python (CPU)."""
+import os
+
+import numpy as np
+import pytest
+
+from oracle import trimkv_oracle as orc
+
+
+def _load(golden_dir, name):
+    return np.load(os.path.join(golden_dir, name))
+
+
+def test_config1_lockstep_positions_and_lengths(golden_dir):
+    g = _load(golden_dir, "config1_lockstep.npz")
+    M, B, S, T = int(g["M"]), int(g["B"]), int(g["S"]), int(g["T"])
+    logb = g["log_beta"][None]  # [1,H,S+T]
+    H = logb.shape[1]
+    cache = orc.OracleTrimKVCache()
+    lens, kept = [], []
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        k = np.broadcast_to(np.arange(lo, hi, dtype=np.float32)[None, None, :, None], (1, H, hi - lo, 4)).copy()
+        cache.update(k, k.copy(), logb[:, :, lo:hi], np.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(memory_size=M, buffer_size=B)
+        lens.append(cache.get_cache_length(0))
+        if lens[-1] != before:
+            kept.append(cache.kv_positions[0][0].astype(np.int32))
+            # moved rows carry their payload: K row value == its position
+            assert np.array_equal(cache.key_cache[0][0, :, :, 0], cache.kv_positions[0][0].astype(np.float32))
+    assert np.array_equal(np.asarray(lens, np.int32), g["lens"])
+    assert np.array_equal(np.stack(kept), g["kept_positions"])
+
+
+def test_ties_bf16_kept_score_multiset(golden_dir):
+    g = _load(golden_dir, "ties_bf16.npz")
+    M, B, S, T = int(g["M"]), int(g["B"]), int(g["S"]), int(g["T"])
+    bits = g["log_beta_bits"].astype(np.uint16).astype(np.uint32) << 16
+    logb = bits.view(np.float32)  # bf16 -> fp32, exact
+    Bt, H, _ = logb.shape
+    cache = orc.OracleTrimKVCache()
+    ev = 0
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        k = np.zeros((Bt, H, hi - lo, 2), np.float32)
+        cache.update(k, k, logb[:, :, lo:hi], np.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        q_idx = cache.get_seq_length(0) + 1
+        cache.compress(memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            assert t == int(g["evict_steps"][ev])
+            sc = orc.retention_scores(cache.retention_weights[0], cache.kv_positions[0], q_idx)
+            got = np.sort(sc.reshape(Bt * H, M), axis=-1)
+            # The kept-score multiset is independent of how boundary ties are broken.
+            assert np.array_equal(got, g["kept_scores_sorted"][ev])
+            # No boundary tie occurs in this run, so the canonical rule and the reference agree.
+            assert np.array_equal(cache.kv_positions[0].reshape(Bt * H, M), g["kept_positions_reference"][ev])
+            ev += 1
+    assert ev == len(g["evict_steps"])
+
+
+def test_ties_single_shot_boundary_classes(golden_dir):
+    g = _load(golden_dir, "ties_single_shot.npz")
+    M = int(g["M"])
+    logb = g["log_beta"]
+    R, n = logb.shape
+    pos = np.broadcast_to(np.arange(n), (R, n))
+    sc = orc.retention_scores(logb, pos, n + 1)
+    keep = orc.canonical_topm(sc, M)
+    kept_sc = np.take_along_axis(sc, keep, -1)
+    # Same multiset of kept scores as the reference's topk, whatever its tie order.
+    assert np.array_equal(np.sort(kept_sc, -1), g["kept_scores_sorted"])
+    differing = 0
+    for r in range(R):
+        ref = g["kept_positions_reference"][r]
+        thr = kept_sc[r].min()
+        only_mine, only_ref = np.setdiff1d(keep[r], ref), np.setdiff1d(ref, keep[r])
+        differing += only_mine.size
+        # Differences are confined to the class of scores equal to the threshold ...
+        assert np.all(sc[r, only_mine] == thr) and np.all(sc[r, only_ref] == thr)
+        # ... and inside that class the canonical rule keeps the lowest positions.
+        tie_idx = np.nonzero(sc[r] == thr)[0]
+        kept_ties = np.intersect1d(tie_idx, keep[r])
+        assert np.array_equal(kept_ties, tie_idx[:kept_ties.size])
+    assert differing > 0  # the fixture does exercise the tie rule
+
+
+def test_flat_layout(golden_dir):
+    g = _load(golden_dir, "flat_layout.npz")
+    S = int(g["S"])
+    k, b = g["k"], g["log_beta"]
+    cache = orc.OracleBatchedFlatCache()
+    cache.update(k[:, :, :S], k[:, :, :S] * 2, b[:, :, :S], np.arange(S), 0)
+    for lo, hi in ((S, S + 1), (S + 1, S + 2), (S + 2, S + 4)):
+        _, _, _, _, kw = cache.update(k[:, :, lo:hi], k[:, :, lo:hi] * 2, b[:, :, lo:hi], np.arange(lo, hi), 0)
+    assert np.array_equal(cache.key_cache[0], g["key_flat"])
+    assert np.array_equal(cache.value_cache[0], g["value_flat"])
+    assert np.array_equal(cache.retention_weights[0], g["rw_flat"])
+    assert np.array_equal(cache.kv_positions[0], g["pos_flat"])
+    assert np.array_equal(kw["head_lens"], g["head_lens"])
+    assert np.array_equal(kw["cu_seqlens_k"], g["cu_seqlens_k"])
+
+
+@pytest.mark.parametrize("ql", [1, 3])
+def test_attention_vs_reference_eager(golden_dir, ql):
+    g = _load(golden_dir, "eager_attention.npz")
+    o = orc.dense_gqa_attention(g[f"q{ql}"], g[f"k{ql}"], g[f"v{ql}"])
+    assert np.allclose(o, g[f"o{ql}"], atol=2e-5, rtol=1e-5)
+
+
+def test_canonical_topm_tie_rule():
+    s = np.array([[-1.0, -2.0, -1.0, -0.0, 0.0, -2.0, np.nan, -1.0]], np.float32)
+    assert orc.canonical_topm(s, 1).tolist() == [[6]]          # NaN is the largest
+    assert orc.canonical_topm(s, 2).tolist() == [[3, 6]]       # -0.0 == +0.0, lower index first
+    assert orc.canonical_topm(s, 3).tolist() == [[3, 4, 6]]
+    assert orc.canonical_topm(s, 5).tolist() == [[0, 2, 3, 4, 6]]
+    assert orc.canonical_topm(s, 7).tolist() == [[0, 1, 2, 3, 4, 6, 7]]
+    assert orc.canonical_topm(s, 8).tolist() == [list(range(8))]
+
+
+def test_score_is_single_fp32_multiply():
+    lb = np.array([-0.3, -1e-3, -7.25], np.float32)
+    pos = np.array([0, 16777217, 5], np.int64)
+    got = orc.retention_scores(lb, pos, 16777300)
+    want = lb * (16777300 - pos).astype(np.float32)
+    assert got.dtype == np.float32 and np.array_equal(got, want)
