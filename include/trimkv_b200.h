@@ -1,0 +1,162 @@
+/*
+ * trimkv_b200 — C ABI of the B200 (sm_100a) TRIM-KV cache hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream and
+ * returns an int: 0 = launched, negative = argument error detected on the host
+ * before any launch (tkv_last_error() describes it).  Problems that only the
+ * device can see (a segment that would overflow its capacity, a length beyond
+ * the stated bound) are reported through the caller-provided `status` word: the
+ * kernel records the code with atomicMax and skips the offending segment; it
+ * never traps and never waits without a bound.  The library allocates no device
+ * memory and keeps no state besides the per-thread error string.
+ *
+ * Cache layout ("capacity-strided flat cache").  A cache holds `nseg` segments,
+ * one per (request b, KV head h), segment index b*Hkv + h — the order of the
+ * reference's flat cache (src/trimkv/cache_utils.py:621,632-643).  Segment s
+ * owns rows [s*cap, s*cap + len[s]) of
+ *     k_cache, v_cache : [nseg*cap, D]   bf16 / f16 / f32
+ *     beta_cache       : [nseg*cap]      f32   (log beta, the retention gate output)
+ *     pos_cache        : [nseg*cap]      i32   (original token position)
+ *     seg_len          : [nseg]          i32
+ *     cu_seqlens       : [nseg+1]        i32   exclusive prefix sum of seg_len
+ *                        (what the reference hands to flash-attn as cu_seqlens_k,
+ *                        src/trimkv/cache_utils.py:682-687)
+ * Rows of a segment are in ascending position order.
+ */
+#ifndef TRIMKV_B200_H_
+#define TRIMKV_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* tkv_stream_t; /* == cudaStream_t */
+
+/* element types of K/V rows and of incoming log beta */
+enum { TKV_BF16 = 0, TKV_F16 = 1, TKV_F32 = 2 };
+
+/* host-side return codes */
+enum {
+  TKV_OK = 0,
+  TKV_ERR_ARG = -1,       /* bad pointer / size / dtype / alignment */
+  TKV_ERR_UNSUPPORTED = -2,
+  TKV_ERR_LAUNCH = -3     /* cudaGetLastError() after the launch was not cudaSuccess */
+};
+
+/* device-side codes written to *status (atomicMax; 0 = clean) */
+enum {
+  TKV_DEV_OK = 0,
+  TKV_DEV_CAPACITY = 1,   /* len + s_new > cap: segment skipped */
+  TKV_DEV_LEN_BOUND = 2,  /* len > max_len given by the host: segment skipped */
+  TKV_DEV_BAD_INDEX = 3   /* a kept index outside [0, n): row skipped */
+};
+
+int tkv_version(void);
+
+/* Text of the last host-side error on the calling thread ("" if none). */
+const char* tkv_last_error(void);
+
+/*
+ * Append s_new tokens to every segment, in place.
+ * Replaces TrimKVCache.update's torch.cat x4 (src/trimkv/cache_utils.py:104-108) and
+ * update_flatten_view_triton x4 + the head_lens / cu_seqlens_k bumps
+ * (src/trimkv/triton/db_cache_utils.py:86-186, src/trimkv/cache_utils.py:649-680).
+ *
+ * k_new/v_new : [batch, hkv, s_new, D] with element strides (k_sb, k_sh, k_ss), rows contiguous.
+ * beta_new    : [batch, hkv, s_new] of beta_dtype, element strides (b_sb, b_sh, b_ss); stored as f32.
+ * pos_new     : int64, element strides (p_sb, p_sh, p_ss); a 1-D [s_new] position vector is
+ *               passed with p_sb = p_sh = 0 (src/trimkv/cache_utils.py:79).
+ * seg_len[s] += s_new; cu_seqlens[i] += i*s_new (cu_seqlens may be NULL).
+ */
+int tkv_append(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+               int32_t* seg_len, int32_t* cu_seqlens,
+               const void* k_new, const void* v_new, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+               const void* beta_new, int beta_dtype, int64_t b_sb, int64_t b_sh, int64_t b_ss,
+               const int64_t* pos_new, int64_t p_sb, int64_t p_sh, int64_t p_ss,
+               int batch, int hkv, int s_new, int head_dim, int64_t cap, int kv_dtype,
+               int32_t* status, tkv_stream_t stream);
+
+/*
+ * Retention-score top-M selection only (no data movement).
+ * Replaces the score + topk + sort of TrimKVCache.compress_layer
+ * (src/trimkv/cache_utils.py:172-192): score = f32(log beta) * f32(q_idx - pos), one
+ * rounding; keep the `memory_size` largest; equal scores: lower index first; -0 == +0; NaN
+ * largest.  For every segment with n = seg_len[s] (or n_uniform if seg_len is NULL):
+ *   n >= trigger_len and n > memory_size : kept_idx[s, 0..M) = ascending kept indices, kept_cnt[s] = M
+ *   otherwise                            : kept_cnt[s] = n (kept_idx untouched: nothing is evicted)
+ * beta: f32 [nseg, beta_stride]; pos: i32 [nseg, pos_stride] (pos_stride 0 = shared by all segments).
+ * max_len: host-known upper bound of n (sizes shared memory; <= 57000).
+ */
+int tkv_evict_select(const float* beta, int64_t beta_stride, const int32_t* pos, int64_t pos_stride,
+                     const int32_t* seg_len, int n_uniform, int nseg, int64_t q_idx,
+                     int memory_size, int trigger_len, int max_len,
+                     int32_t* kept_idx, int32_t* kept_cnt, int32_t* status, tkv_stream_t stream);
+
+/*
+ * Gather kept rows from a source into a (different) capacity-strided cache:
+ * dst row j of segment s <- src row kept_idx[s, j], j < kept_cnt[s] (kept_idx NULL or
+ * kept_cnt[s] == n means identity: copy the first kept_cnt[s] rows).
+ * Replaces the four gathers of TrimKVCache.compress_layer (src/trimkv/cache_utils.py:195-198)
+ * for the prefill hand-off, where the source is the dense prompt K/V [batch, hkv, n, D]
+ * (element strides k_sb, k_sh, k_ss).  src and dst must not overlap.
+ * Sets seg_len[s] = kept_cnt[s] and rebuilds cu_seqlens (if not NULL) per group of
+ * `group` segments (cu_seqlens: [nseg/group, group+1]).
+ */
+int tkv_compact(void* k_dst, void* v_dst, float* beta_dst, int32_t* pos_dst, int64_t cap,
+                const void* k_src, const void* v_src, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                const float* beta_src, int64_t beta_stride, const int32_t* pos_src, int64_t pos_stride,
+                const int32_t* kept_idx, int64_t kept_stride, const int32_t* kept_cnt,
+                int32_t* seg_len, int32_t* cu_seqlens, int group,
+                int batch, int hkv, int n_src, int head_dim, int kv_dtype,
+                int32_t* status, tkv_stream_t stream);
+
+/*
+ * Fused eviction, in place: select (as tkv_evict_select) then stable stream compaction of
+ * K, V, log beta and position rows of every segment with seg_len >= trigger_len down to
+ * memory_size rows, then seg_len = memory_size and cu_seqlens rebuilt per group.
+ * Replaces TrimKVCache.compress / compress_layer (src/trimkv/cache_utils.py:140-198) and the
+ * head_lens / cu_seqlens_k rebuild of the flat caches (:406-416, :829-834).
+ * kept_idx_out (nullable, [nseg, memory_size]) receives the kept indices of evicted segments.
+ */
+int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+              int32_t* seg_len, int32_t* cu_seqlens, int group,
+              int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+              int memory_size, int trigger_len, int max_len,
+              int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
+
+/* Rebuild cu_seqlens[g, 0..group] = exclusive prefix sum of seg_len[g*group .. ] for each group. */
+int tkv_rebuild_cu_seqlens(const int32_t* seg_len, int32_t* cu_seqlens, int nseg, int group,
+                           tkv_stream_t stream);
+
+/*
+ * Split-KV varlen GQA decode attention, one query token per request.
+ * Replaces batched_dynamic_kv_budget_attention_forward -> flash_attn_varlen_func
+ * (src/trimkv/attn/flash_attn.py:79-151) and the dense path for TrimKVCache:
+ * for segment s = b*hkv + h the G = hq/hkv query heads h*G..h*G+G-1 of request b attend to
+ * rows [start(s), start(s)+seg_len[s]) of k_cache/v_cache, softmax in f32, scale applied to
+ * q.k before the softmax.  start(s) = seg_start[s] if seg_start != NULL (packed layout,
+ * cu_seqlens_k of the reference) else s*cap.
+ * q   : [batch, hq, D] with element strides (q_sb, q_sh); same dtype as K/V (bf16 or f16).
+ * out : [batch, hq, D] contiguous (the reference's [B, Q=1, Hq, D], flash_attn.py:147-149).
+ * workspace: tkv_decode_attn_workspace_bytes(...) bytes of scratch, 256-byte aligned.
+ * max_len: host-known upper bound of seg_len (sizes the grid).
+ */
+size_t tkv_decode_attn_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len);
+
+int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
+                    const void* k_cache, const void* v_cache,
+                    const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                    void* out, void* workspace, size_t workspace_bytes,
+                    int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                    float scale, int max_len, int32_t* status, tkv_stream_t stream);
+
+/* Blocks until `stream` is idle, then returns *status (a TKV_DEV_* code) and clears it. */
+int tkv_read_status(int32_t* status, tkv_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIMKV_B200_H_ */

@@ -1,0 +1,269 @@
+"""Parity of the CUDA path (called through the C ABI) against the numpy oracle.  Needs a B200."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import trimkv_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from trimkv_b200 import ops as _ops
+    _ops.lib()  # fail loudly if the library is missing
+    return _ops
+
+
+def _slab(nseg, cap, d, dtype):
+    return (torch.zeros(nseg * cap, d, dtype=dtype, device=DEV), torch.zeros(nseg * cap, d, dtype=dtype, device=DEV),
+            torch.zeros(nseg * cap, dtype=torch.float32, device=DEV), torch.zeros(nseg * cap, dtype=torch.int32, device=DEV),
+            torch.zeros(nseg, dtype=torch.int32, device=DEV), torch.zeros(nseg + 1, dtype=torch.int32, device=DEV))
+
+
+def _logbeta(gen, *shape):
+    return torch.nn.functional.logsigmoid(torch.randn(*shape, generator=gen) * 1.5 + 3.0)
+
+
+# ---------------------------------------------------------------- append
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("b,h,d,steps", [(1, 8, 128, [5, 1, 1, 3, 40, 1]), (3, 2, 64, [1, 1, 9, 1]), (2, 1, 128, [17])])
+def test_append_matches_oracle(ops, dtype, b, h, d, steps):
+    gen = torch.Generator().manual_seed(7)
+    nseg, cap = b * h, sum(steps) + 3
+    k, v, beta, pos, ln, cu = _slab(nseg, cap, d, dtype)
+    status = ops.new_status(DEV)
+    ref_k = [np.zeros((0, d), np.float32) for _ in range(nseg)]
+    ref_b = [np.zeros((0,), np.float32) for _ in range(nseg)]
+    ref_p = [np.zeros((0,), np.int64) for _ in range(nseg)]
+    seen = 0
+    for s in steps:
+        # [B,S,H,D] storage viewed as [B,H,S,D]: the strided layout the model hands over.
+        kn = torch.randn(b, s, h, d, generator=gen).to(dtype).to(DEV).transpose(1, 2)
+        vn = (kn.float() * 2).to(dtype)
+        bn = _logbeta(gen, b, s, h).to(dtype).to(DEV).transpose(1, 2)
+        pn = torch.arange(seen, seen + s, device=DEV)
+        ops.append(k, v, beta, pos, ln, cu, kn, vn, bn, pn, cap, status)
+        for sg in range(nseg):
+            ref_k[sg] = np.concatenate([ref_k[sg], kn[sg // h, sg % h].float().cpu().numpy()])
+            ref_b[sg] = np.concatenate([ref_b[sg], bn[sg // h, sg % h].float().cpu().numpy()])
+            ref_p[sg] = np.concatenate([ref_p[sg], np.arange(seen, seen + s)])
+        seen += s
+    assert ops.read_status(status) == 0
+    assert ln.cpu().tolist() == [seen] * nseg
+    assert cu.cpu().tolist() == list(range(0, nseg * seen + 1, seen))
+    kk, vv = k.view(nseg, cap, d).float().cpu().numpy(), v.view(nseg, cap, d).float().cpu().numpy()
+    for sg in range(nseg):
+        assert np.array_equal(kk[sg, :seen], ref_k[sg])
+        assert np.array_equal(vv[sg, :seen], (torch.from_numpy(ref_k[sg]) * 2).to(dtype).float().numpy())
+        assert np.array_equal(beta.view(nseg, cap)[sg, :seen].cpu().numpy(), ref_b[sg])
+        assert np.array_equal(pos.view(nseg, cap)[sg, :seen].cpu().numpy(), ref_p[sg])
+
+
+def test_append_over_capacity_sets_status_and_skips(ops):
+    k, v, beta, pos, ln, cu = _slab(2, 4, 128, torch.bfloat16)
+    status = ops.new_status(DEV)
+    kn = torch.ones(1, 2, 3, 128, dtype=torch.bfloat16, device=DEV)
+    bn = torch.zeros(1, 2, 3, dtype=torch.bfloat16, device=DEV)
+    ops.append(k, v, beta, pos, ln, None, kn, kn, bn, torch.arange(3, device=DEV), 4, status)
+    assert ops.read_status(status) == 0 and ln.cpu().tolist() == [3, 3]
+    ops.append(k, v, beta, pos, ln, None, kn, kn, bn, torch.arange(3, 6, device=DEV), 4, status)
+    assert ops.read_status(status) == 1      # TKV_DEV_CAPACITY
+    assert ln.cpu().tolist() == [3, 3]       # nothing written
+    assert ops.read_status(status) == 0      # cleared by the read
+
+
+# ---------------------------------------------------------------- eviction
+def _fill(gen, nseg, cap, d, lens, dtype, beta_fn, step):
+    k, v, beta, pos, ln, cu = _slab(nseg, cap, d, dtype)
+    kv = torch.randn(nseg, cap, d, generator=gen).to(dtype)
+    k.copy_(kv.view(-1, d)); v.copy_((kv.float() + 1).to(dtype).view(-1, d))
+    b = beta_fn(gen, nseg, cap)
+    beta.copy_(b.view(-1))
+    p = torch.stack([torch.sort(torch.randperm(step, generator=gen)[:cap])[0] for _ in range(nseg)]).to(torch.int32)
+    pos.copy_(p.view(-1))
+    ln.copy_(torch.tensor(lens, dtype=torch.int32))
+    return (k, v, beta, pos, ln, cu), kv.float().numpy(), b.numpy(), p.numpy().astype(np.int64)
+
+
+def _bf16_logbeta(gen, *shape):
+    return _logbeta(gen, *shape).to(torch.bfloat16).float()
+
+
+def _coarse_logbeta(gen, *shape):
+    vals = torch.tensor([-0.5, -0.25, -0.125, -0.0, 0.0])
+    return vals[torch.randint(0, 5, shape, generator=gen)]
+
+
+CASES = [
+    # nseg, cap, d, M, trigger, lens-spec, dtype, beta generator
+    (8, 640, 128, 512, 640, "full", torch.float32, _logbeta),            # config-1 steady state n = M+B
+    (4, 4096, 128, 512, 640, "full", torch.float32, _logbeta),           # prefill-like n >> M
+    (6, 700, 128, 256, 320, "ragged", torch.bfloat16, _bf16_logbeta),    # some segments below the trigger
+    (5, 333, 64, 100, 101, "ragged", torch.bfloat16, _coarse_logbeta),   # heavy ties, -0.0/+0.0, odd sizes
+    (1, 130, 128, 129, 130, "full", torch.bfloat16, _bf16_logbeta),      # evict exactly one token
+    (3, 77, 128, 1, 2, "full", torch.float16, _coarse_logbeta),          # keep a single token
+    (2, 4224, 128, 4096, 4224, "full", torch.bfloat16, _bf16_logbeta),   # config-2 steady state
+]
+
+
+@pytest.mark.parametrize("nseg,cap,d,m,trigger,spec,dtype,beta_fn", CASES)
+def test_evict_inplace_bit_exact(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn):
+    gen = torch.Generator().manual_seed(11)
+    if spec == "full":
+        lens = [cap] * nseg
+    else:
+        lens = [int(x) for x in torch.randint(m // 2, cap + 1, (nseg,), generator=gen)]
+        lens[0], lens[-1] = cap, trigger
+    step = 4 * cap
+    (k, v, beta, pos, ln, cu), kv, b, p = _fill(gen, nseg, cap, d, lens, dtype, beta_fn, step)
+    status = ops.new_status(DEV)
+    kept = torch.full((nseg, m), -1, dtype=torch.int32, device=DEV)
+    q_idx = step + 1
+    ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, trigger, cap, kept, status)
+    assert ops.read_status(status) == 0
+    new_len = ln.cpu().numpy()
+    kk = k.view(nseg, cap, d).float().cpu().numpy()
+    vv = v.view(nseg, cap, d).float().cpu().numpy()
+    bb, pp = beta.view(nseg, cap).cpu().numpy(), pos.view(nseg, cap).cpu().numpy()
+    v_src = (torch.from_numpy(kv) + 1).to(dtype).float().numpy()
+    for s in range(nseg):
+        n = lens[s]
+        if n >= trigger and n > m:
+            sc = orc.retention_scores(b[s, :n], p[s, :n], q_idx)
+            want = orc.canonical_topm(sc[None], m)[0]
+            assert np.array_equal(kept[s].cpu().numpy(), want)
+            assert new_len[s] == m
+        else:
+            want = np.arange(n)
+            assert new_len[s] == n
+        assert np.array_equal(pp[s, :len(want)], p[s, want])
+        assert np.array_equal(bb[s, :len(want)], b[s, want])
+        assert np.array_equal(kk[s, :len(want)], kv[s, want])
+        assert np.array_equal(vv[s, :len(want)], v_src[s, want])
+    assert np.array_equal(cu.cpu().numpy(), np.concatenate([[0], np.cumsum(new_len)]))
+    # idempotence: nothing reaches the trigger any more unless trigger <= M was asked for
+    before = (k.clone(), pos.clone(), ln.clone())
+    ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, max(trigger, m + 1), cap, None, status)
+    assert torch.equal(before[0], k) and torch.equal(before[1], pos) and torch.equal(before[2], ln)
+
+
+def test_evict_grouped_cu_seqlens(ops):
+    """Several layers in one launch: cu_seqlens is rebuilt per group of B*Hkv segments."""
+    gen = torch.Generator().manual_seed(5)
+    layers, nseg, cap, d, m = 3, 4, 96, 128, 64
+    total = layers * nseg
+    (k, v, beta, pos, ln, _), kv, b, p = _fill(gen, total, cap, d, [cap] * total, torch.bfloat16, _bf16_logbeta, 500)
+    cu = torch.zeros(layers, nseg + 1, dtype=torch.int32, device=DEV)
+    ops.evict(k, v, beta, pos, ln, cu, nseg, total, cap, 501, m, cap, cap, None, None)
+    assert cu.cpu().tolist() == [list(range(0, nseg * m + 1, m))] * layers
+    want = orc.canonical_topm(orc.retention_scores(b, p, 501), m)
+    assert np.array_equal(pos.view(total, cap)[:, :m].cpu().numpy(), np.take_along_axis(p, want, -1))
+
+
+def test_select_then_compact_from_dense_prompt(ops):
+    """Prefill hand-off: select on the dense prompt, gather into a capacity-strided cache."""
+    gen = torch.Generator().manual_seed(3)
+    bsz, h, n, d, m, cap = 2, 3, 1000, 128, 300, 364
+    nseg = bsz * h
+    kd = torch.randn(bsz, n, h, d, generator=gen).to(torch.bfloat16).to(DEV).transpose(1, 2)  # strided view
+    vd = (kd.float() - 1).to(torch.bfloat16)
+    b = _bf16_logbeta(gen, nseg, n).to(DEV)
+    p = torch.arange(n, dtype=torch.int32, device=DEV)
+    kept = torch.empty(nseg, m, dtype=torch.int32, device=DEV)
+    cnt = torch.empty(nseg, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    ops.evict_select(b, p, None, n, nseg, n + 1, m, m + 64, n, kept, cnt, status)
+    want = orc.canonical_topm(orc.retention_scores(b.cpu().numpy(), np.arange(n), n + 1), m)
+    assert np.array_equal(kept.cpu().numpy(), want) and cnt.cpu().tolist() == [m] * nseg
+    k, v, beta, pos, ln, cu = _slab(nseg, cap, d, torch.bfloat16)
+    ops.compact(k, v, beta, pos, cap, kd, vd, b, p.expand(nseg, n).contiguous(), kept, cnt, ln, cu, nseg, status)
+    assert ops.read_status(status) == 0
+    assert ln.cpu().tolist() == [m] * nseg and cu.cpu().tolist() == list(range(0, nseg * m + 1, m))
+    kk = k.view(bsz, h, cap, d)[:, :, :m].float().cpu().numpy()
+    src = kd.float().cpu().numpy()
+    assert np.array_equal(kk, np.take_along_axis(src, want.reshape(bsz, h, m)[..., None], axis=2))
+    assert np.array_equal(pos.view(nseg, cap)[:, :m].cpu().numpy(), want)
+
+
+def test_full_size_eviction_properties(ops):
+    """BASELINE config-3 sizes (2048 segments, M=4096, B=128): properties that need no oracle."""
+    gen = torch.Generator(device=DEV).manual_seed(0)
+    nseg, m, bsz, d = 2048, 4096, 128, 128
+    cap = m + bsz
+    k = torch.randn(nseg * cap, d, generator=gen, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(nseg * cap, d, generator=gen, device=DEV, dtype=torch.bfloat16)
+    beta = torch.nn.functional.logsigmoid(torch.randn(nseg, cap, generator=gen, device=DEV) * 1.5 + 3).bfloat16().float()
+    step = 4 * m
+    pos = torch.sort(torch.rand(nseg, step, generator=gen, device=DEV).argsort(-1)[:, :cap], -1)[0].to(torch.int32)
+    ln = torch.randint(m, cap + 1, (nseg,), generator=gen, device=DEV, dtype=torch.int32)
+    cu = torch.zeros(nseg + 1, dtype=torch.int32, device=DEV)
+    k0, v0, b0, p0, l0 = k.clone(), v.clone(), beta.clone(), pos.clone(), ln.clone()
+    status = ops.new_status(DEV)
+    ops.evict(k, v, beta.view(-1), pos.view(-1), ln, cu, nseg, nseg, cap, step + 1, m, m + 1, cap, None, status)
+    assert ops.read_status(status) == 0
+    fired = l0 > m
+    assert torch.equal(ln, torch.where(fired, torch.full_like(l0, m), l0))
+    assert torch.equal(cu[1:].long(), ln.long().cumsum(0))
+    valid = torch.arange(cap, device=DEV)[None, :] < l0[:, None]
+    score = (beta.new_tensor(float(step + 1)) - p0.float()) * b0
+    score = torch.where(valid, score, torch.full_like(score, -float("inf")))
+    # kept positions ascending and a subset of the old ones; kept set = M best scores (threshold property)
+    kp = pos[:, :m]
+    assert bool((kp[:, 1:] > kp[:, :-1]).all())
+    thr = torch.topk(score, m, dim=-1).values[:, -1]
+    new_score = (float(step + 1) - kp.float()) * beta[:, :m]
+    assert bool((new_score[fired] >= thr[fired, None]).all())
+    assert torch.equal(new_score.sort(-1, descending=True)[0][fired], torch.topk(score, m, -1).values[fired])
+    # payload moved with its row: look each kept position up in the original segment
+    idx = torch.searchsorted(p0.contiguous(), kp.contiguous())
+    rows = (torch.arange(nseg, device=DEV)[:, None] * cap + idx).view(-1)
+    assert torch.equal(k.view(nseg, cap, d)[:, :m].reshape(-1, d), k0[rows])
+    assert torch.equal(v.view(nseg, cap, d)[:, :m].reshape(-1, d), v0[rows])
+
+
+# ---------------------------------------------------------------- decode attention
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 5e-3)])
+@pytest.mark.parametrize("bsz,hq,hkv,d,cap,lens_spec", [
+    (2, 16, 8, 128, 300, "ragged"), (1, 8, 8, 128, 70, "ragged"), (3, 40, 8, 128, 1100, "ragged"),
+    (2, 32, 8, 128, 2100, "full"), (2, 8, 2, 64, 257, "ragged"), (1, 2, 1, 128, 5, "tiny"),
+])
+def test_decode_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, d, cap, lens_spec):
+    gen = torch.Generator().manual_seed(21)
+    nseg = bsz * hkv
+    if lens_spec == "full":
+        lens = [cap] * nseg
+    elif lens_spec == "tiny":
+        lens = [1] * nseg
+    else:
+        lens = [int(x) for x in torch.randint(1, cap + 1, (nseg,), generator=gen)]
+        lens[0] = 0 if nseg > 1 else lens[0]  # an empty segment yields zeros
+        lens[-1] = cap
+    q = torch.randn(bsz, 1, hq, d, generator=gen).to(dtype).to(DEV).transpose(1, 2)  # [B,Hq,1,D] strided
+    k = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.empty(bsz, hq, d, dtype=dtype, device=DEV)
+    max_len = max(lens)
+    ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, max_len), dtype=torch.uint8, device=DEV)
+    status = ops.new_status(DEV)
+    ops.decode_attn(q[:, :, 0, :], k, v, ln, None, cap, out, ws, hkv, d ** -0.5, max_len, status)
+    assert ops.read_status(status) == 0
+    # oracle on the packed equivalent
+    kf = torch.cat([k[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    vf = torch.cat([v[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    cu = np.concatenate([[0], np.cumsum(lens)])
+    want = orc.varlen_gqa_attention(q.float().cpu().numpy(), kf, vf, cu, bsz, hkv)[:, 0]
+    got = out.float().cpu().numpy()
+    assert np.max(np.abs(got - want)) <= tol
+    # packed layout addressed through cu_seqlens_k, as the reference's flat caches present it
+    kp = torch.cat([k[s, :lens[s]] for s in range(nseg)]).contiguous()
+    vp = torch.cat([v[s, :lens[s]] for s in range(nseg)]).contiguous()
+    out2 = torch.empty_like(out)
+    ops.decode_attn(q[:, :, 0, :], kp, vp, ln, torch.tensor(cu[:-1], dtype=torch.int32, device=DEV), 0, out2, ws, hkv,
+                    d ** -0.5, max_len, status)
+    assert torch.equal(out, out2)

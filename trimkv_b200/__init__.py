@@ -1,0 +1,13 @@
+"""trimkv_b200 — the TRIM-KV memory-bounded KV-cache hot path on B200 (sm_100a).
+
+Host code in Python/PyTorch (device memory, streams), arithmetic in hand-written CUDA behind
+the C ABI of include/trimkv_b200.h.  Importing the package does not need a GPU; using it does.
+"""
+from .cache_utils import TrimKVCache
+from .attn import TRIMKV_ATTENTION_IMPLEMENTATIONS, get_attention_interface
+from .modeling_qwen3 import TrimKVQwen3Config, TrimKVQwen3ForCausalLM, TrimKVQwen3Model
+
+__all__ = [
+    "TrimKVCache", "TRIMKV_ATTENTION_IMPLEMENTATIONS", "get_attention_interface",
+    "TrimKVQwen3Config", "TrimKVQwen3ForCausalLM", "TrimKVQwen3Model",
+]

@@ -1,0 +1,105 @@
+"""Attention registry with the reference's string-keyed interface.
+
+Mirrors src/trimkv/attn/__init__.py:8-37 (``TRIMKV_ATTENTION_IMPLEMENTATIONS``,
+``get_attention_interface``) and the call signature of
+``batched_dynamic_kv_budget_attention_forward`` (src/trimkv/attn/flash_attn.py:79-89):
+
+    fn(module, query[B,Hq,Q,D], key, value, attention_mask, scaling=None, dropout_p=0.0,
+       flash_attn_kwargs={}, **kwargs) -> (attn_output[B,Q,Hq,D], None, None)
+
+Decode (one query token, a cache that carries ``head_lens``) runs the split-KV CUDA kernel; the
+prompt pass (dense K/V, Q > 1) is ordinary causal attention and stays in PyTorch.
+"""
+from __future__ import annotations
+
+from typing import Callable, Dict
+
+import torch
+import torch.nn.functional as F
+
+from . import ops
+
+_workspaces: Dict[torch.device, torch.Tensor] = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def _dense_causal(query, key, value, scaling):
+    """Causal attention with bottom-right alignment over dense ``[B,Hkv,n,D]`` keys (prompt pass)."""
+    ql, n = query.shape[2], key.shape[2]
+    if ql == n:
+        out = F.scaled_dot_product_attention(query, key, value, is_causal=True, scale=scaling, enable_gqa=True)
+    else:
+        mask = torch.ones(ql, n, dtype=torch.bool, device=query.device).tril(n - ql)
+        out = F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling, enable_gqa=True)
+    return out.transpose(1, 2)
+
+
+def tkv_attention_forward(
+    module,
+    query: torch.Tensor,
+    key: torch.Tensor,
+    value: torch.Tensor,
+    attention_mask=None,
+    scaling: float = None,
+    dropout_p: float = 0.0,
+    flash_attn_kwargs: dict = {},
+    **kwargs,  # retention_weights, kv_positions, offset, dropout, sliding_window, is_causal: accepted, unused
+):
+    bsz, hq, ql, dim = query.shape
+    if scaling is None:
+        scaling = dim ** -0.5  # the reference's varlen wrappers always use flash-attn's default (flash_attn.py:85)
+    head_lens = flash_attn_kwargs.get("head_lens") if flash_attn_kwargs else None
+    if head_lens is None or ql != 1:
+        if key.dim() != 4:
+            raise NotImplementedError("multi-token queries over a packed flat cache")
+        return _dense_causal(query, key, value, scaling), None, None
+
+    q3 = query[:, :, 0, :]
+    out = torch.empty(bsz, 1, hq, dim, dtype=query.dtype, device=query.device)
+    if key.dim() == 4:
+        # Strided views of the capacity-strided cache: the segment stride is the capacity.
+        hkv, max_len = key.shape[1], key.shape[2]
+        if key.stride(3) != 1 or key.stride(2) != dim or key.stride(0) != hkv * key.stride(1):
+            raise ValueError("key is not a view of a capacity-strided cache")
+        cap, seg_start = key.stride(1) // dim, None
+    else:
+        # Packed [sum n, D] layout of the reference's flat caches: segment starts are cu_seqlens_k.
+        hkv = flash_attn_kwargs.get("num_kv_heads") or head_lens.shape[0] // bsz
+        seg_start = flash_attn_kwargs["cu_seqlens_k"]
+        max_len = flash_attn_kwargs.get("max_seqlen_k") or int(head_lens.max().item())
+        cap = 0
+    ws = _workspace(query.device, ops.decode_attn_workspace_bytes(bsz, hq, hkv, dim, max_len))
+    ops.decode_attn(q3, key, value, head_lens, seg_start, cap, out, ws, hkv, scaling, max_len,
+                    flash_attn_kwargs.get("status"))
+    return out, None, None
+
+
+def dense_attention_forward(module, query, key, value, attention_mask=None, scaling=None, **kwargs):
+    """Stand-in for the reference's wrapper around HF attention functions (attn/__init__.py:15-26)."""
+    if scaling is None:
+        scaling = query.shape[-1] ** -0.5
+    return _dense_causal(query, key, value, scaling), None, None
+
+
+TRIMKV_ATTENTION_IMPLEMENTATIONS: Dict[str, Callable] = {
+    "tkv_b200": tkv_attention_forward,
+    "db_attn_flash": tkv_attention_forward,
+    "db_attn_flash_batched": tkv_attention_forward,
+}
+
+
+def get_attention_interface(attn_impl: str, compile: bool = False) -> Callable:
+    if compile:
+        raise NotImplementedError("torch.compile is not used on this path")
+    if attn_impl in TRIMKV_ATTENTION_IMPLEMENTATIONS:
+        return TRIMKV_ATTENTION_IMPLEMENTATIONS[attn_impl]
+    if attn_impl in ("sdpa", "eager", "attn_eager", "flash_attention_2"):
+        return dense_attention_forward
+    raise KeyError(f"unknown attention implementation {attn_impl!r}")

@@ -1,0 +1,391 @@
+"""`TrimKVCache` on the B200 kernels: same surface as the reference class, different storage.
+
+Mirrors ``TrimKVCache`` of the reference (src/trimkv/cache_utils.py:11-223): ``update`` returns the
+5-tuple ``(K, V, log beta, positions, flash_attn_kwargs)``, ``compress`` applies the per-head
+keep-top-M policy once a layer holds ``M + B`` tokens, and the bookkeeping methods keep their names
+and meaning.  Storage differs: after the prompt all layers live in one *capacity-strided flat cache*
+(one slab per tensor kind, ``[layers, B*Hkv, cap, ...]``), appended to and compacted in place by the
+CUDA kernels, instead of per-layer tensors re-allocated by ``torch.cat``/``gather`` every step.
+
+What a caller sees:
+  * ``key_cache[l]`` / ``value_cache[l]``: ``[B, Hkv, n, D]`` views (strided by ``cap``) — same shape as
+    the reference's tensors; ``retention_weights[l]`` ``[B, Hkv, n]`` is held in fp32 (the exact upcast
+    the reference applies before scoring, :172) and ``kv_positions[l]`` in int32 (``log()`` returns int64).
+  * ``flash_attn_kwargs`` carries ``head_lens`` / ``cu_seqlens_k`` (int32, per segment ``b*Hkv + h``) like
+    the reference's flat caches (:682-687).
+There is no CPU path: tensors must live on a CUDA device.
+"""
+from __future__ import annotations
+
+from typing import Any, Dict, Iterable, List, Optional, Tuple
+
+import torch
+
+from . import ops
+
+__all__ = ["TrimKVCache"]
+
+
+class _LayerViews:
+    """List-like accessor (``cache.key_cache[layer]``) that builds views of the slabs on demand."""
+
+    def __init__(self, cache: "TrimKVCache", kind: str):
+        self._cache, self._kind = cache, kind
+
+    def __len__(self):
+        return len(self._cache)
+
+    def __getitem__(self, layer_idx: int) -> torch.Tensor:
+        if isinstance(layer_idx, slice):
+            return [self[i] for i in range(*layer_idx.indices(len(self)))]
+        if layer_idx < 0:
+            layer_idx += len(self)
+        return self._cache._view(self._kind, layer_idx)
+
+    def __iter__(self):
+        for i in range(len(self)):
+            yield self[i]
+
+
+class TrimKVCache:
+    def __init__(
+        self,
+        max_seq_len: int = 20480,
+        _distributed_cache_data: Iterable = None,
+        device: str = "cuda",
+        memory_size: Optional[int] = None,
+        buffer_size: Optional[int] = None,
+    ) -> None:
+        # Same first three arguments as the reference (cache_utils.py:12-33).  memory_size/buffer_size are
+        # optional hints: when given, the slabs are sized M+B at the first decode step even if compress()
+        # has not been called yet.
+        if _distributed_cache_data is not None:
+            raise NotImplementedError("Distributed cache data is not supported for TrimKVCache")
+        self.max_seq_len = max_seq_len
+        self.device = device
+        self._seen_tokens = 0
+        self.n_seen_tokens: List[int] = []
+        self.offset = torch.tensor(0, dtype=torch.int64)
+        self.block_mask = None
+        self.sliding_window_size = 0
+        self._hint_m, self._hint_b = memory_size, buffer_size
+
+        self._pending: List[Optional[Tuple[torch.Tensor, ...]]] = []  # per layer: dense prompt (K, V, beta, pos)
+        self._cache_len: List[int] = []                               # per layer: live rows per segment
+        self._slab = None  # dict(k, v, beta, pos, len, cu) once materialised
+        self._cap = 0
+        self._batch = self._hkv = self._dim = None
+        self._status = None
+        self.last_kept_idx: Optional[torch.Tensor] = None  # filled when record_kept is set (tests, log)
+        self.record_kept = False
+
+        self.key_cache = _LayerViews(self, "k")
+        self.value_cache = _LayerViews(self, "v")
+        self.retention_weights = _LayerViews(self, "beta")
+        self.kv_positions = _LayerViews(self, "pos")
+        self.head_lens = _LayerViews(self, "len")
+        self.cu_seqlens_k = _LayerViews(self, "cu")
+
+    # ------------------------------------------------------------------ container protocol
+    def __len__(self):
+        return len(self._cache_len)
+
+    def __getitem__(self, layer_idx: int):
+        if layer_idx < len(self):
+            return (self.key_cache[layer_idx], self.value_cache[layer_idx],
+                    self.retention_weights[layer_idx], self.kv_positions[layer_idx])
+        raise KeyError(f"Cache only has {len(self)} layers, attempted to access layer with index {layer_idx}")
+
+    def __iter__(self):
+        for layer_idx in range(len(self)):
+            yield self[layer_idx]
+
+    # ------------------------------------------------------------------ bookkeeping (cache_utils.py:48-60,134-138)
+    def get_seq_length(self, layer_idx: Optional[int] = None) -> int:
+        if layer_idx is None:
+            return self._seen_tokens
+        return self.n_seen_tokens[layer_idx] if layer_idx < len(self.n_seen_tokens) else 0
+
+    def get_cache_length(self, layer_idx: int = 0) -> int:
+        return self._cache_len[layer_idx] if layer_idx < len(self._cache_len) else 0
+
+    def get_total_cached_tokens(self, num_key_value_heads: Optional[int] = None) -> int:
+        if num_key_value_heads is None:
+            num_key_value_heads = self._hkv or 0
+        return sum(self.get_cache_length(l) * num_key_value_heads for l in range(len(self)))
+
+    # HF generate() probes these on any cache object.
+    is_compileable = False
+    is_sliding = [False]
+
+    def get_mask_sizes(self, cache_position: torch.Tensor, layer_idx: int = 0) -> Tuple[int, int]:
+        return self.get_cache_length(layer_idx) + cache_position.shape[0], 0
+
+    def advance(self, num_tokens: int = 1) -> None:
+        """Host-side counters of one ``update`` per layer, for callers that replay a captured CUDA graph
+        of the decode step (the kernels bump the device-side lengths themselves)."""
+        self._seen_tokens += num_tokens
+        for l in range(len(self)):
+            self.n_seen_tokens[l] += num_tokens
+            self._cache_len[l] += num_tokens
+
+    # ------------------------------------------------------------------ views
+    def _view(self, kind: str, l: int):
+        if l >= len(self):
+            raise IndexError(l)
+        if self._pending[l] is not None:
+            k, v, beta, pos = self._pending[l]
+            if kind in ("len", "cu"):
+                b, h, s, _ = k.shape
+                if kind == "len":
+                    return torch.full((b * h,), s, dtype=torch.int32, device=k.device)
+                return torch.arange(0, b * h * s + 1, s, dtype=torch.int32, device=k.device)
+            return {"k": k, "v": v, "beta": beta, "pos": pos}[kind]
+        if self._slab is None:  # skipped layer that never received data (cache_utils.py:82-88)
+            return torch.tensor([])
+        n, s = self._cache_len[l], self._slab
+        if kind == "k" or kind == "v":
+            return s[kind][l].view(self._batch, self._hkv, self._cap, self._dim)[:, :, :n]
+        if kind == "beta" or kind == "pos":
+            return s[kind][l].view(self._batch, self._hkv, self._cap)[:, :, :n]
+        return s[kind][l]
+
+    # ------------------------------------------------------------------ update (cache_utils.py:62-110)
+    def update(
+        self,
+        key_states: torch.Tensor,
+        value_states: torch.Tensor,
+        retention_weights: torch.Tensor,
+        cache_positions: torch.Tensor,
+        layer_idx: int,
+        cache_kwargs: Optional[Dict[str, Any]] = None,
+    ):
+        if key_states is not None:
+            bsz, num_heads, seq_len, dim = key_states.shape
+            if not key_states.is_cuda:
+                raise ops._lib.TrimKVNativeError("TrimKVCache (B200) holds CUDA tensors only; there is no CPU path")
+            if layer_idx == 0:
+                self._seen_tokens += seq_len
+            while len(self._cache_len) <= layer_idx:  # includes skipped layers
+                self._pending.append(None)
+                self._cache_len.append(0)
+                self.n_seen_tokens.append(0)
+            if self._cache_len[layer_idx] == 0 and self._slab is None:
+                # First tokens of this layer: keep the caller's tensors, as the reference does (:90-94).
+                if cache_positions.dim() == 1:
+                    cache_positions = cache_positions[None, None, :].expand_as(retention_weights)
+                self._pending[layer_idx] = (key_states, value_states, retention_weights, cache_positions)
+                self._cache_len[layer_idx] = seq_len
+                self.n_seen_tokens[layer_idx] = seq_len
+                self._batch, self._hkv, self._dim = bsz, num_heads, dim
+            else:
+                if self._slab is None or self._pending[layer_idx] is not None:
+                    self._materialise(extra=seq_len)
+                if layer_idx >= self._slab["k"].shape[0]:
+                    raise NotImplementedError("a layer that first receives tokens after the prompt hand-off")
+                if (bsz, num_heads, dim) != (self._batch, self._hkv, self._dim):
+                    raise ValueError("batch size / KV heads / head_dim changed between updates")
+                if self._cache_len[layer_idx] + seq_len > self._cap:
+                    self._grow(self._cache_len[layer_idx] + seq_len)
+                s = self._slab
+                ops.append(s["k"][layer_idx], s["v"][layer_idx], s["beta"][layer_idx], s["pos"][layer_idx],
+                           s["len"][layer_idx], s["cu"][layer_idx], key_states, value_states, retention_weights,
+                           cache_positions, self._cap, self._status)
+                self._cache_len[layer_idx] += seq_len
+                self.n_seen_tokens[layer_idx] += seq_len
+        return (self.key_cache[layer_idx], self.value_cache[layer_idx], self.retention_weights[layer_idx],
+                self.kv_positions[layer_idx], self._attn_kwargs(layer_idx))
+
+    def _attn_kwargs(self, l: int) -> Dict[str, Any]:
+        if self._slab is None or self._pending[l] is not None:
+            return {}
+        return {"head_lens": self._slab["len"][l], "cu_seqlens_k": self._slab["cu"][l],
+                "batch_size": self._batch, "num_kv_heads": self._hkv, "status": self._status}
+
+    # ------------------------------------------------------------------ storage
+    def _alloc(self, cap: int):
+        dev, nl, nseg = self._any_pending_or_slab_device(), len(self), self._batch * self._hkv
+        dt = self._kv_dtype
+        slab = {
+            "k": torch.empty(nl, nseg * cap, self._dim, dtype=dt, device=dev),
+            "v": torch.empty(nl, nseg * cap, self._dim, dtype=dt, device=dev),
+            "beta": torch.empty(nl, nseg * cap, dtype=torch.float32, device=dev),
+            "pos": torch.empty(nl, nseg * cap, dtype=torch.int32, device=dev),
+            "len": torch.zeros(nl, nseg, dtype=torch.int32, device=dev),
+            "cu": torch.zeros(nl, nseg + 1, dtype=torch.int32, device=dev),
+        }
+        return slab
+
+    def _any_pending_or_slab_device(self):
+        if self._slab is not None:
+            return self._slab["k"].device
+        return next(p[0].device for p in self._pending if p is not None)
+
+    def _materialise(self, extra: int = 0, memory_size: Optional[int] = None, buffer_size: Optional[int] = None):
+        """Moves the dense prompt tensors of every layer into the slabs (the prefill hand-off)."""
+        pend = [p for p in self._pending if p is not None]
+        if not pend:
+            return
+        m = memory_size if memory_size is not None else self._hint_m
+        bsz = buffer_size if buffer_size is not None else self._hint_b
+        self._kv_dtype = pend[0][0].dtype
+        dev = pend[0][0].device
+        if self._status is None:
+            self._status = ops.new_status(dev)
+        longest = max(self._cache_len)
+        if m is not None and bsz is not None:
+            kept_longest = max((m if n >= m + bsz else n) for n in self._cache_len)
+            cap = max(m + bsz, kept_longest + extra)
+        else:
+            cap = 1 << max(8, (longest + extra + 255).bit_length())
+        first = self._slab is None
+        if first:
+            self._cap = cap
+            self._slab = self._alloc(cap)
+        nseg = self._batch * self._hkv
+        s = self._slab
+        kept_all = []
+        for l, p in enumerate(self._pending):
+            if p is None:
+                continue
+            k, v, beta, pos = p
+            n = k.shape[2]
+            beta32 = beta.to(torch.float32).reshape(nseg, n).contiguous()
+            pos32 = pos.to(torch.int32).reshape(nseg, n).contiguous()
+            kept_idx = kept_cnt = None
+            if m is not None and bsz is not None and n >= m + bsz:
+                kept_idx = torch.empty(nseg, m, dtype=torch.int32, device=dev)
+                kept_cnt = torch.empty(nseg, dtype=torch.int32, device=dev)
+                ops.evict_select(beta32, pos32, None, n, nseg, self.n_seen_tokens[l] + 1, m, m + bsz, n,
+                                 kept_idx, kept_cnt, self._status)
+                self._cache_len[l] = m
+                if self.record_kept:
+                    kept_all.append(kept_idx.view(self._batch, self._hkv, m))
+            ops.compact(s["k"][l], s["v"][l], s["beta"][l], s["pos"][l], self._cap, k, v, beta32, pos32,
+                        kept_idx, kept_cnt, s["len"][l], s["cu"][l], nseg, self._status)
+            self._pending[l] = None
+        if kept_all:
+            self.last_kept_idx = torch.stack(kept_all)  # [layers, B, Hkv, M]
+
+    def _grow(self, need: int):
+        """Re-homes every layer in slabs of at least ``need`` rows per segment (rare: no eviction or a large chunk)."""
+        old, old_cap = self._slab, self._cap
+        new_cap = max(need, 2 * old_cap)
+        self._slab, self._cap = self._alloc(new_cap), new_cap
+        nseg = self._batch * self._hkv
+        for l in range(len(self)):
+            n = self._cache_len[l]
+            if n == 0:
+                continue
+            k = old["k"][l].view(self._batch, self._hkv, old_cap, self._dim)[:, :, :n]
+            v = old["v"][l].view(self._batch, self._hkv, old_cap, self._dim)[:, :, :n]
+            ops.compact(self._slab["k"][l], self._slab["v"][l], self._slab["beta"][l], self._slab["pos"][l], new_cap,
+                        k, v, old["beta"][l].view(nseg, old_cap), old["pos"][l].view(nseg, old_cap),
+                        None, old["len"][l], self._slab["len"][l], self._slab["cu"][l], nseg, self._status)
+
+    # ------------------------------------------------------------------ compress (cache_utils.py:140-198)
+    def compress(
+        self,
+        strategy: str = "alpha",
+        memory_size: int = 2048,
+        buffer_size: int = 512,
+        floor_budget_ratio: float = 0.0,   # accepted and unused, as in the reference (:145-146)
+        alpha_threshold: float = 0.0,
+        num_layers: Optional[int] = None,
+        num_key_value_heads: Optional[int] = None,
+        skip_layers: int = 0,
+    ):
+        if strategy != "alpha":
+            if strategy == "knorm_alpha":
+                raise NotImplementedError("compress strategy 'knorm_alpha' is not built on the CUDA path")
+            raise ValueError(f"Unknown compression strategy: {strategy}")
+        if self.sliding_window_size:
+            raise NotImplementedError("sliding_window_size > 0 is not built on the CUDA path")
+        num_layers = len(self) if num_layers is None else num_layers
+        if num_layers == 0:
+            return
+        if any(p is not None for p in self._pending):
+            if skip_layers:
+                raise NotImplementedError("skip_layers with a pending prompt")
+            self._materialise(memory_size=memory_size, buffer_size=buffer_size)
+            return
+        trigger = memory_size + buffer_size
+        fire = [l for l in range(skip_layers, num_layers) if trigger <= self._cache_len[l]]
+        if not fire:
+            return
+        s, nseg = self._slab, self._batch * self._hkv
+        all_same = (len(fire) == len(self) and len({self.n_seen_tokens[l] for l in fire}) == 1
+                    and len({self._cache_len[l] for l in fire}) == 1)
+        kept = None
+        if all_same:
+            # Every layer fires in the same forward (same lengths): one launch over the whole slab.
+            nl, n = len(self), self._cache_len[0]
+            if self.record_kept:
+                kept = torch.empty(nl * nseg, memory_size, dtype=torch.int32, device=s["k"].device)
+            ops.evict(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap,
+                      self.n_seen_tokens[0] + 1, memory_size, trigger, n, kept, self._status)
+            if kept is not None:
+                self.last_kept_idx = kept.view(nl, self._batch, self._hkv, memory_size)
+        else:
+            for l in fire:
+                if self.record_kept:
+                    kept = torch.empty(nseg, memory_size, dtype=torch.int32, device=s["k"].device)
+                ops.evict(s["k"][l], s["v"][l], s["beta"][l], s["pos"][l], s["len"][l], s["cu"][l], nseg, nseg,
+                          self._cap, self.n_seen_tokens[l] + 1, memory_size, trigger, self._cache_len[l], kept,
+                          self._status)
+                if kept is not None:
+                    self.last_kept_idx = kept.view(self._batch, self._hkv, memory_size)
+        for l in fire:
+            self._cache_len[l] = memory_size
+
+    # ------------------------------------------------------------------ misc API (cache_utils.py:112-132,200-223)
+    def check_status(self) -> None:
+        """Synchronises and raises if a kernel reported a device-side problem."""
+        if self._status is not None:
+            code = ops.read_status(self._status)
+            if code:
+                names = {1: "segment capacity exceeded", 2: "segment longer than the stated bound", 3: "bad kept index"}
+                raise ops._lib.TrimKVNativeError(f"device status {code}: {names.get(code, 'unknown')}")
+
+    def log(self, layer_idx: int = None):
+        logs = {}
+        if layer_idx is None:
+            for l in range(len(self)):
+                logs[l] = {"seen_tokens": self.get_seq_length(l),
+                           "kv_positions": self.kv_positions[l].detach().to(torch.int64).cpu()}
+        else:
+            logs["seen_tokens"] = self.get_seq_length(layer_idx)
+            logs["kv_positions"] = self.kv_positions[layer_idx].detach().to(torch.int64).cpu()
+        return logs
+
+    def _clone_from_dense(self, layers, device=None) -> "TrimKVCache":
+        new = TrimKVCache(max_seq_len=self.max_seq_len, device=device or self.device,
+                          memory_size=self._hint_m, buffer_size=self._hint_b)
+        new._seen_tokens = self._seen_tokens
+        for l, (k, v, b, p) in enumerate(layers):
+            new._pending.append((k, v, b, p))
+            new._cache_len.append(k.shape[2])
+            new.n_seen_tokens.append(self.n_seen_tokens[l])
+            new._batch, new._hkv, new._dim = k.shape[0], k.shape[1], k.shape[3]
+        return new
+
+    def batch_select_indices(self, indices: torch.Tensor):
+        dense = [(k[indices, ...].contiguous(), v[indices, ...].contiguous(), b[indices, ...].contiguous(),
+                  p[indices, ...].contiguous()) for (k, v, b, p) in self]
+        other = self._clone_from_dense(dense)
+        self.__dict__.update({k: v for k, v in other.__dict__.items()
+                              if k not in ("key_cache", "value_cache", "retention_weights", "kv_positions",
+                                           "head_lens", "cu_seqlens_k")})
+
+    def batch_split(self, full_batch_size: int, split_size: int) -> List["TrimKVCache"]:
+        out = []
+        for i in range(0, full_batch_size, split_size):
+            dense = [(k[i:i + split_size].contiguous(), v[i:i + split_size].contiguous(),
+                      b[i:i + split_size].contiguous(), p[i:i + split_size].contiguous()) for (k, v, b, p) in self]
+            out.append(self._clone_from_dense(dense))
+        return out
+
+    def copy_to_device(self, device: str) -> "TrimKVCache":
+        dense = [(k.to(device).contiguous(), v.to(device).contiguous(), b.to(device).contiguous(),
+                  p.to(device).contiguous()) for (k, v, b, p) in self]
+        return self._clone_from_dense(dense, device=device)

@@ -1,0 +1,309 @@
+// Split-KV varlen GQA decode attention over the capacity-strided (or packed) flat cache.
+//
+// Replaces batched_dynamic_kv_budget_attention_forward -> flash_attn_varlen_func
+// (src/trimkv/attn/flash_attn.py:79-151): there every (request, KV head) pair becomes one varlen
+// "sequence" of an MQA problem after a split/stack/permute of Q and a host sync for max_seqlen_k.
+// Here the segment table is read on the device; a work item is (segment, chunk of kChunk tokens); each
+// item produces an unnormalised partial output and its (max, sum) in log2 domain, and a combine kernel
+// merges the chunks of a segment.  Per cached token the kernel reads 2*D*elem bytes exactly once.
+#include "tkv_common.cuh"
+#include "tkv_attn.cuh"
+
+namespace tkv {
+
+template <int kDtype> struct Cvt;
+template <> struct Cvt<TKV_BF16> {
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+template <> struct Cvt<TKV_F16> {
+  static __device__ __forceinline__ void unpack(uint32_t w, float& lo, float& hi) {
+    float2 f = __half22float2(*reinterpret_cast<__half2*>(&w));
+    lo = f.x; hi = f.y;
+  }
+  static __device__ __forceinline__ uint32_t pack(float lo, float hi) {
+    __half2 v = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+  }
+};
+
+template <int kDtype>
+__device__ __forceinline__ void unpack8(uint4 v, float* f) {
+  Cvt<kDtype>::unpack(v.x, f[0], f[1]);
+  Cvt<kDtype>::unpack(v.y, f[2], f[3]);
+  Cvt<kDtype>::unpack(v.z, f[4], f[5]);
+  Cvt<kDtype>::unpack(v.w, f[6], f[7]);
+}
+
+constexpr int kAttnWarps = 4;
+constexpr int kAttnThreads = kAttnWarps * 32;
+constexpr int kTokUnroll = 4;
+
+// One CTA = one (segment, chunk).  kLanes = D/8 lanes cover one row with 16-byte loads, so a warp
+// handles 32/kLanes tokens per step; each such lane group keeps its own online-softmax state.
+template <int kDtype, int kD, int kG>
+__global__ void __launch_bounds__(kAttnThreads)
+decode_attn_split_kernel(AttnParams p) {
+  constexpr int kLanes = kD / 8;
+  constexpr int kGroupsPerWarp = 32 / kLanes;
+  constexpr int kStates = kAttnWarps * kGroupsPerWarp;
+  extern __shared__ __align__(16) float smem[];  // [kStates][kG][kD] partial outputs, then [kStates][kG][2]
+  const int seg = blockIdx.x / p.nchunks, chunk = blockIdx.x - seg * p.nchunks;
+  const int len = min(p.seg_len[seg], p.max_len);
+  const int t0 = chunk * p.chunk;
+  if (t0 >= len) return;
+  const int t1 = min(len, t0 + p.chunk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = lane / kLanes, gl = lane - grp * kLanes;
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+  const int64_t row_bytes = (int64_t)kD * 2;
+  const int64_t start = p.seg_start != nullptr ? (int64_t)p.seg_start[seg] : (int64_t)seg * p.cap;
+  const char* kb = p.k + start * row_bytes + gl * 16;
+  const char* vb = p.v + start * row_bytes + gl * 16;
+
+  float qf[kG][8];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    const char* qp = p.q + ((int64_t)b * p.q_sb + (int64_t)(h * kG + g) * p.q_sh) * 2 + gl * 16;
+    unpack8<kDtype>(ld16(qp), qf[g]);
+#pragma unroll
+    for (int d = 0; d < 8; ++d) qf[g][d] *= p.scale_log2;
+  }
+  float m[kG], l[kG], acc[kG][8];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+    for (int d = 0; d < 8; ++d) acc[g][d] = 0.f;
+  }
+
+  constexpr int kStride = kStates;  // tokens advanced by the whole CTA per sub-step
+#pragma unroll 1
+  for (int tb = t0 + warp * kGroupsPerWarp; tb < t1; tb += kStride * kTokUnroll) {
+    const int t = tb + grp;  // the loop bound is warp-uniform; tokens past t1 are masked below
+    uint4 kr[kTokUnroll], vr[kTokUnroll];
+#pragma unroll
+    for (int u = 0; u < kTokUnroll; ++u) {
+      const int tt = t + u * kStride;
+      if (tt < t1) {
+        kr[u] = ld16_stream(kb + (int64_t)tt * row_bytes);
+        vr[u] = ld16_stream(vb + (int64_t)tt * row_bytes);
+      } else {
+        kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    float s[kTokUnroll][kG];
+#pragma unroll
+    for (int u = 0; u < kTokUnroll; ++u) {
+      float kf[8];
+      unpack8<kDtype>(kr[u], kf);
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        float x = 0.f;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) x = fmaf(qf[g][d], kf[d], x);
+        s[u][g] = x;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kTokUnroll; ++u)
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        float x = s[u][g];
+#pragma unroll
+        for (int o = kLanes / 2; o >= 1; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+        s[u][g] = (t + u * kStride < t1) ? x : -INFINITY;
+      }
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      float mn = m[g];
+#pragma unroll
+      for (int u = 0; u < kTokUnroll; ++u) mn = fmaxf(mn, s[u][g]);
+      if (mn == -INFINITY) continue;  // only masked tokens so far (uniform inside the lane group)
+      const float corr = exp2f(m[g] - mn);
+      m[g] = mn;
+      l[g] *= corr;
+#pragma unroll
+      for (int d = 0; d < 8; ++d) acc[g][d] *= corr;
+    }
+#pragma unroll
+    for (int u = 0; u < kTokUnroll; ++u) {
+      float vf[8];
+      unpack8<kDtype>(vr[u], vf);
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        const float pw = (m[g] == -INFINITY) ? 0.f : exp2f(s[u][g] - m[g]);
+        l[g] += pw;
+#pragma unroll
+        for (int d = 0; d < 8; ++d) acc[g][d] = fmaf(pw, vf[d], acc[g][d]);
+      }
+    }
+  }
+
+  // Merge the kStates lane-group states of this CTA.
+  float* so = smem;                           // [kStates][kG][kD]
+  float* sml = smem + kStates * kG * kD;      // [kStates][kG][2]
+  const int state = warp * kGroupsPerWarp + grp;
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    float* dst = so + ((state * kG + g) * kD) + gl * 8;
+    *reinterpret_cast<float4*>(dst) = make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[g][4], acc[g][5], acc[g][6], acc[g][7]);
+    if (gl == 0) { sml[(state * kG + g) * 2] = m[g]; sml[(state * kG + g) * 2 + 1] = l[g]; }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < kG * kD; i += kAttnThreads) {
+    const int g = i / kD, d = i - g * kD;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int s_ = 0; s_ < kStates; ++s_) mx = fmaxf(mx, sml[(s_ * kG + g) * 2]);
+    float o = 0.f, ls = 0.f;
+#pragma unroll
+    for (int s_ = 0; s_ < kStates; ++s_) {
+      const float ms = sml[(s_ * kG + g) * 2];
+      const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - mx);
+      o = fmaf(so[(s_ * kG + g) * kD + d], w, o);
+      ls = fmaf(sml[(s_ * kG + g) * 2 + 1], w, ls);
+    }
+    if (p.nchunks == 1) {
+      // Single chunk: normalise and write the final output here.
+      const float r = ls > 0.f ? o / ls : 0.f;
+      char* op = p.out + ((int64_t)b * p.hq + h * kG + g) * row_bytes;
+      if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16_rn(r);
+      else reinterpret_cast<__half*>(op)[d] = __float2half_rn(r);
+    } else {
+      const int64_t item = (int64_t)seg * p.nchunks + chunk;
+      p.part_o[(item * kG + g) * kD + d] = o;
+      if (d == 0) { p.part_ml[(item * kG + g) * 2] = mx; p.part_ml[(item * kG + g) * 2 + 1] = ls; }
+    }
+  }
+}
+
+// Merges the chunk partials of one segment; also writes zeros for empty segments.
+template <int kDtype, int kD>
+__global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
+  const int seg = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
+  if (p.seg_len[seg] > p.max_len && g == 0 && d == 0) report(p.status, TKV_DEV_LEN_BOUND);
+  const int len = min(p.seg_len[seg], p.max_len);
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+  const int G = p.hq / p.hkv;
+  char* op = p.out + ((int64_t)b * p.hq + h * G + g) * (int64_t)kD * 2;
+  float r = 0.f;
+  if (len > 0) {
+    if (p.nchunks == 1) return;  // written by the split kernel
+    const int nact = (len + p.chunk - 1) / p.chunk;
+    float mx = -INFINITY;
+    for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(((int64_t)seg * p.nchunks + c) * G + g) * 2]);
+    float o = 0.f, ls = 0.f;
+    for (int c = 0; c < nact; ++c) {
+      const int64_t it = ((int64_t)seg * p.nchunks + c) * G + g;
+      const float mc = p.part_ml[it * 2];
+      const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
+      o = fmaf(p.part_o[it * kD + d], w, o);
+      ls = fmaf(p.part_ml[it * 2 + 1], w, ls);
+    }
+    r = ls > 0.f ? o / ls : 0.f;
+  }
+  if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16_rn(r);
+  else reinterpret_cast<__half*>(op)[d] = __float2half_rn(r);
+}
+
+template <int kDtype, int kD, int kG>
+static int launch_split(const AttnParams& p, int nseg, cudaStream_t st) {
+  constexpr int kStates = kAttnWarps * (32 / (kD / 8));
+  const size_t smem = (size_t)kStates * kG * (kD + 2) * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_split_kernel<kDtype, kD, kG>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn: %s", cudaGetErrorString(e));
+  }
+  decode_attn_split_kernel<kDtype, kD, kG><<<(unsigned)((int64_t)nseg * p.nchunks), kAttnThreads, smem, st>>>(p);
+  return check_launch("tkv_decode_attn(split)");
+}
+
+template <int kDtype, int kD>
+static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st) {
+  int rc;
+  switch (G) {
+    case 1: rc = launch_split<kDtype, kD, 1>(p, nseg, st); break;
+    case 2: rc = launch_split<kDtype, kD, 2>(p, nseg, st); break;
+    case 3: rc = launch_split<kDtype, kD, 3>(p, nseg, st); break;
+    case 4: rc = launch_split<kDtype, kD, 4>(p, nseg, st); break;
+    case 5: rc = launch_split<kDtype, kD, 5>(p, nseg, st); break;
+    case 6: rc = launch_split<kDtype, kD, 6>(p, nseg, st); break;
+    case 7: rc = launch_split<kDtype, kD, 7>(p, nseg, st); break;
+    case 8: rc = launch_split<kDtype, kD, 8>(p, nseg, st); break;
+    default: return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn: %d query heads per KV head (supported: 1..8)", G);
+  }
+  if (rc != TKV_OK) return rc;
+  decode_attn_combine_kernel<kDtype, kD><<<dim3(nseg, G), kD, 0, st>>>(p);
+  return check_launch("tkv_decode_attn(combine)");
+}
+
+int attn_chunk_tokens(int nseg, int max_len) {
+  // Enough work items to fill 148 SMs several times over, but chunks long enough to amortise the merge.
+  int chunk = 512;
+  while (chunk > 64 && (int64_t)nseg * ((max_len + chunk - 1) / chunk) < 148 * 8) chunk >>= 1;
+  return chunk;
+}
+
+int launch_decode_attn_simt(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st) {
+  if (kv_dtype == TKV_BF16 && head_dim == 128) return launch_for_g<TKV_BF16, 128>(p, nseg, G, st);
+  if (kv_dtype == TKV_F16 && head_dim == 128) return launch_for_g<TKV_F16, 128>(p, nseg, G, st);
+  if (kv_dtype == TKV_BF16 && head_dim == 64) return launch_for_g<TKV_BF16, 64>(p, nseg, G, st);
+  if (kv_dtype == TKV_F16 && head_dim == 64) return launch_for_g<TKV_F16, 64>(p, nseg, G, st);
+  return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn: head_dim=%d dtype=%d (supported: bf16/f16, 64 or 128)", head_dim,
+              kv_dtype);
+}
+
+}  // namespace tkv
+
+extern "C" size_t tkv_decode_attn_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len) {
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || head_dim <= 0 || max_len <= 0 || hq % hkv != 0) return 0;
+  const int nseg = batch * hkv, G = hq / hkv;
+  const int chunk = tkv::attn_chunk_tokens(nseg, max_len);
+  const int64_t items = (int64_t)nseg * ((max_len + chunk - 1) / chunk);
+  return (size_t)(items * G * (head_dim + 2) * sizeof(float) + 256);
+}
+
+extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
+                               const void* k_cache, const void* v_cache,
+                               const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                               void* out, void* workspace, size_t workspace_bytes,
+                               int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                               float scale, int max_len, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!q || !k_cache || !v_cache || !seg_len || !out) return fail(TKV_ERR_ARG, "tkv_decode_attn: NULL pointer argument");
+  if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || head_dim <= 0 || max_len <= 0)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn: bad sizes batch=%d hq=%d hkv=%d head_dim=%d max_len=%d", batch, hq, hkv,
+                head_dim, max_len);
+  if (seg_start == nullptr && cap <= 0) return fail(TKV_ERR_ARG, "tkv_decode_attn: cap=%lld without seg_start", (long long)cap);
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+    return fail(TKV_ERR_ARG, "tkv_decode_attn: pointers must be 16-byte aligned");
+  if ((q_sb * 2) % 16 || (q_sh * 2) % 16) return fail(TKV_ERR_ARG, "tkv_decode_attn: q strides must be multiples of 16 bytes");
+  if (batch == 0) return TKV_OK;
+  const size_t need = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
+    return fail(TKV_ERR_ARG, "tkv_decode_attn: workspace of %zu bytes (256-byte aligned) required, got %zu", need,
+                workspace_bytes);
+  const int nseg = batch * hkv, G = hq / hkv;
+  AttnParams p;
+  p.q = (const char*)q; p.q_sb = q_sb; p.q_sh = q_sh;
+  p.k = (const char*)k_cache; p.v = (const char*)v_cache;
+  p.seg_len = seg_len; p.seg_start = seg_start; p.cap = cap;
+  p.out = (char*)out;
+  p.chunk = attn_chunk_tokens(nseg, max_len);
+  p.nchunks = (max_len + p.chunk - 1) / p.chunk;
+  p.part_ml = reinterpret_cast<float*>(workspace);
+  p.part_o = p.part_ml + (((int64_t)nseg * p.nchunks * G * 2 + 63) / 64) * 64;
+  p.hq = hq; p.hkv = hkv; p.max_len = max_len;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+}

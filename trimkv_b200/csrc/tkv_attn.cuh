@@ -1,0 +1,23 @@
+// Parameters shared by the decode-attention kernels.
+#pragma once
+#include <stdint.h>
+
+namespace tkv {
+
+struct AttnParams {
+  const char* q; int64_t q_sb, q_sh;      // element strides of q[b, head, :]
+  const char* k; const char* v;
+  const int32_t* seg_len; const int32_t* seg_start; int64_t cap;
+  char* out;                              // [batch, hq, D]
+  float* part_ml;                         // [nseg, nchunks, G, 2]  (max, sum) in log2 domain
+  float* part_o;                          // [nseg, nchunks, G, D]  unnormalised partial outputs
+  int chunk, nchunks;
+  int hq, hkv, max_len;
+  float scale_log2;                       // softmax scale * log2(e)
+  int32_t* status;
+};
+
+// Tokens per work item, a pure function of the problem size (the workspace size depends on it).
+int attn_chunk_tokens(int nseg, int max_len);
+
+}  // namespace tkv

@@ -1,0 +1,81 @@
+// Shared helpers of the trimkv_b200 kernels (sm_100a).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include "../../include/trimkv_b200.h"
+
+namespace tkv {
+
+// Records a host-side error message for tkv_last_error() and returns `code`.
+int fail(int code, const char* fmt, ...);
+// Checks cudaGetLastError() after a launch.
+int check_launch(const char* what);
+
+inline int elem_size(int dtype) {
+  return dtype == TKV_F32 ? 4 : (dtype == TKV_BF16 || dtype == TKV_F16) ? 2 : 0;
+}
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+__device__ __forceinline__ void report(int32_t* status, int code) {
+  if (status != nullptr) atomicMax(status, code);
+}
+
+// Order-preserving map fp32 -> uint32 with the selection's conventions:
+// larger score = larger key, -0.0 and +0.0 share a key, NaN is the largest key.
+__device__ __forceinline__ uint32_t score_key(float s) {
+  if (s != s) return 0xFFFFFFFFu;
+  s = s + 0.0f;  // -0.0 -> +0.0
+  uint32_t u = __float_as_uint(s);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// score = f32(log beta) * f32(q_idx - pos): exactly one rounding, never contracted.
+__device__ __forceinline__ float retention_score(float log_beta, int32_t pos, int64_t q_idx) {
+  return __fmul_rn(log_beta, __ll2float_rn(q_idx - (int64_t)pos));
+}
+
+__device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ void st16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
+
+// Streaming (evict-first) 16-byte accesses for data that is touched once.
+__device__ __forceinline__ uint4 ld16_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
+template <int kThreads>
+__device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums /* [kThreads/32 + 1] */, int* total) {
+  // Inclusive warp scan, then scan of the warp totals by warp 0.
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int x = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    int y = __shfl_up_sync(0xffffffffu, x, o);
+    if (lane >= o) x += y;
+  }
+  if (lane == 31) warp_sums[warp] = x;
+  __syncthreads();
+  if (warp == 0) {
+    constexpr int kWarps = kThreads / 32;
+    int w = lane < kWarps ? warp_sums[lane] : 0;
+    int s = w;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      int y = __shfl_up_sync(0xffffffffu, s, o);
+      if (lane >= o) s += y;
+    }
+    if (lane < kWarps) warp_sums[lane] = s - w;  // exclusive
+    if (lane == kWarps - 1) warp_sums[kWarps] = s;
+  }
+  __syncthreads();
+  int excl = warp_sums[warp] + x - v;
+  *total = warp_sums[kThreads / 32];
+  __syncthreads();  // warp_sums may be reused by the caller right away
+  return excl;
+}
+
+}  // namespace tkv

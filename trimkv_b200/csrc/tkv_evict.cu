@@ -1,0 +1,403 @@
+// Retention-score top-M eviction: selection, stable stream compaction, cu_seqlens rebuild.
+//
+// Replaces TrimKVCache.compress / compress_layer (src/trimkv/cache_utils.py:140-198): fp32 score,
+// torch.topk, torch.sort and four gathers into fresh allocations.  Here one CTA owns one segment:
+//   1. keys: score = f32(log beta) * f32(q_idx - pos) mapped to an order-preserving uint32, kept in
+//      shared memory (4 bytes per live token);
+//   2. 4-pass, 8-bit radix select of the M-th largest key, warp-aggregated histogram updates;
+//   3. one ordered block scan turns "key > T, or key == T and among the first r equal keys" into the
+//      ascending list of kept indices (written over the keys);
+//   4. in-place stable compaction: tiles of kept rows are loaded into registers (16-byte vectors),
+//      a barrier, then stored at their destination.  dst <= src for every row and tiles are handled
+//      in ascending order, so a tile's stores can only land on rows whose content was already consumed.
+// Algorithmic bytes per segment: 8n (scan) + 2*M*row_pair_bytes (move K,V) + 8M (metadata).
+#include "tkv_common.cuh"
+
+namespace tkv {
+
+constexpr int kEvictThreads = 256;
+constexpr int kEvictUnroll = 8;              // 16-byte vectors in flight per thread and tile
+constexpr int kMaxSelectLen = 57000;         // keys must fit in 227 KB of shared memory
+
+struct SelectScratch {
+  int hist[256];
+  int warp_sums[kEvictThreads / 32 + 1];
+  int sel_digit;
+  int sel_k;
+  int first_evicted;
+};
+
+// Finds T = key of the m-th largest element and r = how many elements equal to T are kept.
+// All threads of the block call this; keys[0..n) are in shared memory.
+__device__ __forceinline__ void radix_select_mth(const uint32_t* keys, int n, int m, SelectScratch* sc,
+                                                 uint32_t* thresh, int* n_eq_keep) {
+  const int lane = threadIdx.x & 31;
+  uint32_t prefix = 0, decided = 0;
+  int k = m;
+  const int n_round = (n + kEvictThreads - 1) / kEvictThreads * kEvictThreads;
+#pragma unroll 1
+  for (int shift = 24; shift >= 0; shift -= 8) {
+    sc->hist[threadIdx.x] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n_round; i += kEvictThreads) {
+      uint32_t key = i < n ? keys[i] : 0u;
+      const bool valid = i < n && (key & decided) == prefix;
+      const int digit = valid ? (int)((key >> shift) & 255u) : 256 + lane;
+      // Lanes with the same digit elect one leader that adds their count: the high digits of the
+      // scores are nearly constant, which would serialise plain shared-memory atomics.
+      const unsigned peers = __match_any_sync(0xffffffffu, digit);
+      if (valid && lane == __ffs(peers) - 1) atomicAdd(&sc->hist[digit], __popc(peers));
+    }
+    __syncthreads();
+    // Thread t looks at bin 255 - t: an exclusive scan in this order is the count of strictly larger digits.
+    const int bin = 255 - threadIdx.x;
+    const int c = sc->hist[bin];
+    int total;
+    const int above = block_exclusive_scan<kEvictThreads>(c, sc->warp_sums, &total);
+    if (above < k && k <= above + c) { sc->sel_digit = bin; sc->sel_k = k - above; }
+    __syncthreads();
+    prefix |= (uint32_t)sc->sel_digit << shift;
+    decided |= 255u << shift;
+    k = sc->sel_k;
+    __syncthreads();
+  }
+  *thresh = prefix;
+  *n_eq_keep = k;
+}
+
+// Overwrites keys[0..m) with the ascending indices of the kept elements; returns the first evicted index.
+__device__ __forceinline__ int build_kept_list(uint32_t* keys, int n, uint32_t thresh, int n_eq_keep,
+                                               SelectScratch* sc) {
+  constexpr int kItems = 4;
+  constexpr int kChunk = kEvictThreads * kItems;
+  if (threadIdx.x == 0) sc->first_evicted = n;
+  int eq_base = 0, gt_base = 0;
+#pragma unroll 1
+  for (int base = 0; base < n; base += kChunk) {
+    uint32_t key[kItems];
+    int packed = 0;  // low 16 bits: #equal, high 16 bits: #greater (n < 65536)
+    const int i0 = base + threadIdx.x * kItems;
+#pragma unroll
+    for (int u = 0; u < kItems; ++u) {
+      const int i = i0 + u;
+      key[u] = i < n ? keys[i] : 0u;
+      if (i < n) packed += (key[u] == thresh) ? 1 : (key[u] > thresh ? (1 << 16) : 0);
+    }
+    int total;
+    const int excl = block_exclusive_scan<kEvictThreads>(packed, sc->warp_sums, &total);  // syncs inside
+    int eq = eq_base + (excl & 0xffff), gt = gt_base + (excl >> 16);
+    int my_first_evicted = n;
+#pragma unroll
+    for (int u = 0; u < kItems; ++u) {
+      const int i = i0 + u;
+      if (i >= n) break;
+      const bool is_eq = key[u] == thresh, is_gt = key[u] > thresh;
+      const bool keep = is_gt || (is_eq && eq < n_eq_keep);
+      if (keep) keys[gt + min(eq, n_eq_keep)] = (uint32_t)i;
+      else my_first_evicted = min(my_first_evicted, i);
+      eq += is_eq; gt += is_gt;
+    }
+    if (my_first_evicted < n) atomicMin(&sc->first_evicted, my_first_evicted);
+    eq_base += total & 0xffff; gt_base += total >> 16;
+  }
+  __syncthreads();
+  return sc->first_evicted;
+}
+
+struct EvictParams {
+  char* k; char* v; float* beta; int32_t* pos;
+  int32_t* seg_len;
+  int nseg; int64_t cap; int row_vecs; int64_t q_idx;
+  int m, trigger_len, max_len;
+  int32_t* kept_idx_out; int32_t* status;
+};
+
+__global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParams p) {
+  extern __shared__ __align__(16) uint32_t keys[];
+  __shared__ SelectScratch sc;
+  const int seg = blockIdx.x;
+  const int n = p.seg_len[seg];
+  if (n < p.trigger_len || n <= p.m) return;
+  if (n > p.max_len || n > p.cap) {
+    if (threadIdx.x == 0) report(p.status, TKV_DEV_LEN_BOUND);
+    return;
+  }
+  const int64_t row0 = (int64_t)seg * p.cap;
+  for (int i = threadIdx.x; i < n; i += kEvictThreads)
+    keys[i] = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+  __syncthreads();
+  uint32_t thresh; int n_eq_keep;
+  radix_select_mth(keys, n, p.m, &sc, &thresh, &n_eq_keep);
+  const int j0 = build_kept_list(keys, n, thresh, n_eq_keep, &sc);
+  const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
+  if (p.kept_idx_out != nullptr)
+    for (int j = threadIdx.x; j < p.m; j += kEvictThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
+
+  // Stable in-place compaction of rows j0..m (rows before the first evicted one stay where they are).
+  const int nvec = 2 * p.row_vecs;                       // K vectors then V vectors of one token
+  const int tile_rows = min(kEvictThreads, (kEvictThreads * kEvictUnroll) / nvec);
+  const int64_t row_bytes = (int64_t)p.row_vecs * 16;
+  char* kbase = p.k + row0 * row_bytes;
+  char* vbase = p.v + row0 * row_bytes;
+#pragma unroll 1
+  for (int jb = j0; jb < p.m; jb += tile_rows) {
+    const int rows = min(tile_rows, p.m - jb);
+    const int nv = rows * nvec;
+    uint4 reg[kEvictUnroll];
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int i = threadIdx.x + u * kEvictThreads;
+      if (i < nv) {
+        const int r = i / nvec, c = i - r * nvec;
+        const int src = kept[jb + r];
+        const char* ptr = (c < p.row_vecs ? kbase + (int64_t)c * 16 : vbase + (int64_t)(c - p.row_vecs) * 16) +
+                          (int64_t)src * row_bytes;
+        reg[u] = ld16(ptr);
+      }
+    }
+    float bt = 0.f; int32_t ps = 0;
+    if (threadIdx.x < rows) {
+      const int src = kept[jb + threadIdx.x];
+      bt = p.beta[row0 + src];
+      ps = p.pos[row0 + src];
+    }
+    __syncthreads();  // every load of this tile is performed before any of its stores
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int i = threadIdx.x + u * kEvictThreads;
+      if (i < nv) {
+        const int r = i / nvec, c = i - r * nvec;
+        char* ptr = (c < p.row_vecs ? kbase + (int64_t)c * 16 : vbase + (int64_t)(c - p.row_vecs) * 16) +
+                    (int64_t)(jb + r) * row_bytes;
+        st16(ptr, reg[u]);
+      }
+    }
+    if (threadIdx.x < rows) {
+      p.beta[row0 + jb + threadIdx.x] = bt;
+      p.pos[row0 + jb + threadIdx.x] = ps;
+    }
+  }
+  if (threadIdx.x == 0) p.seg_len[seg] = p.m;
+}
+
+struct SelectParams {
+  const float* beta; int64_t beta_stride; const int32_t* pos; int64_t pos_stride;
+  const int32_t* seg_len; int n_uniform; int nseg; int64_t q_idx;
+  int m, trigger_len, max_len;
+  int32_t* kept_idx; int32_t* kept_cnt; int32_t* status;
+};
+
+__global__ void __launch_bounds__(kEvictThreads) evict_select_kernel(SelectParams p) {
+  extern __shared__ __align__(16) uint32_t keys[];
+  __shared__ SelectScratch sc;
+  const int seg = blockIdx.x;
+  const int n = p.seg_len != nullptr ? p.seg_len[seg] : p.n_uniform;
+  if (n < p.trigger_len || n <= p.m) {
+    if (threadIdx.x == 0) p.kept_cnt[seg] = max(n, 0);
+    return;
+  }
+  if (n > p.max_len) {
+    if (threadIdx.x == 0) { report(p.status, TKV_DEV_LEN_BOUND); p.kept_cnt[seg] = n; }
+    return;
+  }
+  const float* beta = p.beta + (int64_t)seg * p.beta_stride;
+  const int32_t* pos = p.pos + (int64_t)seg * p.pos_stride;
+  for (int i = threadIdx.x; i < n; i += kEvictThreads)
+    keys[i] = score_key(retention_score(beta[i], pos[i], p.q_idx));
+  __syncthreads();
+  uint32_t thresh; int n_eq_keep;
+  radix_select_mth(keys, n, p.m, &sc, &thresh, &n_eq_keep);
+  build_kept_list(keys, n, thresh, n_eq_keep, &sc);
+  const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
+  for (int j = threadIdx.x; j < p.m; j += kEvictThreads) p.kept_idx[(int64_t)seg * p.m + j] = kept[j];
+  if (threadIdx.x == 0) p.kept_cnt[seg] = p.m;
+}
+
+struct CompactParams {
+  char* k_dst; char* v_dst; float* beta_dst; int32_t* pos_dst; int64_t cap;
+  const char* k_src; const char* v_src; int64_t k_sb, k_sh, k_ss;  // byte strides
+  const float* beta_src; int64_t beta_stride; const int32_t* pos_src; int64_t pos_stride;
+  const int32_t* kept_idx; int64_t kept_stride; const int32_t* kept_cnt;
+  int32_t* seg_len; int hkv, n_src, row_vecs;
+  int32_t* status;
+};
+
+constexpr int kCompactRows = 32;
+// Out-of-place gather: any number of CTAs per segment, no ordering hazards.
+__global__ void __launch_bounds__(256) compact_gather_kernel(CompactParams p) {
+  const int seg = blockIdx.y;
+  const int cnt = p.kept_cnt != nullptr ? p.kept_cnt[seg] : p.n_src;
+  const int jb = blockIdx.x * kCompactRows;
+  if (blockIdx.x == 0 && threadIdx.x == 0) p.seg_len[seg] = min(cnt, (int)min((int64_t)INT32_MAX, p.cap));
+  if (jb >= cnt) return;
+  if (cnt > p.cap) {
+    if (threadIdx.x == 0) report(p.status, TKV_DEV_CAPACITY);
+    return;
+  }
+  const bool identity = p.kept_idx == nullptr || cnt == p.n_src;
+  const int32_t* kept = identity ? nullptr : p.kept_idx + (int64_t)seg * p.kept_stride;
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+  const int rows = min(kCompactRows, cnt - jb);
+  const int nvec = 2 * p.row_vecs;
+  const int64_t row_bytes = (int64_t)p.row_vecs * 16;
+  const int64_t dst_row0 = (int64_t)seg * p.cap;
+  const char* ksrc = p.k_src + b * p.k_sb + h * p.k_sh;
+  const char* vsrc = p.v_src + b * p.k_sb + h * p.k_sh;
+  for (int i = threadIdx.x; i < rows * nvec; i += blockDim.x) {
+    const int r = i / nvec, c = i - r * nvec;
+    const int src = identity ? jb + r : kept[jb + r];
+    if ((unsigned)src >= (unsigned)p.n_src) { report(p.status, TKV_DEV_BAD_INDEX); continue; }
+    const bool is_v = c >= p.row_vecs;
+    const int cc = is_v ? c - p.row_vecs : c;
+    const char* sp = (is_v ? vsrc : ksrc) + (int64_t)src * p.k_ss + (int64_t)cc * 16;
+    char* dp = (is_v ? p.v_dst : p.k_dst) + (dst_row0 + jb + r) * row_bytes + (int64_t)cc * 16;
+    st16(dp, ld16_stream(sp));
+  }
+  for (int r = threadIdx.x; r < rows; r += blockDim.x) {
+    const int src = identity ? jb + r : kept[jb + r];
+    if ((unsigned)src >= (unsigned)p.n_src) continue;
+    p.beta_dst[dst_row0 + jb + r] = p.beta_src[(int64_t)seg * p.beta_stride + src];
+    p.pos_dst[dst_row0 + jb + r] = p.pos_src[(int64_t)seg * p.pos_stride + src];
+  }
+}
+
+// cu_seqlens[g, 0..group] = exclusive prefix sum of seg_len[g*group ..]; one CTA per group.
+__global__ void __launch_bounds__(256) rebuild_cu_kernel(const int32_t* seg_len, int32_t* cu, int group) {
+  __shared__ int warp_sums[256 / 32 + 1];
+  const int g = blockIdx.x;
+  const int32_t* len = seg_len + (int64_t)g * group;
+  int32_t* out = cu + (int64_t)g * (group + 1);
+  int running = 0;
+  for (int base = 0; base < group; base += 256) {
+    const int i = base + threadIdx.x;
+    const int v = i < group ? len[i] : 0;
+    int total;
+    const int excl = block_exclusive_scan<256>(v, warp_sums, &total);
+    if (i < group) out[i] = running + excl;
+    running += total;
+  }
+  if (threadIdx.x == 0) out[group] = running;
+}
+
+static int launch_rebuild(const int32_t* seg_len, int32_t* cu, int nseg, int group, cudaStream_t st) {
+  if (cu == nullptr || nseg == 0) return TKV_OK;
+  if (group <= 0 || nseg % group != 0)
+    return fail(TKV_ERR_ARG, "cu_seqlens rebuild: nseg=%d is not a multiple of group=%d", nseg, group);
+  rebuild_cu_kernel<<<nseg / group, 256, 0, st>>>(seg_len, cu, group);
+  return check_launch("tkv_rebuild_cu_seqlens");
+}
+
+template <typename K>
+static int set_smem(K kernel, size_t bytes, const char* what) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "%s: shared memory %zu: %s", what, bytes, cudaGetErrorString(e));
+  }
+  return TKV_OK;
+}
+
+}  // namespace tkv
+
+extern "C" int tkv_rebuild_cu_seqlens(const int32_t* seg_len, int32_t* cu_seqlens, int nseg, int group,
+                                      tkv_stream_t stream) {
+  if (!seg_len || !cu_seqlens) return tkv::fail(TKV_ERR_ARG, "tkv_rebuild_cu_seqlens: NULL pointer argument");
+  if (nseg < 0) return tkv::fail(TKV_ERR_ARG, "tkv_rebuild_cu_seqlens: nseg=%d", nseg);
+  return tkv::launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
+}
+
+extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                         int32_t* seg_len, int32_t* cu_seqlens, int group,
+                         int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                         int memory_size, int trigger_len, int max_len,
+                         int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  const int es = elem_size(kv_dtype);
+  if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
+  if (!k_cache || !v_cache || !beta_cache || !pos_cache || !seg_len)
+    return fail(TKV_ERR_ARG, "tkv_evict: NULL pointer argument");
+  if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0)
+    return fail(TKV_ERR_ARG, "tkv_evict: bad sizes nseg=%d cap=%lld head_dim=%d M=%d max_len=%d", nseg,
+                (long long)cap, head_dim, memory_size, max_len);
+  if (max_len > kMaxSelectLen)
+    return fail(TKV_ERR_UNSUPPORTED, "tkv_evict: max_len=%d exceeds %d", max_len, kMaxSelectLen);
+  const int64_t row_bytes = (int64_t)head_dim * es;
+  if (row_bytes % 16 != 0 || 2 * (row_bytes / 16) > kEvictThreads * kEvictUnroll)
+    return fail(TKV_ERR_ARG, "tkv_evict: unsupported row of %lld bytes", (long long)row_bytes);
+  if (!aligned16(k_cache) || !aligned16(v_cache)) return fail(TKV_ERR_ARG, "tkv_evict: K/V must be 16-byte aligned");
+  if (nseg == 0) return TKV_OK;
+  EvictParams p;
+  p.k = (char*)k_cache; p.v = (char*)v_cache; p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len;
+  p.nseg = nseg; p.cap = cap; p.row_vecs = (int)(row_bytes / 16); p.q_idx = q_idx;
+  p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
+  p.kept_idx_out = kept_idx_out; p.status = status;
+  const size_t smem = (size_t)max_len * 4;
+  int rc = set_smem(evict_inplace_kernel, smem, "tkv_evict");
+  if (rc != TKV_OK) return rc;
+  evict_inplace_kernel<<<nseg, kEvictThreads, smem, (cudaStream_t)stream>>>(p);
+  rc = check_launch("tkv_evict");
+  if (rc != TKV_OK) return rc;
+  return launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
+}
+
+extern "C" int tkv_evict_select(const float* beta, int64_t beta_stride, const int32_t* pos, int64_t pos_stride,
+                                const int32_t* seg_len, int n_uniform, int nseg, int64_t q_idx,
+                                int memory_size, int trigger_len, int max_len,
+                                int32_t* kept_idx, int32_t* kept_cnt, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!beta || !pos || !kept_idx || !kept_cnt) return fail(TKV_ERR_ARG, "tkv_evict_select: NULL pointer argument");
+  if (nseg < 0 || memory_size <= 0 || max_len <= 0 || (seg_len == nullptr && n_uniform < 0))
+    return fail(TKV_ERR_ARG, "tkv_evict_select: bad sizes nseg=%d M=%d max_len=%d", nseg, memory_size, max_len);
+  if (seg_len == nullptr && n_uniform > max_len)
+    return fail(TKV_ERR_ARG, "tkv_evict_select: n_uniform=%d > max_len=%d", n_uniform, max_len);
+  if (max_len > kMaxSelectLen)
+    return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_select: max_len=%d exceeds %d", max_len, kMaxSelectLen);
+  if (nseg == 0) return TKV_OK;
+  SelectParams p;
+  p.beta = beta; p.beta_stride = beta_stride; p.pos = pos; p.pos_stride = pos_stride;
+  p.seg_len = seg_len; p.n_uniform = n_uniform; p.nseg = nseg; p.q_idx = q_idx;
+  p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
+  p.kept_idx = kept_idx; p.kept_cnt = kept_cnt; p.status = status;
+  const size_t smem = (size_t)max_len * 4;
+  int rc = set_smem(evict_select_kernel, smem, "tkv_evict_select");
+  if (rc != TKV_OK) return rc;
+  evict_select_kernel<<<nseg, kEvictThreads, smem, (cudaStream_t)stream>>>(p);
+  return check_launch("tkv_evict_select");
+}
+
+extern "C" int tkv_compact(void* k_dst, void* v_dst, float* beta_dst, int32_t* pos_dst, int64_t cap,
+                           const void* k_src, const void* v_src, int64_t k_sb, int64_t k_sh, int64_t k_ss,
+                           const float* beta_src, int64_t beta_stride, const int32_t* pos_src, int64_t pos_stride,
+                           const int32_t* kept_idx, int64_t kept_stride, const int32_t* kept_cnt,
+                           int32_t* seg_len, int32_t* cu_seqlens, int group,
+                           int batch, int hkv, int n_src, int head_dim, int kv_dtype,
+                           int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  const int es = elem_size(kv_dtype);
+  if (es == 0) return fail(TKV_ERR_ARG, "tkv_compact: unknown kv_dtype %d", kv_dtype);
+  if (!k_dst || !v_dst || !beta_dst || !pos_dst || !k_src || !v_src || !beta_src || !pos_src || !seg_len)
+    return fail(TKV_ERR_ARG, "tkv_compact: NULL pointer argument");
+  if (batch < 0 || hkv <= 0 || n_src < 0 || head_dim <= 0 || cap <= 0)
+    return fail(TKV_ERR_ARG, "tkv_compact: bad sizes");
+  const int64_t row_bytes = (int64_t)head_dim * es;
+  if (row_bytes % 16 != 0) return fail(TKV_ERR_ARG, "tkv_compact: row of %lld bytes is not a multiple of 16", (long long)row_bytes);
+  if (!aligned16(k_dst) || !aligned16(v_dst) || !aligned16(k_src) || !aligned16(v_src))
+    return fail(TKV_ERR_ARG, "tkv_compact: K/V pointers must be 16-byte aligned");
+  if ((k_sb * es) % 16 || (k_sh * es) % 16 || (k_ss * es) % 16)
+    return fail(TKV_ERR_ARG, "tkv_compact: K/V strides must be multiples of 16 bytes");
+  const int64_t nseg = (int64_t)batch * hkv;
+  if (nseg > 65535) return fail(TKV_ERR_UNSUPPORTED, "tkv_compact: more than 65535 segments per call");
+  if (nseg == 0) return TKV_OK;
+  CompactParams p;
+  p.k_dst = (char*)k_dst; p.v_dst = (char*)v_dst; p.beta_dst = beta_dst; p.pos_dst = pos_dst; p.cap = cap;
+  p.k_src = (const char*)k_src; p.v_src = (const char*)v_src;
+  p.k_sb = k_sb * es; p.k_sh = k_sh * es; p.k_ss = k_ss * es;
+  p.beta_src = beta_src; p.beta_stride = beta_stride; p.pos_src = pos_src; p.pos_stride = pos_stride;
+  p.kept_idx = kept_idx; p.kept_stride = kept_stride; p.kept_cnt = kept_cnt;
+  p.seg_len = seg_len; p.hkv = hkv; p.n_src = n_src; p.row_vecs = (int)(row_bytes / 16); p.status = status;
+  const int max_rows = (int)(n_src < cap ? n_src : cap);
+  dim3 grid((max_rows + kCompactRows - 1) / kCompactRows > 0 ? (max_rows + kCompactRows - 1) / kCompactRows : 1, (unsigned)nseg);
+  compact_gather_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(p);
+  int rc = check_launch("tkv_compact");
+  if (rc != TKV_OK) return rc;
+  return launch_rebuild(seg_len, cu_seqlens, (int)nseg, group, (cudaStream_t)stream);
+}

@@ -1,0 +1,129 @@
+"""Tensor-level wrappers over the C ABI: validate, pass raw pointers, launch on torch's current stream.
+
+PyTorch is used for device memory and streams only; all arithmetic of the cache path runs in the
+CUDA kernels of libtrimkv_b200.so.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import TKV_BF16, TKV_F16, TKV_F32, check, lib
+
+_DTYPE = {torch.bfloat16: TKV_BF16, torch.float16: TKV_F16, torch.float32: TKV_F32}
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DTYPE[dt]
+    except KeyError:
+        raise TypeError(f"unsupported dtype {dt}") from None
+
+
+def _stream(t: torch.Tensor) -> int:
+    if not t.is_cuda:
+        raise _lib.TrimKVNativeError("trimkv_b200 runs on CUDA tensors only (no CPU path)")
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def new_status(device) -> torch.Tensor:
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+def read_status(status: torch.Tensor) -> int:
+    """Synchronises the current stream and returns (then clears) the device status word."""
+    return lib().tkv_read_status(status.data_ptr(), _stream(status))
+
+
+def append(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens,
+           k_new, v_new, beta_new, pos_new, cap: int, status=None) -> None:
+    """In-place append of ``k_new/v_new [B,H,S,D]``, ``beta_new [B,H,S]``, ``pos_new`` int64 ``[S]`` or ``[B,H,S]``."""
+    b, h, s, d = k_new.shape
+    if v_new.shape != k_new.shape or v_new.stride() != k_new.stride():
+        v_new = v_new.contiguous(); k_new = k_new.contiguous()
+    if k_new.stride(3) != 1:
+        k_new = k_new.contiguous(); v_new = v_new.contiguous()
+    if pos_new.dtype != torch.int64:
+        pos_new = pos_new.to(torch.int64)
+    if pos_new.dim() == 1:
+        ps = (0, 0, pos_new.stride(0))
+    else:
+        pos_new = pos_new.expand(b, h, s)
+        ps = pos_new.stride()
+    if beta_new.shape != (b, h, s):
+        raise ValueError(f"retention weights {tuple(beta_new.shape)} do not match keys {tuple(k_new.shape)}")
+    rc = lib().tkv_append(
+        k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
+        seg_len.data_ptr(), _ptr(cu_seqlens),
+        k_new.data_ptr(), v_new.data_ptr(), k_new.stride(0), k_new.stride(1), k_new.stride(2),
+        beta_new.data_ptr(), dtype_code(beta_new.dtype), beta_new.stride(0), beta_new.stride(1), beta_new.stride(2),
+        pos_new.data_ptr(), ps[0], ps[1], ps[2],
+        b, h, s, d, cap, dtype_code(k_cache.dtype), _ptr(status), _stream(k_cache))
+    check(rc, "tkv_append")
+
+
+def evict(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
+          q_idx: int, memory_size: int, trigger_len: int, max_len: int, kept_idx_out=None, status=None) -> None:
+    d = k_cache.shape[-1]
+    rc = lib().tkv_evict(
+        k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
+        seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
+        memory_size, trigger_len, max_len, _ptr(kept_idx_out), _ptr(status), _stream(k_cache))
+    check(rc, "tkv_evict")
+
+
+def evict_select(beta, pos, seg_len, n_uniform: int, nseg: int, q_idx: int, memory_size: int,
+                 trigger_len: int, max_len: int, kept_idx, kept_cnt, status=None) -> None:
+    """beta f32 ``[nseg, n]`` (row stride taken from the tensor); pos i32 ``[nseg, n]`` or ``[n]`` (shared)."""
+    if beta.dtype != torch.float32 or pos.dtype != torch.int32:
+        raise TypeError("evict_select wants f32 log beta and i32 positions")
+    pos_stride = 0 if pos.dim() == 1 else pos.stride(0)
+    rc = lib().tkv_evict_select(
+        beta.data_ptr(), beta.stride(0), pos.data_ptr(), pos_stride, _ptr(seg_len), n_uniform, nseg, q_idx,
+        memory_size, trigger_len, max_len, kept_idx.data_ptr(), kept_cnt.data_ptr(), _ptr(status), _stream(beta))
+    check(rc, "tkv_evict_select")
+
+
+def compact(k_dst, v_dst, beta_dst, pos_dst, cap: int, k_src, v_src, beta_src, pos_src, kept_idx, kept_cnt,
+            seg_len, cu_seqlens, group: int, status=None) -> None:
+    """Gather rows of dense ``k_src/v_src [B,H,n,D]`` listed in ``kept_idx [B*H, M]`` into a strided cache."""
+    b, h, n, d = k_src.shape
+    if v_src.stride() != k_src.stride() or k_src.stride(3) != 1:
+        k_src = k_src.contiguous(); v_src = v_src.contiguous()
+    pos_stride = 0 if pos_src.dim() == 1 else pos_src.stride(0)
+    rc = lib().tkv_compact(
+        k_dst.data_ptr(), v_dst.data_ptr(), beta_dst.data_ptr(), pos_dst.data_ptr(), cap,
+        k_src.data_ptr(), v_src.data_ptr(), k_src.stride(0), k_src.stride(1), k_src.stride(2),
+        beta_src.data_ptr(), beta_src.stride(0), pos_src.data_ptr(), pos_stride,
+        _ptr(kept_idx), 0 if kept_idx is None else kept_idx.stride(0), _ptr(kept_cnt),
+        seg_len.data_ptr(), _ptr(cu_seqlens), group, b, h, n, d, dtype_code(k_dst.dtype),
+        _ptr(status), _stream(k_dst))
+    check(rc, "tkv_compact")
+
+
+def rebuild_cu_seqlens(seg_len, cu_seqlens, nseg: int, group: int) -> None:
+    check(lib().tkv_rebuild_cu_seqlens(seg_len.data_ptr(), cu_seqlens.data_ptr(), nseg, group, _stream(seg_len)),
+          "tkv_rebuild_cu_seqlens")
+
+
+def decode_attn_workspace_bytes(batch: int, hq: int, hkv: int, head_dim: int, max_len: int) -> int:
+    return int(lib().tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len))
+
+
+def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspace, hkv: int, scale: float,
+                max_len: int, status=None) -> None:
+    """q ``[B,Hq,D]`` (any batch/head strides), out ``[B,Hq,D]`` contiguous, workspace uint8."""
+    b, hq, d = q.shape
+    if q.stride(2) != 1:
+        q = q.contiguous()
+    rc = lib().tkv_decode_attn(
+        q.data_ptr(), q.stride(0), q.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
+        seg_len.data_ptr(), _ptr(seg_start), cap, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
+        b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len, _ptr(status), _stream(q))
+    check(rc, "tkv_decode_attn")
