@@ -1,0 +1,362 @@
+#!/usr/bin/env python
+"""Benchmark of the TRIM-KV cache hot path on B200: decode tok/s of the Qwen3-1.7B-shaped model.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (CUDA kernels)
+    python bench.py --impl reference --steps K --warmup W    # the reference's eager path on the host cores
+
+One "step" is one greedy decode step of the whole batch: for each of the 28 layers retention gate ->
+RoPE -> cache append -> split-KV decode attention, then LM head and argmax, then the eviction check
+(`compress`, which fires every `buffer_size` steps).  The prompt pass (32 x 8192 tokens) and its
+hand-off eviction to M = 4096 run before the timed region.  Inputs are synthetic (random-init weights,
+uniform random prompt ids).  With N GPUs every rank runs its own 32 requests (batch partition, no
+collective on the cache path): weak scaling, value = all ranks' tokens / max-over-ranks time.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # BASELINE configs[1]: Qwen3-1.7B architecture, batch 32, 8192-token prompt, M=4096, B=128.
+    "qwen3-1.7b-decode": dict(
+        hidden_size=2048, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
+        intermediate_size=6144, vocab_size=151936, rope_theta=1e6, retention_gate_intermediate_size=128,
+        retention_gate_bias_init=3.0, memory_size=4096, buffer_size=128, batch=32, prompt=8192),
+    # small variant for quick checks of the harness itself (not a bench line)
+    "tiny": dict(
+        hidden_size=256, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128,
+        intermediate_size=512, vocab_size=1024, rope_theta=1e6, retention_gate_intermediate_size=32,
+        retention_gate_bias_init=3.0, memory_size=256, buffer_size=32, batch=4, prompt=512),
+}
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)["hbm_gbs"], "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            if len(r) < 6 or not r[0].isdigit():
+                continue
+            sm.append(int(r[0])); mx = max(mx, int(r[1]))
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx or None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def build_model(cfg_kw, device, dtype=torch.bfloat16):
+    from trimkv_b200 import TrimKVQwen3Config, TrimKVQwen3ForCausalLM
+    kw = {k: v for k, v in cfg_kw.items() if k not in ("batch", "prompt")}
+    cfg = TrimKVQwen3Config(**kw, compress_memory=True, compress_strategy="alpha", attn_implementation="tkv_b200")
+    torch.manual_seed(0)
+    with torch.device(device):
+        model = TrimKVQwen3ForCausalLM(cfg).to(dtype)
+    return model.eval(), cfg
+
+
+def cpu_reference_run(cfg_kw, steps, warmup, sample_batch, seed=0):
+    """Times the eager restatement of the reference's decode step on the host cores (see oracle/qwen3_oracle.py).
+
+    Sample: `sample_batch` requests of the workload's batch, all layers, cache pre-filled with M random
+    rows per head (the 8192-token prompt pass is skipped on the CPU), then `steps` decode steps, each with the
+    reference's torch.cat append, eager attention and the compress check (fires every B steps).
+    """
+    from types import SimpleNamespace
+    from oracle.qwen3_oracle import EagerTrimKVCache, OracleQwen3
+    c = SimpleNamespace(**{k: v for k, v in cfg_kw.items() if k not in ("batch", "prompt")}, rms_norm_eps=1e-6,
+                        compress_memory=True, compress_strategy="alpha")
+    g = torch.Generator().manual_seed(seed)
+    dt = torch.bfloat16
+    L, H, Hq, D, hid, inter = (c.num_hidden_layers, c.num_key_value_heads, c.num_attention_heads, c.head_dim,
+                               c.hidden_size, c.intermediate_size)
+    sd = {"model.embed_tokens.weight": torch.randn(c.vocab_size, hid, generator=g) * 0.02,
+          "model.norm.weight": torch.ones(hid), "lm_head.weight": torch.randn(c.vocab_size, hid, generator=g) * 0.02}
+    for l in range(L):
+        p = f"model.layers.{l}."
+        for name, shape in (("self_attn.q_proj", (Hq * D, hid)), ("self_attn.k_proj", (H * D, hid)),
+                            ("self_attn.v_proj", (H * D, hid)), ("self_attn.o_proj", (hid, Hq * D)),
+                            ("mlp.gate_proj", (inter, hid)), ("mlp.up_proj", (inter, hid)), ("mlp.down_proj", (hid, inter)),
+                            ("self_attn.retention_gate.linear1", (c.retention_gate_intermediate_size, hid)),
+                            ("self_attn.retention_gate.linear2", (H, c.retention_gate_intermediate_size))):
+            sd[p + name + ".weight"] = torch.randn(*shape, generator=g) * 0.02
+        sd[p + "self_attn.retention_gate.linear1.bias"] = torch.zeros(c.retention_gate_intermediate_size)
+        sd[p + "self_attn.retention_gate.bias"] = torch.full((H,), float(c.retention_gate_bias_init))
+        for n in ("input_layernorm", "post_attention_layernorm", "self_attn.q_norm", "self_attn.k_norm"):
+            sd[p + n + ".weight"] = torch.ones(D if "norm.weight" in n + ".weight" and "self_attn" in n else hid)
+    model = OracleQwen3(sd, c, dtype=dt)
+    cache = EagerTrimKVCache(canonical=False)  # torch.topk, exactly the reference's call
+    M, seen = c.memory_size, cfg_kw["prompt"]
+    for l in range(L):
+        cache.key_cache.append(torch.randn(sample_batch, H, M, D, generator=g).to(dt))
+        cache.value_cache.append(torch.randn(sample_batch, H, M, D, generator=g).to(dt))
+        cache.retention_weights.append(torch.nn.functional.logsigmoid(torch.randn(sample_batch, H, M, generator=g) * 1.5 + 3).to(dt))
+        cache.kv_positions.append(torch.sort(torch.rand(sample_batch, H, seen, generator=g).argsort(-1)[..., :M], -1)[0])
+        cache.n_seen_tokens.append(seen)
+    cache._seen_tokens = seen
+    ids = torch.randint(0, c.vocab_size, (sample_batch, 1), generator=g)
+    for _ in range(warmup):
+        ids = model.forward(ids, cache).argmax(-1)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        ids = model.forward(ids, cache).argmax(-1)
+    dt_s = time.perf_counter() - t0
+    return sample_batch * steps / dt_s, dt_s / steps * 1e3
+
+
+def run_reference(args, wl_name, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    sample_batch = args.cpu_batch
+    tok_s, ms = cpu_reference_run(wl, args.steps, args.warmup, sample_batch)
+    sample = (f"{sample_batch} of {wl['batch']} requests, all {wl['num_hidden_layers']} layers, cache pre-filled with "
+              f"M={wl['memory_size']} random rows per head (prompt pass skipped), {args.steps} decode steps in bf16; "
+              "tok/s is that of the sample, not scaled to the full batch")
+    line = {
+        "impl": "reference", "metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl_name, "global_batch": wl["batch"], "prompt_len": wl["prompt"],
+                   "memory_size": wl["memory_size"], "buffer_size": wl["buffer_size"]},
+        "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default="qwen3-1.7b-decode", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-graph", action="store_true", help="dispatch every decode step from Python (no CUDA graph)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-batch", type=int, default=2, help="requests in the host-core baseline sample")
+    ap.add_argument("--cpu-steps", type=int, default=12)
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        if args.steps > 64:
+            args.steps = 64  # bounded sample: the host-core run must end within minutes
+        return run_reference(args, args.workload, wl)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the cache path has no CPU implementation "
+                         "(use --impl reference for the host-core baseline)")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    import torch.distributed as dist
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    from trimkv_b200 import TrimKVCache, attn as tkv_attn, ops
+    from trimkv_b200.decoder import GreedyDecoder
+    ops.lib()
+
+    model, cfg = build_model(wl, dev)
+    B, P, M, Bf = wl["batch"], wl["prompt"], wl["memory_size"], wl["buffer_size"]
+    gen = torch.Generator().manual_seed(1000 + rank)
+    prompt = torch.randint(0, cfg.vocab_size, (B, P), generator=gen).pin_memory()
+    cache = TrimKVCache(device=dev, memory_size=M, buffer_size=Bf)
+    with torch.inference_mode():
+        out = model(input_ids=prompt.to(dev, non_blocking=True), past_key_values=cache, logits_to_keep=1)
+        first = out.logits[:, -1].argmax(-1, keepdim=True)
+        del out
+        torch.cuda.empty_cache()
+        dec = GreedyDecoder(model, cache, use_graph=not args.no_graph)
+        dec.ids.copy_(first)
+        for _ in range(args.warmup):  # eager warm-up steps (allocate workspaces before any capture)
+            dec.step(eager=True)
+        if dec.use_graph:
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                dec.step(eager=True)
+            torch.cuda.current_stream().wait_stream(s)
+            dec.capture()
+            for _ in range(3):
+                dec.step()
+        cache.check_status()
+
+        def barrier():
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        def max_over_ranks(x):
+            if world == 1:
+                return x
+            t = torch.tensor([x], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+
+        # ---- timed region 1: device-resident decode (ids never leave the GPU)
+        sample_every = max(1, args.steps // 8)
+        attn_events, evict_events, lens_at_sample = [], [], []
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = ops.launch_count
+        barrier()
+        with ClockSampler(local) as clocks:
+            e0.record()
+            for i in range(args.steps):
+                sampled = (i % sample_every) == sample_every // 2
+                fires = cache.get_cache_length(0) + 1 >= M + Bf
+                if fires:
+                    # time the eviction kernel (all layers, one launch) on the launching stream
+                    n_before = cache.get_cache_length(0) + 1
+                if sampled:
+                    tkv_attn.event_log = []
+                    lens_at_sample.append(cache.get_cache_length(0) + 1)
+                if fires:
+                    # split the step so the eviction launch can be bracketed by events
+                    comp, cfg.compress_memory = cfg.compress_memory, False
+                    dec.step(eager=sampled)
+                    cfg.compress_memory = comp
+                    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    ev0.record()
+                    cache.compress(memory_size=M, buffer_size=Bf)
+                    ev1.record()
+                    evict_events.append((ev0, ev1, n_before))
+                else:
+                    dec.step(eager=sampled)
+                if sampled:
+                    attn_events.append(tkv_attn.event_log)
+                    tkv_attn.event_log = None
+            e1.record()
+            barrier()
+        ms_total = max_over_ranks(e0.elapsed_time(e1))
+        launches = ops.launch_count - launches0
+        clk = clocks.summary()
+
+        # ---- timed region 2: end to end, ids cross PCIe both ways every step
+        host_ids = torch.zeros(B, 1, dtype=torch.int64).pin_memory()
+        host_ids.copy_(dec.next_ids)
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        f0.record()
+        for i in range(args.steps):
+            nxt = dec.step(host_ids)                      # H2D of this step's input ids (pinned)
+            host_ids.copy_(nxt, non_blocking=True)        # D2H of the step's result
+            torch.cuda.current_stream().synchronize()
+        f1.record()
+        barrier()
+        ms_e2e = max_over_ranks(f0.elapsed_time(f1))
+        cache.check_status()
+
+    tokens = B * args.steps * world
+    value = tokens / (ms_total * 1e-3)
+    e2e = tokens / (ms_e2e * 1e-3)
+
+    # ---- roofline of the dominant kernel (decode attention: reads every cached K/V row once per step)
+    peak, peak_src = measured_peaks()
+    Hq, Hkv, D, L = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.num_hidden_layers
+    ach = []
+    for evs, n in zip(attn_events, lens_at_sample):
+        bytes_per_launch = B * Hkv * n * 4 * D + B * Hq * D * 2 * 2
+        for a, b in evs:
+            ach.append((bytes_per_launch, a.elapsed_time(b) * 1e-3))
+    roofline = None
+    if ach:
+        tot_b, tot_t = sum(x for x, _ in ach), sum(t for _, t in ach)
+        gbs = tot_b / tot_t / 1e9
+        roofline = {"bound": "hbm", "kernel": "decode_attn_split_kernel+combine", "achieved": gbs, "peak": peak,
+                    "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
+                    "launches_timed": len(ach), "avg_launch_us": tot_t / len(ach) * 1e6,
+                    "bytes_per_launch": tot_b / len(ach)}
+    evict = None
+    if evict_events:
+        nseg = L * B * Hkv
+        eb = sum(nseg * (8 * n + (4 * D + 8) * 1 * M + 4 * D * M) for _, _, n in evict_events)  # 8n + 1032 M
+        et = sum(a.elapsed_time(b) for a, b, _ in evict_events) * 1e-3
+        evict = {"kernel": "evict_inplace_kernel", "segments": nseg, "achieved": eb / et / 1e9, "peak": peak,
+                 "unit": "GB/s", "frac": eb / et / 1e9 / peak, "launches_timed": len(evict_events),
+                 "avg_launch_ms": et / len(evict_events) * 1e3}
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        tok_s, ms = cpu_reference_run(wl, args.cpu_steps, 2, args.cpu_batch)
+        cpu = {"value": tok_s, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
+               "sample": f"{args.cpu_batch} of {B} requests, all {L} layers, cache pre-filled with M={M} random rows per head, "
+                         f"{args.cpu_steps} decode steps in bf16 ({ms:.0f} ms/step); not scaled to the full batch"}
+
+    if rank == 0:
+        line = {
+            "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": args.workload, "global_batch": B * world, "batch_per_gpu": B, "prompt_len": P,
+                       "memory_size": M, "buffer_size": Bf, "parallelism": f"batch-partition x{world}",
+                       "cuda_graph": dec.use_graph,
+                       "l2": "per-step working set (weights + 15 GB of K/V) exceeds L2; no explicit flush"},
+            "roofline": roofline, "evict": evict, "cpu_baseline": cpu,
+            "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
+                    "h2d_bytes_per_step": B * 8 * world, "d2h_bytes_per_step": B * 8 * world},
+            "gpu_launches": launches, "clocks": clk,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -21,6 +21,10 @@ from . import ops
 
 _workspaces: Dict[torch.device, torch.Tensor] = {}
 
+# Optional profiling hook: when set to a list, the decode path appends (start_event, end_event, batch, hkv)
+# around each native attention call.  The benchmark uses it to time the kernel on the launching stream.
+event_log = None
+
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
     ws = _workspaces.get(device)
@@ -76,8 +80,14 @@ def tkv_attention_forward(
         max_len = flash_attn_kwargs.get("max_seqlen_k") or int(head_lens.max().item())
         cap = 0
     ws = _workspace(query.device, ops.decode_attn_workspace_bytes(bsz, hq, hkv, dim, max_len))
+    if event_log is not None:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
     ops.decode_attn(q3, key, value, head_lens, seg_start, cap, out, ws, hkv, scaling, max_len,
                     flash_attn_kwargs.get("status"))
+    if event_log is not None:
+        e1.record()
+        event_log.append((e0, e1))
     return out, None, None
 
 

@@ -78,6 +78,9 @@ class TrimKVCache:
         self._status = None
         self.last_kept_idx: Optional[torch.Tensor] = None  # filled when record_kept is set (tests, log)
         self.record_kept = False
+        # When set, K/V views span the whole capacity (shape independent of the live length), which a
+        # captured CUDA graph of the decode step needs; lengths are then read from head_lens only.
+        self.static_views = False
 
         self.key_cache = _LayerViews(self, "k")
         self.value_cache = _LayerViews(self, "v")
@@ -144,6 +147,8 @@ class TrimKVCache:
         if self._slab is None:  # skipped layer that never received data (cache_utils.py:82-88)
             return torch.tensor([])
         n, s = self._cache_len[l], self._slab
+        if self.static_views:
+            n = self._cap
         if kind == "k" or kind == "v":
             return s[kind][l].view(self._batch, self._hkv, self._cap, self._dim)[:, :, :n]
         if kind == "beta" or kind == "pos":
@@ -186,6 +191,8 @@ class TrimKVCache:
                 if (bsz, num_heads, dim) != (self._batch, self._hkv, self._dim):
                     raise ValueError("batch size / KV heads / head_dim changed between updates")
                 if self._cache_len[layer_idx] + seq_len > self._cap:
+                    if torch.cuda.is_current_stream_capturing():
+                        raise RuntimeError("cache capacity exhausted during CUDA graph capture")
                     self._grow(self._cache_len[layer_idx] + seq_len)
                 s = self._slab
                 ops.append(s["k"][layer_idx], s["v"][layer_idx], s["beta"][layer_idx], s["pos"][layer_idx],

@@ -32,6 +32,15 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
     return None if t is None else t.data_ptr()
 
 
+# Kernels launched through this module since import (the benchmark reports the delta of a timed region).
+launch_count = 0
+
+
+def _count(n: int) -> None:
+    global launch_count
+    launch_count += n
+
+
 def new_status(device) -> torch.Tensor:
     return torch.zeros(1, dtype=torch.int32, device=device)
 
@@ -66,6 +75,7 @@ def append(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens,
         pos_new.data_ptr(), ps[0], ps[1], ps[2],
         b, h, s, d, cap, dtype_code(k_cache.dtype), _ptr(status), _stream(k_cache))
     check(rc, "tkv_append")
+    _count(1 if s <= 8 else 2)
 
 
 def evict(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
@@ -76,6 +86,7 @@ def evict(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: i
         seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
         memory_size, trigger_len, max_len, _ptr(kept_idx_out), _ptr(status), _stream(k_cache))
     check(rc, "tkv_evict")
+    _count(1 if cu_seqlens is None else 2)
 
 
 def evict_select(beta, pos, seg_len, n_uniform: int, nseg: int, q_idx: int, memory_size: int,
@@ -88,6 +99,7 @@ def evict_select(beta, pos, seg_len, n_uniform: int, nseg: int, q_idx: int, memo
         beta.data_ptr(), beta.stride(0), pos.data_ptr(), pos_stride, _ptr(seg_len), n_uniform, nseg, q_idx,
         memory_size, trigger_len, max_len, kept_idx.data_ptr(), kept_cnt.data_ptr(), _ptr(status), _stream(beta))
     check(rc, "tkv_evict_select")
+    _count(1)
 
 
 def compact(k_dst, v_dst, beta_dst, pos_dst, cap: int, k_src, v_src, beta_src, pos_src, kept_idx, kept_cnt,
@@ -105,6 +117,7 @@ def compact(k_dst, v_dst, beta_dst, pos_dst, cap: int, k_src, v_src, beta_src, p
         seg_len.data_ptr(), _ptr(cu_seqlens), group, b, h, n, d, dtype_code(k_dst.dtype),
         _ptr(status), _stream(k_dst))
     check(rc, "tkv_compact")
+    _count(1 if cu_seqlens is None else 2)
 
 
 def rebuild_cu_seqlens(seg_len, cu_seqlens, nseg: int, group: int) -> None:
@@ -127,3 +140,4 @@ def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspac
         seg_len.data_ptr(), _ptr(seg_start), cap, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
         b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len, _ptr(status), _stream(q))
     check(rc, "tkv_decode_attn")
+    _count(2)
