@@ -176,8 +176,91 @@ def run_reference(args, wl_name, wl):
     print(json.dumps(line))
 
 
+def run_micro(args):
+    """Kernel microbenchmarks on BASELINE's kernel-level shapes (configs[2] and configs[3]); one JSON line each.
+
+    evict : nseg segments, live lengths uniform in [M, M+B], keep top-M on every segment (forced), bf16, D=128.
+    attn  : one layer of decode attention, batch x 8 KV heads, lengths lognormal(median 2048, sigma 1) in [64, 8192].
+    append: one token per segment.
+    Each timed launch works on data that was not touched by the previous one (buffers rotate; each is > L2).
+    """
+    from trimkv_b200 import ops
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peak, peak_src = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    D, M, Bf, nseg = 128, args.M, 128, args.nseg
+    res = {"micro": args.micro, "steps": args.steps, "warmup": args.warmup, "peak": peak, "peak_source": peak_src}
+    times = []
+    if args.micro in ("evict", "append"):
+        cap = M + Bf
+        nbuf = max(2, min(4, int(2e9 // (nseg * cap * 512)) or 2)) if args.micro == "evict" else 1
+        bufs = []
+        for _ in range(nbuf):
+            k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+            v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+            beta = torch.nn.functional.logsigmoid(torch.randn(nseg * cap, generator=g, device=dev) * 1.5 + 3).bfloat16().float()
+            pos = torch.sort(torch.rand(nseg, 4 * M, generator=g, device=dev).argsort(-1)[:, :cap], -1)[0].to(torch.int32).view(-1)
+            bufs.append((k, v, beta, pos))
+        len0 = torch.randint(M + 1 if args.micro == "evict" else M, cap + (1 if args.micro == "evict" else 0),
+                             (nseg,), generator=g, device=dev, dtype=torch.int32)
+        ln, cu = len0.clone(), torch.zeros(nseg + 1, dtype=torch.int32, device=dev)
+        status = ops.new_status(dev)
+        kn = torch.randn(nseg // 8, 8, 1, D, generator=g, device=dev, dtype=torch.bfloat16)
+        bn = torch.zeros(nseg // 8, 8, 1, device=dev, dtype=torch.bfloat16)
+        pn = torch.tensor([4 * M], device=dev)
+        for i in range(args.warmup + args.steps):
+            k, v, beta, pos = bufs[i % nbuf]
+            ln.copy_(len0)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            if args.micro == "evict":
+                ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, None, status)
+            else:
+                ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
+            e1.record()
+            if i >= args.warmup:
+                times.append((e0, e1))
+        torch.cuda.synchronize()
+        assert ops.read_status(status) == 0
+        n_sum = int(len0.long().sum())
+        alg = (8 * n_sum + nseg * 1032 * M) if args.micro == "evict" else nseg * 2 * 520
+        res["config"] = {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16", "buffers": nbuf}
+    else:
+        batch, hq, hkv = args.nseg // 8, 32, 8
+        lens = torch.exp(torch.randn(nseg, generator=g, device=dev) + 7.6246).clamp(64, 8192).round().to(torch.int32)
+        cap = 8192
+        nbuf = 2
+        bufs = [(torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16),
+                 torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)) for _ in range(nbuf)]
+        q = torch.randn(batch, hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        ws = torch.empty(ops.decode_attn_workspace_bytes(batch, hq, hkv, D, cap), dtype=torch.uint8, device=dev)
+        for i in range(args.warmup + args.steps):
+            k, v = bufs[i % nbuf]
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, D ** -0.5, cap, None)
+            e1.record()
+            if i >= args.warmup:
+                times.append((e0, e1))
+        torch.cuda.synchronize()
+        alg = int(lens.long().sum()) * 4 * D + batch * hq * D * 4
+        res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
+                         "mean_len": float(lens.float().mean()), "buffers": nbuf}
+    ms = sorted(a.elapsed_time(b) for a, b in times)
+    avg = sum(ms) / len(ms)
+    res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
+                "achieved_gbs": alg / (avg * 1e-3) / 1e9, "frac_of_peak": alg / (avg * 1e-3) / 1e9 / peak})
+    print(json.dumps(res))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append"],
+                    help="run one kernel microbenchmark instead of the decode benchmark")
+    ap.add_argument("--M", type=int, default=4096)
+    ap.add_argument("--nseg", type=int, default=2048)
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
@@ -191,6 +274,8 @@ def main():
     wl = WORKLOADS[args.workload]
     if args.warmup < 3:
         args.warmup = 3
+    if args.micro:
+        return run_micro(args)
     if args.impl == "reference":
         if args.steps > 64:
             args.steps = 64  # bounded sample: the host-core run must end within minutes
