@@ -267,6 +267,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--workload", default="qwen3-1.7b-decode", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="dispatch every decode step from Python (no CUDA graph)")
+    ap.add_argument("--no-fused", action="store_true", help="run the layer as separate PyTorch ops around the cache kernels")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-batch", type=int, default=2, help="requests in the host-core baseline sample")
     ap.add_argument("--cpu-steps", type=int, default=12)
@@ -307,7 +308,7 @@ def main():
         first = out.logits[:, -1].argmax(-1, keepdim=True)
         del out
         torch.cuda.empty_cache()
-        dec = GreedyDecoder(model, cache, use_graph=not args.no_graph)
+        dec = GreedyDecoder(model, cache, use_graph=not args.no_graph, fused=not args.no_fused)
         dec.ids.copy_(first)
         for _ in range(args.warmup):  # eager warm-up steps (allocate workspaces before any capture)
             dec.step(eager=True)
@@ -431,7 +432,7 @@ def main():
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "global_batch": B * world, "batch_per_gpu": B, "prompt_len": P,
                        "memory_size": M, "buffer_size": Bf, "parallelism": f"batch-partition x{world}",
-                       "cuda_graph": dec.use_graph,
+                       "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
                        "l2": "per-step working set (weights + 15 GB of K/V) exceeds L2; no explicit flush"},
             "roofline": roofline, "evict": evict, "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,

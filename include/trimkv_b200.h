@@ -153,6 +153,43 @@ int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
                     int batch, int hq, int hkv, int head_dim, int kv_dtype,
                     float scale, int max_len, int32_t* status, tkv_stream_t stream);
 
+/*
+ * Fused producer of one decode step (one new token per request), head_dim 128, bf16/f16.
+ * Replaces, per layer, q_norm / k_norm, the retention-gate tail, RoPE, the transposes and
+ * cache.update of TrimKVQwen3Attention.forward
+ * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:328-353, gate tail :174-178).
+ * qkvg : [batch, row_stride] rows holding  q (hq*128) | k (hkv*128) | v (hkv*128) | gate hidden (gate_inter),
+ *        i.e. the output of one GEMM over the concatenated q/k/v/linear1 weights (linear1 bias included).
+ * cos/sin : [128] of the model dtype for this token's position; pos: int64[1], that position.
+ * Writes q_out [batch, hq, 128] = RoPE(RMSNorm(q)) and appends RoPE(RMSNorm(k)), v,
+ * log beta = logsigmoid(gate_w2 . SiLU(gate hidden) + gate_bias) and pos to every segment
+ * (seg_len += 1, cu_seqlens[i] += i), rounding to the model dtype after every step the eager
+ * PyTorch sequence rounds at.
+ */
+int tkv_decode_prep(const void* qkvg, int64_t row_stride,
+                    const void* q_norm_w, const void* k_norm_w, float eps,
+                    const void* cos, const void* sin,
+                    const void* gate_w2, const void* gate_bias, int gate_inter,
+                    const int64_t* pos, void* q_out,
+                    void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                    int32_t* seg_len, int32_t* cu_seqlens, int64_t cap,
+                    int batch, int hq, int hkv, int head_dim, int dtype,
+                    int32_t* status, tkv_stream_t stream);
+
+/*
+ * residual[r, :] += delta[r, :] (skipped if delta is NULL); out[r, :] = weight * RMSNorm(residual[r, :]).
+ * Replaces the residual add + Qwen3RMSNorm pairs of the decoder layer
+ * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:414-437).  cols % 8 == 0; out may not alias residual.
+ */
+int tkv_add_rmsnorm(void* residual, const void* delta, const void* weight, void* out,
+                    int rows, int cols, float eps, int dtype, tkv_stream_t stream);
+
+/*
+ * out[r, j] = SiLU(gate_up[r, j]) * gate_up[r, inter + j]: the activation of Qwen3MLP over the output of one
+ * GEMM with the concatenated gate/up weights (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:436).
+ */
+int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, tkv_stream_t stream);
+
 /* Blocks until `stream` is idle, then returns *status (a TKV_DEV_* code) and clears it. */
 int tkv_read_status(int32_t* status, tkv_stream_t stream);
 

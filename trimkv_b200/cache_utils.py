@@ -203,6 +203,27 @@ class TrimKVCache:
         return (self.key_cache[layer_idx], self.value_cache[layer_idx], self.retention_weights[layer_idx],
                 self.kv_positions[layer_idx], self._attn_kwargs(layer_idx))
 
+    def decode_prep(self, layer_idx: int, qkvg, q_norm_w, k_norm_w, eps, cos, sin, gate_w2, gate_bias, pos, q_out,
+                    num_q_heads: int):
+        """Fused form of ``update`` for one new token per request: the kernel normalises and rotates q and k,
+        finishes the retention gate and appends K, V, log beta and the position in one launch.  Same counter
+        updates as ``update``; returns ``(K view, V view, flash_attn_kwargs)``."""
+        if self._slab is None or self._pending[layer_idx] is not None:
+            self._materialise(extra=1)
+        if self._cache_len[layer_idx] + 1 > self._cap:
+            if torch.cuda.is_current_stream_capturing():
+                raise RuntimeError("cache capacity exhausted during CUDA graph capture")
+            self._grow(self._cache_len[layer_idx] + 1)
+        if layer_idx == 0:
+            self._seen_tokens += 1
+        s = self._slab
+        ops.decode_prep(qkvg, q_norm_w, k_norm_w, eps, cos, sin, gate_w2, gate_bias, pos, q_out,
+                        s["k"][layer_idx], s["v"][layer_idx], s["beta"][layer_idx], s["pos"][layer_idx],
+                        s["len"][layer_idx], s["cu"][layer_idx], self._cap, num_q_heads, self._hkv, self._status)
+        self._cache_len[layer_idx] += 1
+        self.n_seen_tokens[layer_idx] += 1
+        return self.key_cache[layer_idx], self.value_cache[layer_idx], self._attn_kwargs(layer_idx)
+
     def _attn_kwargs(self, l: int) -> Dict[str, Any]:
         if self._slab is None or self._pending[l] is not None:
             return {}

@@ -15,6 +15,72 @@ from . import ops
 from .cache_utils import TrimKVCache
 
 
+class FusedDecodeStep:
+    """One-token forward of the whole decoder with the fused CUDA kernels around the GEMMs.
+
+    Per layer: add+RMSNorm -> one GEMM for q|k|v|gate.linear1 -> decode_prep (q/k-norm, RoPE, gate tail,
+    append) -> split-KV decode attention -> o_proj -> add+RMSNorm -> one GEMM for gate|up -> SiLU*up ->
+    down_proj: 10 launches instead of ~60.  The GEMMs stay cuBLAS (through torch); the concatenated
+    weights replace the originals' storage (the module parameters become views of them).
+    """
+
+    def __init__(self, model, cache: TrimKVCache):
+        cfg = model.config
+        if cfg.head_dim != 128 or cfg.retention_gate != "rg":
+            raise NotImplementedError("fused decode step needs head_dim 128 and retention_gate 'rg'")
+        self.model, self.cache, self.cfg = model, cache, cfg
+        self.layers = []
+        with torch.no_grad():
+            for layer in model.model.layers[: cfg.num_hidden_layers]:
+                at, mlp = layer.self_attn, layer.mlp
+                parts = [at.q_proj, at.k_proj, at.v_proj, at.retention_gate.linear1]
+                w = torch.cat([m.weight for m in parts], 0).contiguous()
+                bias = None
+                if any(m.bias is not None for m in parts):
+                    bias = torch.cat([m.bias if m.bias is not None else m.weight.new_zeros(m.weight.shape[0])
+                                      for m in parts]).contiguous()
+                off = 0
+                for m in parts:  # re-point the module parameters at the fused storage
+                    n = m.weight.shape[0]
+                    m.weight.data = w[off:off + n]
+                    if m.bias is not None:
+                        m.bias.data = bias[off:off + n]
+                    off += n
+                gu = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], 0).contiguous()
+                inter = mlp.gate_proj.weight.shape[0]
+                mlp.gate_proj.weight.data, mlp.up_proj.weight.data = gu[:inter], gu[inter:]
+                self.layers.append((layer, w, bias, gu))
+        self.hq, self.hkv, self.eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps
+
+    def __call__(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """ids [B,1] int64, pos [1] int64 (device) -> logits [B, vocab]."""
+        import torch.nn.functional as F
+        from .attn import tkv_attention_forward
+        m, cache = self.model.model, self.cache
+        bsz = ids.shape[0]
+        x = F.embedding(ids.view(bsz), m.embed_tokens.weight)          # residual stream, updated in place
+        cos, sin = m.rotary_emb(x, pos.view(1, 1))
+        cos, sin = cos.reshape(-1), sin.reshape(-1)
+        h = torch.empty_like(x)
+        q_out = torch.empty(bsz, self.hq, 1, 128, dtype=x.dtype, device=x.device)
+        delta = None
+        for l, (layer, w_qkvg, b_qkvg, w_gu) in enumerate(self.layers):
+            at = layer.self_attn
+            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps)
+            qkvg = F.linear(h, w_qkvg, b_qkvg)
+            k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin,
+                                         at.retention_gate.linear2.weight, at.retention_gate.bias, pos, q_out, self.hq)
+            o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
+            a = F.linear(o.view(bsz, -1), at.o_proj.weight, at.o_proj.bias)
+            ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps)
+            gu = F.linear(h, w_gu)
+            act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
+            ops.silu_mul(gu, act)
+            delta = F.linear(act, layer.mlp.down_proj.weight)
+        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps)
+        return F.linear(h, self.model.lm_head.weight)
+
+
 class GreedyDecoder:
     """Steps a prefilled (model, cache) pair one token at a time.
 
@@ -22,8 +88,12 @@ class GreedyDecoder:
     previous step's argmax without leaving the device.  Returns the device tensor holding the new ids.
     """
 
-    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True):
+    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True):
         self.model, self.cache, self.cfg = model, cache, model.config
+        self.fused = None
+        if fused and model.config.head_dim == 128 and model.config.retention_gate == "rg" \
+                and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
+            self.fused = FusedDecodeStep(model, cache)
         dev = model.device
         self.batch = cache._batch
         self.ids = torch.zeros(self.batch, 1, dtype=torch.int64, device=dev)
@@ -34,13 +104,17 @@ class GreedyDecoder:
 
     def _forward(self):
         cfg = self.cfg
-        compress, cfg.compress_memory = cfg.compress_memory, False  # eviction is driven from step()
-        try:
-            out = self.model(input_ids=self.ids, past_key_values=self.cache, cache_position=self.pos,
-                             logits_to_keep=1)
-        finally:
-            cfg.compress_memory = compress
-        self.next_ids.copy_(out.logits[:, -1].argmax(-1, keepdim=True))
+        if self.fused is not None:
+            self.logits = self.fused(self.ids, self.pos)
+        else:
+            compress, cfg.compress_memory = cfg.compress_memory, False  # eviction is driven from step()
+            try:
+                out = self.model(input_ids=self.ids, past_key_values=self.cache, cache_position=self.pos,
+                                 logits_to_keep=1)
+            finally:
+                cfg.compress_memory = compress
+            self.logits = out.logits[:, -1]
+        self.next_ids.copy_(self.logits.argmax(-1, keepdim=True))
         self.ids.copy_(self.next_ids)
         self.pos.add_(1)
 

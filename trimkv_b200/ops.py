@@ -141,3 +141,34 @@ def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspac
         b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len, _ptr(status), _stream(q))
     check(rc, "tkv_decode_attn")
     _count(2)
+
+
+def decode_prep(qkvg, q_norm_w, k_norm_w, eps: float, cos, sin, gate_w2, gate_bias, pos, q_out,
+                k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, cap: int, hq: int, hkv: int,
+                status=None) -> None:
+    """Fused q/k-norm + RoPE + retention-gate tail + append for one new token per request (head_dim 128)."""
+    b = qkvg.shape[0]
+    rc = lib().tkv_decode_prep(
+        qkvg.data_ptr(), qkvg.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), float(eps),
+        cos.data_ptr(), sin.data_ptr(), gate_w2.data_ptr(), gate_bias.data_ptr(), gate_w2.shape[1],
+        pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(),
+        pos_cache.data_ptr(), seg_len.data_ptr(), _ptr(cu_seqlens), cap, b, hq, hkv, 128,
+        dtype_code(qkvg.dtype), _ptr(status), _stream(qkvg))
+    check(rc, "tkv_decode_prep")
+    _count(1)
+
+
+def add_rmsnorm(residual, delta, weight, out, eps: float) -> None:
+    rows, cols = residual.shape
+    rc = lib().tkv_add_rmsnorm(residual.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), rows, cols,
+                               float(eps), dtype_code(residual.dtype), _stream(residual))
+    check(rc, "tkv_add_rmsnorm")
+    _count(1)
+
+
+def silu_mul(gate_up, out) -> None:
+    rows, two_inter = gate_up.shape
+    rc = lib().tkv_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two_inter // 2, dtype_code(gate_up.dtype),
+                            _stream(gate_up))
+    check(rc, "tkv_silu_mul")
+    _count(1)
