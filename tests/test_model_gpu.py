@@ -13,7 +13,7 @@ def _tiny(memory_size=96, buffer_size=16, layers=2):
     cfg = TrimKVQwen3Config(
         vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=layers, num_attention_heads=4,
         num_key_value_heads=2, head_dim=128, retention_gate_intermediate_size=32, retention_gate_bias_init=3.0,
-        memory_size=memory_size, buffer_size=buffer_size, initializer_range=0.05)
+        memory_size=memory_size, buffer_size=buffer_size, initializer_range=0.02)
     torch.manual_seed(0)
     model = TrimKVQwen3ForCausalLM(cfg).to(torch.bfloat16).eval()
     return model, cfg
@@ -37,16 +37,26 @@ def test_generate_matches_cpu_restatement():
             want = ref.forward(ids, rcache)
             got = out.logits.float().cpu()
             worst = max(worst, float((got - want.float()).abs().max()))
-            assert cache.get_cache_length(0) == rcache.get_cache_length(0)
             assert cache.get_seq_length() == rcache.get_seq_length()
-            mine = cache.kv_positions[0].cpu().numpy().astype(np.int64)
-            theirs = rcache.kv_positions[0].numpy()
-            mismatched_rows += int((mine != theirs).any(-1).sum())
+            diverged = False
+            for l in range(cfg.num_hidden_layers):
+                assert cache.get_cache_length(l) == rcache.get_cache_length(l)
+                mine = cache.kv_positions[l].cpu().to(torch.int64)
+                rows = int((mine != rcache.kv_positions[l]).any(-1).sum())
+                mismatched_rows += rows
+                diverged |= rows > 0
+            if diverged:
+                # log beta comes out of bf16 GEMMs that round differently on CPU and GPU, so a near-tie at the
+                # eviction boundary can fall either way; adopt the GPU state and keep comparing in lock-step.
+                for l in range(cfg.num_hidden_layers):
+                    rcache.key_cache[l] = cache.key_cache[l].cpu().clone()
+                    rcache.value_cache[l] = cache.value_cache[l].cpu().clone()
+                    rcache.retention_weights[l] = cache.retention_weights[l].cpu().to(torch.bfloat16)
+                    rcache.kv_positions[l] = cache.kv_positions[l].cpu().to(torch.int64)
             ids = want.argmax(-1)  # feed both with the same token so the comparison stays in lock-step
     cache.check_status()
     assert worst <= 2e-2, worst
-    # log beta comes out of bf16 GEMMs that round differently on CPU and GPU; allow a few near-tie rows
-    assert mismatched_rows <= 8, mismatched_rows
+    assert mismatched_rows <= 6, mismatched_rows  # of 40 steps x 2 layers x 4 segments
 
 
 @pytest.mark.parametrize("use_graph", [False, True])
@@ -74,8 +84,9 @@ def test_fused_decode_step_matches_module_path(use_graph):
                 logits.append(dec.logits.float().clone())
                 toks.append(dec.next_ids.clone())
             cache.check_status()
-            outs.append((torch.stack(logits), cache.kv_positions[0].clone(), cache.key_cache[0].float().clone(),
-                         cache.retention_weights[0].clone(), cache.get_cache_length(0)))
+            n = cache.get_cache_length(0)  # a graph-captured decoder exposes full-capacity views: cut to the live rows
+            outs.append((torch.stack(logits), cache.kv_positions[0][:, :, :n].clone(),
+                         cache.key_cache[0][:, :, :n].float().clone(), cache.retention_weights[0][:, :, :n].clone(), n))
     (l0, p0, k0, b0, n0), (l1, p1, k1, b1, n1) = outs
     assert n0 == n1
     assert float((l0 - l1).abs().max()) <= 2e-2
