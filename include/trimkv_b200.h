@@ -154,6 +154,29 @@ int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
                     float scale, int max_len, int32_t* status, tkv_stream_t stream);
 
 /*
+ * tkv_decode_attn for callers that cannot allocate device memory.  (No counterpart in the reference: its
+ * attention always runs inside PyTorch, whose allocator provides flash-attn's temporaries.)
+ * Meant for hosts that cannot hand the library a workspace: a server whose block arena already owns the whole
+ * device, a plug-in slot without access to the host's allocator, or a loop that cannot afford the device-wide
+ * synchronisation of cudaMalloc/cudaFree.  Same arguments and results as tkv_decode_attn without
+ * `workspace`; the per-chunk partial results live in an array of TKV_STATIC_SCRATCH_BYTES that is part of
+ * the library image, so every GPU that loads the library holds that much memory until the process exits.
+ *  - Limit: problems whose tkv_decode_attn_workspace_bytes(...) exceeds TKV_STATIC_SCRATCH_BYTES are
+ *    refused with TKV_ERR_UNSUPPORTED (nothing is launched); use tkv_decode_attn for those.
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
+ *    device current); make that first call outside any stream capture.  No call allocates or frees memory.
+ *  - All calls on a device share the one array, and it keeps whatever the previous call left there (no call
+ *    relies on its initial content).  Two calls that can overlap on the GPU (different streams, or a second
+ *    process thread) race on it: serialise them on one stream or order them with events.
+ */
+#define TKV_STATIC_SCRATCH_BYTES (32u << 20)
+int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
+                           const void* k_cache, const void* v_cache,
+                           const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                           void* out, int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                           float scale, int max_len, int32_t* status, tkv_stream_t stream);
+
+/*
  * Fused producer of one decode step (one new token per request), head_dim 128, bf16/f16.
  * Replaces, per layer, q_norm / k_norm, the retention-gate tail, RoPE, the transposes and
  * cache.update of TrimKVQwen3Attention.forward

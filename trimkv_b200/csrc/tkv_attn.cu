@@ -307,3 +307,75 @@ extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
   p.status = status;
   return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Decode attention for callers that cannot allocate device memory.
+//
+// tkv_decode_attn needs a caller-provided workspace for the per-chunk partial results.  Some hosts have no way
+// to provide one: an inference server that handed the whole device to its own block arena at start-up and has
+// nothing left to carve a workspace from, a plug-in slot whose host does not expose its allocator, or a
+// latency-critical loop where the implicit device-wide synchronisation of cudaMalloc/cudaFree is not acceptable.
+// For them the partials live in the fixed array below, which is part of the library image: every GPU that
+// loads the library holds these TKV_STATIC_SCRATCH_BYTES until the process exits.
+//
+// The array's name is only a host-side handle in host code; the kernels need its device address, which is
+// looked up once per device with cudaGetSymbolAddress while that device is current.
+static __device__ __align__(256) unsigned char g_attn_scratch[TKV_STATIC_SCRATCH_BYTES];
+
+namespace tkv {
+constexpr int kMaxDevices = 64;
+static void* g_scratch_addr[kMaxDevices];   // device address of g_attn_scratch on each device (0 = not looked up)
+}  // namespace tkv
+
+extern "C" int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
+                                      const void* k_cache, const void* v_cache,
+                                      const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                                      void* out, int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                                      float scale, int max_len, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!q || !k_cache || !v_cache || !seg_len || !out)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_static: NULL pointer argument");
+  if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || head_dim <= 0 || max_len <= 0)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_static: bad sizes batch=%d hq=%d hkv=%d head_dim=%d max_len=%d", batch,
+                hq, hkv, head_dim, max_len);
+  if (seg_start == nullptr && cap <= 0)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_static: cap=%lld without seg_start", (long long)cap);
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_static: pointers must be 16-byte aligned");
+  if ((q_sb * 2) % 16 || (q_sh * 2) % 16)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_static: q strides must be multiples of 16 bytes");
+  if (batch == 0) return TKV_OK;
+  const size_t need = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  if (need > (size_t)TKV_STATIC_SCRATCH_BYTES)
+    return fail(TKV_ERR_UNSUPPORTED,
+                "tkv_decode_attn_static: this problem needs %zu bytes of scratch but the built-in array holds %zu; "
+                "use tkv_decode_attn with a caller-provided workspace", need, (size_t)TKV_STATIC_SCRATCH_BYTES);
+  // Set-up on the first call per device: resolve the device address of the array (no allocation happens).
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn_static: device %d", dev);
+  void* scratch = __atomic_load_n(&g_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (scratch == nullptr) {
+    e = cudaGetSymbolAddress(&scratch, g_attn_scratch);
+    if (e != cudaSuccess || scratch == nullptr)
+      return fail(TKV_ERR_LAUNCH, "tkv_decode_attn_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    __atomic_store_n(&g_scratch_addr[dev], scratch, __ATOMIC_RELEASE);  // same value from every thread
+  }
+  const int nseg = batch * hkv, G = hq / hkv;
+  AttnParams p;
+  p.q = (const char*)q; p.q_sb = q_sb; p.q_sh = q_sh;
+  p.k = (const char*)k_cache; p.v = (const char*)v_cache;
+  p.seg_len = seg_len; p.seg_start = seg_start; p.cap = cap;
+  p.out = (char*)out;
+  p.chunk = attn_chunk_tokens(nseg, max_len);
+  p.nchunks = (max_len + p.chunk - 1) / p.chunk;
+  // Nothing in the scratch has to start at zero: the merge step reads only the partials of the chunks that the
+  // first step of this same call has written.
+  p.part_ml = reinterpret_cast<float*>(scratch);
+  p.part_o = p.part_ml + (((int64_t)nseg * p.nchunks * G * 2 + 63) / 64) * 64;
+  p.hq = hq; p.hkv = hkv; p.max_len = max_len;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+}
