@@ -51,7 +51,8 @@ enum {
   TKV_DEV_OK = 0,
   TKV_DEV_CAPACITY = 1,   /* len + s_new > cap: segment skipped */
   TKV_DEV_LEN_BOUND = 2,  /* len > max_len given by the host: segment skipped */
-  TKV_DEV_BAD_INDEX = 3   /* a kept index outside [0, n): row skipped */
+  TKV_DEV_BAD_INDEX = 3,  /* a kept index outside [0, n): row skipped */
+  TKV_DEV_TIMEOUT = 4     /* a bounded wait inside a kernel ran out: that work item produced no output */
 };
 
 int tkv_version(void);

@@ -6,6 +6,7 @@
 // Here the segment table is read on the device; a work item is (segment, chunk of kChunk tokens); each
 // item produces an unnormalised partial output and its (max, sum) in log2 domain, and a combine kernel
 // merges the chunks of a segment.  Per cached token the kernel reads 2*D*elem bytes exactly once.
+#include <cstdlib>
 #include "tkv_common.cuh"
 #include "tkv_attn.cuh"
 
@@ -246,6 +247,25 @@ static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st) {
   return check_launch("tkv_decode_attn(combine)");
 }
 
+int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st) {
+  if (head_dim == 128 && kv_dtype == TKV_BF16) decode_attn_combine_kernel<TKV_BF16, 128><<<dim3(nseg, G), 128, 0, st>>>(p);
+  else if (head_dim == 128 && kv_dtype == TKV_F16) decode_attn_combine_kernel<TKV_F16, 128><<<dim3(nseg, G), 128, 0, st>>>(p);
+  else return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(combine): head_dim=%d dtype=%d", head_dim, kv_dtype);
+  return check_launch("tkv_decode_attn(combine)");
+}
+
+// Which split kernel serves a problem: the tensor-core one whenever its layout requirements hold, unless the
+// environment variable TKV_ATTN_IMPL=simt asks for the CUDA-core kernel (A/B measurements).
+static bool use_tensor_core_path(int head_dim, int kv_dtype, int G, const void* seg_start, int64_t rows) {
+  static int forced = -1;
+  if (forced < 0) {
+    const char* e = getenv("TKV_ATTN_IMPL");
+    forced = (e != nullptr && e[0] == 's') ? 1 : 0;
+  }
+  return forced == 0 && head_dim == 128 && (kv_dtype == TKV_BF16 || kv_dtype == TKV_F16) && G <= 8 && seg_start == nullptr &&
+         rows >= 128;  // the TMA box is 128 rows
+}
+
 int attn_chunk_tokens(int nseg, int max_len) {
   // Enough work items to fill 148 SMs several times over, but chunks long enough to amortise the merge.
   int chunk = 512;
@@ -267,7 +287,9 @@ int launch_decode_attn_simt(const AttnParams& p, int nseg, int G, int head_dim, 
 extern "C" size_t tkv_decode_attn_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len) {
   if (batch <= 0 || hq <= 0 || hkv <= 0 || head_dim <= 0 || max_len <= 0 || hq % hkv != 0) return 0;
   const int nseg = batch * hkv, G = hq / hkv;
-  const int chunk = tkv::attn_chunk_tokens(nseg, max_len);
+  // Large enough for either split kernel (they cut segments into chunks of different lengths).
+  int chunk = tkv::attn_chunk_tokens(nseg, max_len);
+  if (head_dim == 128 && tkv::attn_tc_chunk_tokens() < chunk) chunk = tkv::attn_tc_chunk_tokens();
   const int64_t items = (int64_t)nseg * ((max_len + chunk - 1) / chunk);
   return (size_t)(items * G * (head_dim + 2) * sizeof(float) + 256);
 }
@@ -298,14 +320,18 @@ extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
   p.k = (const char*)k_cache; p.v = (const char*)v_cache;
   p.seg_len = seg_len; p.seg_start = seg_start; p.cap = cap;
   p.out = (char*)out;
-  p.chunk = attn_chunk_tokens(nseg, max_len);
+  const bool tc = use_tensor_core_path(head_dim, kv_dtype, G, seg_start, (int64_t)nseg * cap);
+  p.chunk = tc ? attn_tc_chunk_tokens() : attn_chunk_tokens(nseg, max_len);
   p.nchunks = (max_len + p.chunk - 1) / p.chunk;
   p.part_ml = reinterpret_cast<float*>(workspace);
   p.part_o = p.part_ml + (((int64_t)nseg * p.nchunks * G * 2 + 63) / 64) * 64;
   p.hq = hq; p.hkv = hkv; p.max_len = max_len;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
-  return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+  if (!tc) return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+  int rc = launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
+  if (rc != TKV_OK) return rc;
+  return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------

@@ -1,6 +1,7 @@
 // Parameters shared by the decode-attention kernels.
 #pragma once
 #include <stdint.h>
+#include <cuda_runtime.h>
 
 namespace tkv {
 
@@ -19,5 +20,12 @@ struct AttnParams {
 
 // Tokens per work item, a pure function of the problem size (the workspace size depends on it).
 int attn_chunk_tokens(int nseg, int max_len);
+
+
+// Tensor-core (tcgen05 + TMA) split kernel: fixed chunk, needs the capacity-strided layout and head_dim 128.
+int attn_tc_chunk_tokens();
+int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, int64_t rows, cudaStream_t st);
+// Merge kernel shared by both split kernels.
+int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st);
 
 }  // namespace tkv

@@ -1,0 +1,406 @@
+// Split-KV decode attention on the 5th-generation tensor cores (tcgen05 + TMEM), K/V tiles staged by TMA.
+//
+// Same contract as the CUDA-core kernel in tkv_attn.cu (it replaces flash_attn_varlen_func as called by
+// src/trimkv/attn/flash_attn.py:135-145 for one query token per request).  One CTA = (segment, chunk of
+// 256 cached tokens) = two tiles of 128 tokens:
+//   S[128 tokens x 16] = K_tile[128 x 128] . Q^T     tcgen05.mma, A = K tile (smem, K-major, 128B swizzle, as
+//                                                    written by TMA), B = Q of the G <= 16 query heads of this
+//                                                    KV head (smem, K-major, no swizzle), D in TMEM
+//   softmax over the chunk                           one thread per token row (tcgen05.ld 32x32b), fp32, log2 domain
+//   O^T[128 dims x 16] += V_tile^T[128 x 128] . P    A = V tile (smem, MN-major, 128B swizzle: the same bytes TMA
+//                                                    wrote), B = P (smem, K-major, no swizzle, bf16/f16)
+// and the unnormalised O with (max, sum) goes to the workspace that decode_attn_combine_kernel merges.
+// Three 32 KB stage buffers hold K0, K1, V0; V1 reuses K0's buffer once the S MMAs have completed, so two CTAs fit
+// on an SM and keep ~190 KB of loads in flight.  Every mbarrier wait is bounded: on expiry the CTA records
+// TKV_DEV_TIMEOUT, skips the remaining work, frees its TMEM and returns.
+#include <cuda.h>
+#include "tkv_common.cuh"
+#include "tkv_attn.cuh"
+
+namespace tkv {
+
+constexpr int kTcThreads = 128;
+constexpr int kTileTokens = 128;
+constexpr int kTcChunk = 256;
+constexpr int kStageBytes = 32768;            // 128 rows x 256 B (two 64-element halves of 16 KB)
+constexpr int kHalfBytes = 16384;
+constexpr int kQBytes = 4096;                 // 16 heads x 128 dims
+constexpr int kPBytes = 4096;                 // 16 heads x 128 tokens
+constexpr int kTmemCols = 64;                 // S tile 0: [0,16)  S tile 1: [16,32)  O: [32,48)
+constexpr uint32_t kSpinLimit = 1u << 24;
+
+struct TcSmem {                               // after the 1024-byte aligned stage buffers
+  uint64_t bar_k[2], bar_v[2], bar_s, bar_o;
+  uint32_t tmem_base;
+  int abort_flag;
+  float red_max[4][16];
+  float red_sum[4][16];
+};
+constexpr int kTcSmemBytes = 3 * kStageBytes + kQBytes + 2 * kPBytes + (int)sizeof(TcSmem) + 1024;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait on phase `parity`; false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+  }
+  return false;
+}
+// Same, but also gives up as soon as another thread of the CTA has raised the abort flag.
+__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+    if (done) return true;
+    if ((it & 63u) == 63u && *abort_flag != 0) return false;
+  }
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (tcgen05): address, leading/stride byte offsets in 16-byte units, version 1,
+// layout type in bits [61,64) (0 = no swizzle, 2 = 128-byte swizzle).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
+         (1ull << 46) | ((uint64_t)layout << 61);
+}
+// Instruction descriptor, kind::f16: D = f32, A/B = bf16 or f16, M = 128, N = 16.
+__device__ __forceinline__ uint32_t make_idesc(int fmt /*0 f16, 1 bf16*/, int a_mn_major) {
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn_major << 15) | (0u << 16) |
+         ((16u >> 3) << 17) | ((128u >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accum) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accum), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+template <int kDtype, int kG>
+__global__ void __launch_bounds__(kTcThreads)
+decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const int seg = blockIdx.x / p.nchunks, chunk = blockIdx.x - seg * p.nchunks;
+  const int len = min(p.seg_len[seg], p.max_len);
+  const int t0 = chunk * kTcChunk;
+  if (t0 >= len) return;
+  const int n_valid = min(kTcChunk, len - t0);
+  const int ntiles = (n_valid + kTileTokens - 1) / kTileTokens;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* stage = base;                                   // 3 x 32 KB, each 1024-byte aligned
+  uint8_t* q_s = base + 3 * kStageBytes;
+  uint8_t* p_s = q_s + kQBytes;                            // 2 x 4 KB
+  TcSmem* sm = reinterpret_cast<TcSmem*>(p_s + 2 * kPBytes);
+
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  if (tid == 0) {
+    mbar_init(&sm->bar_k[0], 1); mbar_init(&sm->bar_k[1], 1);
+    mbar_init(&sm->bar_v[0], 1); mbar_init(&sm->bar_v[1], 1);
+    mbar_init(&sm->bar_s, 1); mbar_init(&sm->bar_o, 1);
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  // Q of this KV head's query heads as the B operand: rows = heads (16, zero beyond kG), K-major without
+  // swizzle: 8x8 core matrices of 128 B, K-adjacent cores 128 B apart, the second group of 8 heads 2048 B further.
+  for (int i = tid; i < 256; i += kTcThreads) {
+    const int hh = i >> 4, c = i & 15;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (hh < kG) v = ld16(p.q + ((int64_t)b * p.q_sb + (int64_t)(h * kG + hh) * p.q_sh) * 2 + c * 16);
+    st16(q_s + (hh >> 3) * 2048 + c * 128 + (hh & 7) * 16, v);
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const int64_t row0 = (p.seg_start != nullptr ? (int64_t)p.seg_start[seg] : (int64_t)seg * p.cap) + t0;
+  const uint32_t idesc_qk = make_idesc(kDtype == TKV_BF16 ? 1 : 0, 0);
+  const uint32_t idesc_pv = make_idesc(kDtype == TKV_BF16 ? 1 : 0, 1);
+  volatile int* abort_flag = &sm->abort_flag;
+  bool v1_issued = false;
+
+  // ---- thread 0: start every load this CTA can hold, then S = K . Q^T for both tiles
+  if (tid == 0) {
+    for (int i = 0; i < ntiles; ++i) {
+      mbar_expect_tx(&sm->bar_k[i], kStageBytes);
+      tma_load_2d(stage + i * kStageBytes, &map_k, &sm->bar_k[i], 0, (int)(row0 + i * kTileTokens));
+      tma_load_2d(stage + i * kStageBytes + kHalfBytes, &map_k, &sm->bar_k[i], 64, (int)(row0 + i * kTileTokens));
+    }
+    mbar_expect_tx(&sm->bar_v[0], kStageBytes);
+    tma_load_2d(stage + 2 * kStageBytes, &map_v, &sm->bar_v[0], 0, (int)row0);
+    tma_load_2d(stage + 2 * kStageBytes + kHalfBytes, &map_v, &sm->bar_v[0], 64, (int)row0);
+    bool ok = true;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      ok = mbar_wait(&sm->bar_k[i], 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a0 = smem_u32(stage + i * kStageBytes);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {  // 16 dims per MMA; 4 steps inside a 128-byte swizzle atom, then the next half
+        const uint64_t ad = make_desc(a0 + (k >> 2) * kHalfBytes + (k & 3) * 32, 16, 1024, 2);
+        const uint64_t bd = make_desc(smem_u32(q_s) + k * 256, 128, 2048, 0);
+        umma(tmem + 16 * i, ad, bd, idesc_qk, k > 0);
+      }
+    }
+    if (ok) umma_commit(&sm->bar_s);
+    else { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+  }
+  __syncwarp();
+  // ---- everyone: wait for S (bounded; leaves early if thread 0 gave up)
+  if (!mbar_wait_or_abort(&sm->bar_s, 0, abort_flag)) {
+    if (*abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+  }
+  tc_fence_after();
+  if (tid == 0 && ntiles == 2 && *abort_flag == 0) {
+    // K tile 0 has been consumed by the tensor core: its buffer takes V tile 1.
+    mbar_expect_tx(&sm->bar_v[1], kStageBytes);
+    tma_load_2d(stage, &map_v, &sm->bar_v[1], 0, (int)(row0 + kTileTokens));
+    tma_load_2d(stage + kHalfBytes, &map_v, &sm->bar_v[1], 64, (int)(row0 + kTileTokens));
+    v1_issued = true;
+  }
+  __syncthreads();
+  const bool aborted = *abort_flag != 0;
+
+  float s[2][kG], mloc[kG];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) mloc[g] = -INFINITY;
+  if (!aborted) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float v[16];
+      if (i < ntiles) tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + 16 * i, v);
+      const bool valid = i < ntiles && (i * kTileTokens + tid) < n_valid;
+#pragma unroll
+      for (int g = 0; g < kG; ++g) {
+        s[i][g] = valid ? v[g] * p.scale_log2 : -INFINITY;
+        mloc[g] = fmaxf(mloc[g], s[i][g]);
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) mloc[g] = fmaxf(mloc[g], __shfl_xor_sync(0xffffffffu, mloc[g], o));
+    if (lane == 0) sm->red_max[warp][g] = mloc[g];
+  }
+  __syncthreads();
+  float mx[kG], lsum[kG];
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+    mx[g] = fmaxf(fmaxf(sm->red_max[0][g], sm->red_max[1][g]), fmaxf(sm->red_max[2][g], sm->red_max[3][g]));
+    lsum[g] = 0.f;
+  }
+  // P as the B operand of the second product: rows = heads, K = tokens, K-major without swizzle (same core-matrix
+  // arrangement as Q).  The sum uses the rounded values so numerator and denominator see the same weights.
+  if (!aborted) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      if (i < ntiles) {
+        uint8_t* pt = p_s + i * kPBytes + (tid >> 3) * 128 + (tid & 7) * 2;
+#pragma unroll
+        for (int g = 0; g < kG; ++g) {
+          const float pw = (s[i][g] == -INFINITY) ? 0.f : exp2f(s[i][g] - mx[g]);
+          unsigned short bits;
+          float back;
+          if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
+          else { __half x = __float2half_rn(pw); bits = __half_as_ushort(x); back = __half2float(x); }
+          lsum[g] += back;
+          *reinterpret_cast<unsigned short*>(pt + (g >> 3) * 2048 + (g & 7) * 16) = bits;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int g = 0; g < kG; ++g) {
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) lsum[g] += __shfl_xor_sync(0xffffffffu, lsum[g], o);
+    if (lane == 0) sm->red_sum[warp][g] = lsum[g];
+  }
+  // Rows of a V tile beyond the segment's length may hold anything (stale rows, another segment): their weight
+  // is zero, but 0 x NaN would poison the product, so they are cleared in shared memory.
+  if (!aborted && (n_valid & (kTileTokens - 1)) != 0) {
+    const int i = ntiles - 1;
+    if (!mbar_wait_or_abort(&sm->bar_v[i], 0, abort_flag)) {
+      if (*abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+    } else if (i * kTileTokens + tid >= n_valid) {
+      uint8_t* vt = stage + (i == 0 ? 2 : 0) * kStageBytes + tid * 128;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) { st16(vt + c * 16, make_uint4(0, 0, 0, 0)); st16(vt + kHalfBytes + c * 16, make_uint4(0, 0, 0, 0)); }
+    }
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  // ---- thread 0: O^T += V^T . P for both tiles
+  if (tid == 0 && *abort_flag == 0) {
+    bool ok = true;
+    for (int i = 0; i < ntiles && ok; ++i) {
+      ok = mbar_wait(&sm->bar_v[i], 0);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t a0 = smem_u32(stage + (i == 0 ? 2 : 0) * kStageBytes);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {  // 16 tokens per MMA = 2048 bytes further down both 64-dim halves
+        const uint64_t ad = make_desc(a0 + k * 2048, kHalfBytes, 1024, 2);
+        const uint64_t bd = make_desc(smem_u32(p_s + i * kPBytes) + k * 256, 128, 2048, 0);
+        umma(tmem + 32, ad, bd, idesc_pv, (i > 0 || k > 0));
+      }
+    }
+    if (ok) umma_commit(&sm->bar_o);
+    else { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+  }
+  __syncwarp();
+  bool have_o = *abort_flag == 0 && mbar_wait_or_abort(&sm->bar_o, 0, abort_flag);
+  if (!have_o && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+  tc_fence_after();
+  if (have_o) {
+    float o[16];
+    tmem_ld16(tmem + ((uint32_t)(warp * 32) << 16) + 32, o);   // this thread owns output dimension `tid`
+    const int64_t item = (int64_t)seg * p.nchunks + chunk;
+#pragma unroll
+    for (int g = 0; g < kG; ++g) {
+      const float ls = sm->red_sum[0][g] + sm->red_sum[1][g] + sm->red_sum[2][g] + sm->red_sum[3][g];
+      if (p.nchunks == 1) {
+        const float r = ls > 0.f ? o[g] / ls : 0.f;
+        char* op = p.out + ((int64_t)b * p.hq + h * kG + g) * 256;
+        if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[tid] = __float2bfloat16_rn(r);
+        else reinterpret_cast<__half*>(op)[tid] = __float2half_rn(r);
+      } else {
+        p.part_o[(item * kG + g) * 128 + tid] = o[g];
+        if (tid == 0) { p.part_ml[(item * kG + g) * 2] = mx[g]; p.part_ml[(item * kG + g) * 2 + 1] = ls; }
+      }
+    }
+  }
+  // An aborting CTA still drains the copies it started before its shared memory is released.
+  if (tid == 0 && *abort_flag != 0) {
+    for (int i = 0; i < ntiles; ++i) mbar_wait(&sm->bar_k[i], 0);
+    mbar_wait(&sm->bar_v[0], 0);
+    if (v1_issued) mbar_wait(&sm->bar_v[1], 0);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols));
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int kv_dtype) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {128, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {256};
+  const cuuint32_t box[2] = {64, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, kv_dtype == TKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                  const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return TKV_OK;
+}
+
+int attn_tc_chunk_tokens() { return kTcChunk; }
+
+template <int kDtype, int kG>
+static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int nseg, cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_tc_kernel<kDtype, kG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kTcSmemBytes);
+    if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  decode_attn_tc_kernel<kDtype, kG><<<(unsigned)((int64_t)nseg * p.nchunks), kTcThreads, kTcSmemBytes, st>>>(mk, mv, p);
+  return check_launch("tkv_decode_attn(tc)");
+}
+
+template <int kDtype>
+static int launch_tc_g(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int nseg, int G, cudaStream_t st) {
+  switch (G) {
+    case 1: return launch_tc<kDtype, 1>(mk, mv, p, nseg, st);
+    case 2: return launch_tc<kDtype, 2>(mk, mv, p, nseg, st);
+    case 3: return launch_tc<kDtype, 3>(mk, mv, p, nseg, st);
+    case 4: return launch_tc<kDtype, 4>(mk, mv, p, nseg, st);
+    case 5: return launch_tc<kDtype, 5>(mk, mv, p, nseg, st);
+    case 6: return launch_tc<kDtype, 6>(mk, mv, p, nseg, st);
+    case 7: return launch_tc<kDtype, 7>(mk, mv, p, nseg, st);
+    case 8: return launch_tc<kDtype, 8>(mk, mv, p, nseg, st);
+    default: return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(tc): %d query heads per KV head", G);
+  }
+}
+
+// Launches the tensor-core split kernel; `rows` = number of rows addressable behind k/v (bounds of the tensor maps).
+int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, int64_t rows, cudaStream_t st) {
+  CUtensorMap mk, mv;
+  int rc = make_map(&mk, p.k, rows, kv_dtype);
+  if (rc != TKV_OK) return rc;
+  rc = make_map(&mv, p.v, rows, kv_dtype);
+  if (rc != TKV_OK) return rc;
+  return kv_dtype == TKV_BF16 ? launch_tc_g<TKV_BF16>(mk, mv, p, nseg, G, st) : launch_tc_g<TKV_F16>(mk, mv, p, nseg, G, st);
+}
+
+}  // namespace tkv

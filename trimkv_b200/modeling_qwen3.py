@@ -164,16 +164,27 @@ class TrimKVQwen3DecoderLayer(nn.Module):
 
 
 class Qwen3RotaryEmbedding(nn.Module):
+    """cos/sin of the rotary embedding.  The inverse frequencies stay in fp32 whatever dtype the model is cast
+    to (they are not a registered buffer, so ``model.to(bfloat16)`` cannot round them), as they do when the
+    reference model is loaded through ``from_pretrained(torch_dtype=bfloat16)``."""
+
     def __init__(self, config):
         super().__init__()
         d = config.head_dim
-        inv_freq = 1.0 / (config.rope_theta ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
-        self.register_buffer("inv_freq", inv_freq, persistent=False)
+        self._inv_freq = 1.0 / (config.rope_theta ** (torch.arange(0, d, 2, dtype=torch.int64).float() / d))
+        self._per_device = {}
+
+    def inv_freq_on(self, device):
+        t = self._per_device.get(device)
+        if t is None:
+            t = self._inv_freq.to(device=device, dtype=torch.float32)
+            self._per_device[device] = t
+        return t
 
     @torch.no_grad()
     def forward(self, x, position_ids):
-        inv = self.inv_freq[None, :, None].float().expand(position_ids.shape[0], -1, 1)
-        freqs = (inv @ position_ids[:, None, :].float()).transpose(1, 2)
+        inv = self.inv_freq_on(x.device)
+        freqs = position_ids[:, :, None].float() * inv[None, None, :]
         emb = torch.cat((freqs, freqs), dim=-1)
         return emb.cos().to(x.dtype), emb.sin().to(x.dtype)
 
