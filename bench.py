@@ -227,10 +227,15 @@ def run_micro(args):
         alg = (8 * n_sum + nseg * 1032 * M) if args.micro == "evict" else nseg * 2 * 520
         res["config"] = {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16", "buffers": nbuf}
     else:
-        batch, hq, hkv = args.nseg // 8, 32, 8
-        lens = torch.exp(torch.randn(nseg, generator=g, device=dev) + 7.6246).clamp(64, 8192).round().to(torch.int32)
-        cap = 8192
-        nbuf = 2
+        if args.attn_shape == "config4":   # Qwen3-8B heads, ragged lengths
+            batch, hq, hkv = args.nseg // 8, 32, 8
+            lens = torch.exp(torch.randn(nseg, generator=g, device=dev) + 7.6246).clamp(64, 8192).round().to(torch.int32)
+            cap = 8192
+        else:                              # one layer of the decode benchmark: Qwen3-1.7B heads, n ~ M + B/2
+            batch, hq, hkv = args.nseg // 8, 16, 8
+            cap = M + Bf
+            lens = torch.full((nseg,), M + Bf // 2, device=dev, dtype=torch.int32)
+        nbuf = 2 if nseg * cap * 512 > (1 << 28) else 4
         bufs = [(torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16),
                  torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)) for _ in range(nbuf)]
         q = torch.randn(batch, hq, D, generator=g, device=dev, dtype=torch.bfloat16)
@@ -247,7 +252,7 @@ def run_micro(args):
         torch.cuda.synchronize()
         alg = int(lens.long().sum()) * 4 * D + batch * hq * D * 4
         res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
-                         "mean_len": float(lens.float().mean()), "buffers": nbuf}
+                         "mean_len": float(lens.float().mean()), "buffers": nbuf, "shape": args.attn_shape}
     ms = sorted(a.elapsed_time(b) for a, b in times)
     avg = sum(ms) / len(ms)
     res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
@@ -259,6 +264,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, choices=["evict", "attn", "append"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
+    ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--nseg", type=int, default=2048)
     ap.add_argument("--gpus", type=int, default=1)

@@ -190,6 +190,7 @@ decode_attn_split_kernel(AttnParams p) {
 template <int kDtype, int kD>
 __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   const int seg = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
+  grid_dependency_wait();  // launched with programmatic serialization behind the split kernel
   if (p.seg_len[seg] > p.max_len && g == 0 && d == 0) report(p.status, TKV_DEV_LEN_BOUND);
   const int len = min(p.seg_len[seg], p.max_len);
   const int b = seg / p.hkv, h = seg - b * p.hkv;
@@ -200,8 +201,10 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
     if (p.nchunks == 1) return;  // written by the split kernel
     const int nact = (len + p.chunk - 1) / p.chunk;
     float mx = -INFINITY;
+#pragma unroll 8
     for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(((int64_t)seg * p.nchunks + c) * G + g) * 2]);
     float o = 0.f, ls = 0.f;
+#pragma unroll 8
     for (int c = 0; c < nact; ++c) {
       const int64_t it = ((int64_t)seg * p.nchunks + c) * G + g;
       const float mc = p.part_ml[it * 2];
@@ -248,9 +251,11 @@ static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st) {
 }
 
 int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st) {
-  if (head_dim == 128 && kv_dtype == TKV_BF16) decode_attn_combine_kernel<TKV_BF16, 128><<<dim3(nseg, G), 128, 0, st>>>(p);
-  else if (head_dim == 128 && kv_dtype == TKV_F16) decode_attn_combine_kernel<TKV_F16, 128><<<dim3(nseg, G), 128, 0, st>>>(p);
+  cudaError_t e;
+  if (head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
+  else if (head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_kernel<TKV_F16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
   else return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(combine): head_dim=%d dtype=%d", head_dim, kv_dtype);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(combine): %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_attn(combine)");
 }
 

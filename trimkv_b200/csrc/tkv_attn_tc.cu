@@ -122,9 +122,21 @@ __global__ void __launch_bounds__(kTcThreads)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
   const int seg = blockIdx.x / p.nchunks, chunk = blockIdx.x - seg * p.nchunks;
+  grid_dependency_wait();  // the lengths and the newest rows come from the preceding kernel of the stream
   const int len = min(p.seg_len[seg], p.max_len);
   const int t0 = chunk * kTcChunk;
-  if (t0 >= len) return;
+  if (t0 >= len) {
+    if (chunk == 0) {  // empty segment: its query heads get zeros
+      const int b0 = seg / p.hkv, h0 = seg - b0 * p.hkv;
+      for (int g = 0; g < kG; ++g) {
+        char* op = p.out + ((int64_t)b0 * p.hq + h0 * kG + g) * 256;
+        if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[threadIdx.x] = __float2bfloat16_rn(0.f);
+        else reinterpret_cast<__half*>(op)[threadIdx.x] = __float2half_rn(0.f);
+      }
+    }
+    return;
+  }
+  if (chunk == 0 && threadIdx.x == 0 && p.seg_len[seg] > p.max_len) report(p.status, TKV_DEV_LEN_BOUND);
   const int n_valid = min(kTcChunk, len - t0);
   const int ntiles = (n_valid + kTileTokens - 1) / kTileTokens;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -136,16 +148,28 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   uint8_t* p_s = q_s + kQBytes;                            // 2 x 4 KB
   TcSmem* sm = reinterpret_cast<TcSmem*>(p_s + 2 * kPBytes);
 
-  if (warp == 0) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kTmemCols));
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-  }
+  const int64_t row0 = (p.seg_start != nullptr ? (int64_t)p.seg_start[seg] : (int64_t)seg * p.cap) + t0;
+  // Thread 0 arms the barriers and starts every copy this CTA can hold before anything else, so the rest of
+  // the prologue (TMEM allocation, Q staging) runs under the latency of the loads.
   if (tid == 0) {
     mbar_init(&sm->bar_k[0], 1); mbar_init(&sm->bar_k[1], 1);
     mbar_init(&sm->bar_v[0], 1); mbar_init(&sm->bar_v[1], 1);
     mbar_init(&sm->bar_s, 1); mbar_init(&sm->bar_o, 1);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int i = 0; i < ntiles; ++i) {
+      mbar_expect_tx(&sm->bar_k[i], kStageBytes);
+      tma_load_2d(stage + i * kStageBytes, &map_k, &sm->bar_k[i], 0, (int)(row0 + i * kTileTokens));
+      tma_load_2d(stage + i * kStageBytes + kHalfBytes, &map_k, &sm->bar_k[i], 64, (int)(row0 + i * kTileTokens));
+    }
+    mbar_expect_tx(&sm->bar_v[0], kStageBytes);
+    tma_load_2d(stage + 2 * kStageBytes, &map_v, &sm->bar_v[0], 0, (int)row0);
+    tma_load_2d(stage + 2 * kStageBytes + kHalfBytes, &map_v, &sm->bar_v[0], 64, (int)row0);
+  }
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
   }
   // Q of this KV head's query heads as the B operand: rows = heads (16, zero beyond kG), K-major without
   // swizzle: 8x8 core matrices of 128 B, K-adjacent cores 128 B apart, the second group of 8 heads 2048 B further.
@@ -160,22 +184,13 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const int64_t row0 = (p.seg_start != nullptr ? (int64_t)p.seg_start[seg] : (int64_t)seg * p.cap) + t0;
   const uint32_t idesc_qk = make_idesc(kDtype == TKV_BF16 ? 1 : 0, 0);
   const uint32_t idesc_pv = make_idesc(kDtype == TKV_BF16 ? 1 : 0, 1);
   volatile int* abort_flag = &sm->abort_flag;
   bool v1_issued = false;
 
-  // ---- thread 0: start every load this CTA can hold, then S = K . Q^T for both tiles
+  // ---- thread 0: S = K . Q^T for both tiles
   if (tid == 0) {
-    for (int i = 0; i < ntiles; ++i) {
-      mbar_expect_tx(&sm->bar_k[i], kStageBytes);
-      tma_load_2d(stage + i * kStageBytes, &map_k, &sm->bar_k[i], 0, (int)(row0 + i * kTileTokens));
-      tma_load_2d(stage + i * kStageBytes + kHalfBytes, &map_k, &sm->bar_k[i], 64, (int)(row0 + i * kTileTokens));
-    }
-    mbar_expect_tx(&sm->bar_v[0], kStageBytes);
-    tma_load_2d(stage + 2 * kStageBytes, &map_v, &sm->bar_v[0], 0, (int)row0);
-    tma_load_2d(stage + 2 * kStageBytes + kHalfBytes, &map_v, &sm->bar_v[0], 64, (int)row0);
     bool ok = true;
     for (int i = 0; i < ntiles && ok; ++i) {
       ok = mbar_wait(&sm->bar_k[i], 0);
@@ -374,7 +389,9 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnPar
     if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
     configured = true;
   }
-  decode_attn_tc_kernel<kDtype, kG><<<(unsigned)((int64_t)nseg * p.nchunks), kTcThreads, kTcSmemBytes, st>>>(mk, mv, p);
+  cudaError_t e = launch_pdl(decode_attn_tc_kernel<kDtype, kG>, dim3((unsigned)((int64_t)nseg * p.nchunks)), dim3(kTcThreads),
+                             (size_t)kTcSmemBytes, st, mk, mv, p);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_attn(tc)");
 }
 

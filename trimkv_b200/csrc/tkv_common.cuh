@@ -47,6 +47,21 @@ __device__ __forceinline__ uint4 ld16_stream(const void* p) {
   return v;
 }
 
+// Programmatic dependent launch: a kernel launched with launch_pdl() may be scheduled while its predecessor in
+// the stream is still draining; it must call grid_dependency_wait() before touching anything the predecessor wrote.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <int kThreads>
 __device__ __forceinline__ int block_exclusive_scan(int v, int* warp_sums /* [kThreads/32 + 1] */, int* total) {
   // Inclusive warp scan, then scan of the warp totals by warp 0.
