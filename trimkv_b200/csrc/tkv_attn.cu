@@ -200,19 +200,53 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   if (len > 0) {
     if (p.nchunks == 1) return;  // written by the split kernel
     const int nact = (len + p.chunk - 1) / p.chunk;
-    float mx = -INFINITY;
+    const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
+    if (nact <= kD) {
+      // One round trip for all (max, sum) pairs: thread c takes chunk c, the block reduces, the weights go to
+      // shared memory; then every thread sums its output dimension over the chunks with independent loads.
+      __shared__ float s_w[kD];
+      __shared__ float s_red[2][kD / 32];
+      const int lane = d & 31, warp = d >> 5;
+      float mc = -INFINITY, lc = 0.f;
+      if (d < nact) {
+        const float2 ml = *reinterpret_cast<const float2*>(&p.part_ml[(it0 + (int64_t)d * G) * 2]);
+        mc = ml.x; lc = ml.y;
+      }
+      float mx = mc;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      if (lane == 0) s_red[0][warp] = mx;
+      __syncthreads();
+      mx = s_red[0][0];
+#pragma unroll
+      for (int w = 1; w < kD / 32; ++w) mx = fmaxf(mx, s_red[0][w]);
+      const float wgt = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
+      if (d < nact) s_w[d] = wgt;
+      float ls = lc * wgt;
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+      if (lane == 0) s_red[1][warp] = ls;
+      __syncthreads();
+      ls = 0.f;
+#pragma unroll
+      for (int w = 0; w < kD / 32; ++w) ls += s_red[1][w];
+      float o = 0.f;
 #pragma unroll 8
-    for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(((int64_t)seg * p.nchunks + c) * G + g) * 2]);
-    float o = 0.f, ls = 0.f;
-#pragma unroll 8
-    for (int c = 0; c < nact; ++c) {
-      const int64_t it = ((int64_t)seg * p.nchunks + c) * G + g;
-      const float mc = p.part_ml[it * 2];
-      const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
-      o = fmaf(p.part_o[it * kD + d], w, o);
-      ls = fmaf(p.part_ml[it * 2 + 1], w, ls);
+      for (int c = 0; c < nact; ++c) o = fmaf(p.part_o[(it0 + (int64_t)c * G) * kD + d], s_w[c], o);
+      r = ls > 0.f ? o / ls : 0.f;
+    } else {
+      float mx = -INFINITY;
+      for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(it0 + (int64_t)c * G) * 2]);
+      float o = 0.f, ls = 0.f;
+      for (int c = 0; c < nact; ++c) {
+        const int64_t it = it0 + (int64_t)c * G;
+        const float mc = p.part_ml[it * 2];
+        const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
+        o = fmaf(p.part_o[it * kD + d], w, o);
+        ls = fmaf(p.part_ml[it * 2 + 1], w, ls);
+      }
+      r = ls > 0.f ? o / ls : 0.f;
     }
-    r = ls > 0.f ? o / ls : 0.f;
   }
   if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16_rn(r);
   else reinterpret_cast<__half*>(op)[d] = __float2half_rn(r);

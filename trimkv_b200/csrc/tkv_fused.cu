@@ -69,6 +69,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   const int w = blockIdx.x * kPrepWarps + (threadIdx.x >> 5);
   const int heads = p.hq + p.hkv;
   if (w >= p.batch * heads) return;
+  grid_dependency_wait();
   const int b = w / heads, head = w - b * heads;
   const bool is_q = head < p.hq;
   const int kvh = head - p.hq;
@@ -133,6 +134,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
                                                           char* out, int cols, float eps) {
   using T = T16<kDtype>;
   __shared__ float red[8];
+  grid_dependency_wait();
   const int64_t off = (int64_t)blockIdx.x * cols * 2;
   const int nvec = cols / 8;  // 16-byte vectors per row
   float ss = 0.f;
@@ -177,6 +179,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const char* gu, char* out
   using T = T16<kDtype>;
   const int nvec = inter / 8;
   const int64_t total = (int64_t)rows * nvec;
+  grid_dependency_wait();
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const int64_t r = i / nvec, c = i - r * nvec;
     const uint4 g = ld16(gu + (r * 2 * inter) * 2 + c * 16);
@@ -227,8 +230,10 @@ extern "C" int tkv_decode_prep(const void* qkvg, int64_t row_stride,
   p.batch = batch; p.hq = hq; p.hkv = hkv; p.status = status;
   const int warps = batch * (hq + hkv);
   const int grid = (warps + kPrepWarps - 1) / kPrepWarps;
-  if (dtype == TKV_BF16) decode_prep_kernel<TKV_BF16><<<grid, kPrepWarps * 32, 0, (cudaStream_t)stream>>>(p);
-  else decode_prep_kernel<TKV_F16><<<grid, kPrepWarps * 32, 0, (cudaStream_t)stream>>>(p);
+  cudaError_t e = dtype == TKV_BF16
+      ? launch_pdl(decode_prep_kernel<TKV_BF16>, dim3(grid), dim3(kPrepWarps * 32), 0, (cudaStream_t)stream, p)
+      : launch_pdl(decode_prep_kernel<TKV_F16>, dim3(grid), dim3(kPrepWarps * 32), 0, (cudaStream_t)stream, p);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_prep: %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_prep");
 }
 
@@ -241,10 +246,12 @@ extern "C" int tkv_add_rmsnorm(void* residual, const void* delta, const void* we
   if (!aligned16(residual) || !aligned16(weight) || !aligned16(out) || (delta && !aligned16(delta)))
     return fail(TKV_ERR_ARG, "tkv_add_rmsnorm: pointers must be 16-byte aligned");
   if (rows == 0) return TKV_OK;
-  if (dtype == TKV_BF16)
-    add_rmsnorm_kernel<TKV_BF16><<<rows, 256, 0, (cudaStream_t)stream>>>((char*)residual, (const char*)delta, weight, (char*)out, cols, eps);
-  else
-    add_rmsnorm_kernel<TKV_F16><<<rows, 256, 0, (cudaStream_t)stream>>>((char*)residual, (const char*)delta, weight, (char*)out, cols, eps);
+  cudaError_t e = dtype == TKV_BF16
+      ? launch_pdl(add_rmsnorm_kernel<TKV_BF16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (char*)residual,
+                   (const char*)delta, weight, (char*)out, cols, eps)
+      : launch_pdl(add_rmsnorm_kernel<TKV_F16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (char*)residual,
+                   (const char*)delta, weight, (char*)out, cols, eps);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_add_rmsnorm: %s", cudaGetErrorString(e));
   return check_launch("tkv_add_rmsnorm");
 }
 
@@ -257,7 +264,9 @@ extern "C" int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter,
   if (rows == 0) return TKV_OK;
   const int64_t total = (int64_t)rows * (inter / 8);
   const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
-  if (dtype == TKV_BF16) silu_mul_kernel<TKV_BF16><<<grid, 256, 0, (cudaStream_t)stream>>>((const char*)gate_up, (char*)out, rows, inter);
-  else silu_mul_kernel<TKV_F16><<<grid, 256, 0, (cudaStream_t)stream>>>((const char*)gate_up, (char*)out, rows, inter);
+  cudaError_t e = dtype == TKV_BF16
+      ? launch_pdl(silu_mul_kernel<TKV_BF16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out, rows, inter)
+      : launch_pdl(silu_mul_kernel<TKV_F16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out, rows, inter);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_silu_mul: %s", cudaGetErrorString(e));
   return check_launch("tkv_silu_mul");
 }

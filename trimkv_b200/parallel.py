@@ -1,0 +1,61 @@
+"""Batch partition of requests across the GPUs of one box.
+
+Every (request, layer, KV head) segment of the cache is appended to, evicted and attended independently
+(the reference's per-head policy is row-wise over ``[B, Hkv]``, src/trimkv/cache_utils.py:190-198), so requests
+are split across ranks and each rank runs its own model replica and cache: there is no collective on the cache
+path.  The only exchange is the gather of the generated token ids at the end.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def partition_bounds(num_requests: int, world_size: int, rank: int) -> Tuple[int, int]:
+    """Contiguous slice ``[lo, hi)`` of the request list owned by ``rank``; sizes differ by at most one."""
+    if not 0 <= rank < world_size:
+        raise ValueError(f"rank {rank} outside world of {world_size}")
+    base, extra = divmod(num_requests, world_size)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def gather_rows(local: torch.Tensor, num_requests: int, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """All ranks' row blocks (rank order = request order) concatenated on every rank.
+
+    ``local`` is ``[n_local, T]`` on any device the backend supports; blocks may have different ``n_local``.
+    """
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return local
+    world = dist.get_world_size(group)
+    width = local.shape[1]
+    sizes = [partition_bounds(num_requests, world, r) for r in range(world)]
+    biggest = max(hi - lo for lo, hi in sizes)
+    padded = local.new_zeros(biggest, width)
+    padded[: local.shape[0]] = local
+    out = [torch.empty_like(padded) for _ in range(world)]
+    dist.all_gather(out, padded, group=group)
+    return torch.cat([o[: hi - lo] for o, (lo, hi) in zip(out, sizes)], dim=0)
+
+
+def generate_partitioned(generate_fn: Callable[[torch.Tensor], torch.Tensor], input_ids: torch.Tensor,
+                         group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Runs ``generate_fn`` on this rank's slice of ``input_ids`` ``[N, S]`` and returns all ``[N, S + new]`` rows.
+
+    ``generate_fn`` is e.g. ``lambda ids: model.generate(ids, max_new_tokens=..., past_key_values=TrimKVCache())``.
+    Results are identical to a single-rank run request by request, because no state is shared between requests.
+    """
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    lo, hi = partition_bounds(input_ids.shape[0], world, rank)
+    local = generate_fn(input_ids[lo:hi]) if hi > lo else input_ids.new_zeros(0, 0)
+    if world == 1:
+        return local
+    # ranks with no request still have to agree on the row width
+    width = torch.tensor([local.shape[1] if hi > lo else 0], dtype=torch.int64, device=input_ids.device)
+    dist.all_reduce(width, op=dist.ReduceOp.MAX, group=group)
+    if hi == lo:
+        local = input_ids.new_zeros(0, int(width.item()))
+    return gather_rows(local, input_ids.shape[0], group)
