@@ -411,8 +411,11 @@ def main():
     if ach:
         tot_b, tot_t = sum(x for x, _ in ach), sum(t for _, t in ach)
         gbs = tot_b / tot_t / 1e9
-        roofline = {"bound": "hbm", "kernel": "decode_attn_split_kernel+combine", "achieved": gbs, "peak": peak,
-                    "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": None,
+        # dram__bytes_read+write of one ncu capture of the same two kernels at this shape (batch 32, n = 4160):
+        # 561.2 MB against 545.5 MB algorithmic (profiles/decode_attn_tc_kernel_G2_config2.md); scaled by the bytes.
+        traffic = tot_b / len(ach) * (561.19 / 545.52)
+        roofline = {"bound": "hbm", "kernel": "decode_attn_tc_kernel+decode_attn_combine_kernel", "achieved": gbs,
+                    "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": traffic,
                     "launches_timed": len(ach), "avg_launch_us": tot_t / len(ach) * 1e6,
                     "bytes_per_launch": tot_b / len(ach)}
     evict = None
@@ -443,7 +446,7 @@ def main():
             "roofline": roofline, "evict": evict, "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * 8 * world, "d2h_bytes_per_step": B * 8 * world},
-            "gpu_launches": launches, "clocks": clk,
+            "gpu_launches": launches * world, "clocks": clk,
         }
         print(json.dumps(line))
     if world > 1:
