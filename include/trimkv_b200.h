@@ -128,6 +128,47 @@ int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cach
               int memory_size, int trigger_len, int max_len,
               int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
 
+/*
+ * tkv_evict with a keep count per segment and a protected tail.
+ * keep_cnt (nullable, [nseg]): segment s keeps its keep_cnt[s] best rows (untouched if keep_cnt[s] >= its
+ * length); with keep_cnt == NULL it behaves as tkv_evict.  protect_last: the newest rows always score +inf
+ * (TrimKVCache.sliding_window_size, src/trimkv/cache_utils.py:186-187).  kept_stride: row stride of
+ * kept_idx_out when keep counts vary.  Used after tkv_group_budget for the budget-sharing strategies.
+ */
+int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                 int32_t* seg_len, int32_t* cu_seqlens, int group,
+                 int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                 int memory_size, int trigger_len, int max_len,
+                 const int32_t* keep_cnt, int protect_last, int kept_stride,
+                 int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
+
+/*
+ * Keep counts under a shared token budget.  Group g consists of the segments
+ * {g*inner + o*outer_stride + i : o < n_outer, i < inner}; among all rows of a group the k_total best scores are
+ * kept (ties: lower index in that concatenated order), or, with use_threshold, every row whose score is
+ * >= threshold.  Per segment the number of kept rows s becomes keep_cnt = s (floor_mode 0),
+ * min(len, s' + floor_cnt) (1) or max(s, min(floor_cnt, len)) (2); in mode 1, s' is s after the reference's
+ * attribution (src/trimkv/cache_utils.py:495-498: a kept row that is the first of its head is counted for the
+ * preceding head of the group).
+ * Replaces the top-k + mask + per-head .item() loops of _compress_layer, _compress_all_layers,
+ * _compress_layer_batched and _compress_all_layers_batched
+ * (src/trimkv/cache_utils.py:371-416, 418-536, 740-834, 836-945); scores are fp32.
+ */
+int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const int32_t* seg_len, int64_t cap,
+                     int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
+                     int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
+                     int32_t* keep_cnt, int32_t* status, tkv_stream_t stream);
+
+/*
+ * Functional append on the reference's packed layout: out[origin_rows + heads*s_new, row] = for every head its
+ * old rows followed by its s_new new rows.  cache: [origin_rows, row_bytes]; state: [heads*s_new, row_bytes];
+ * cu_headlens: [heads+1] exclusive prefix sum of the old per-head lengths.  Any row size (K/V rows, 2-byte log
+ * beta, 8-byte positions).  Same contract as update_flatten_view_triton
+ * (src/trimkv/triton/db_cache_utils.py:86-186) without its host synchronisation.
+ */
+int tkv_flat_append_packed(const void* cache, const void* state, const int32_t* cu_headlens, void* out,
+                           int heads, int s_new, int64_t origin_rows, int64_t row_bytes, tkv_stream_t stream);
+
 /* Rebuild cu_seqlens[g, 0..group] = exclusive prefix sum of seg_len[g*group .. ] for each group. */
 int tkv_rebuild_cu_seqlens(const int32_t* seg_len, int32_t* cu_seqlens, int nseg, int group,
                            tkv_stream_t stream);

@@ -72,13 +72,16 @@ def canonical_topm(scores: np.ndarray, m: int) -> np.ndarray:
     return out.reshape(s.shape[:-1] + (m,))
 
 
-def compress_rows(key, value, log_beta, kv_positions, q_idx: int, m: int):
+def compress_rows(key, value, log_beta, kv_positions, q_idx: int, m: int, sliding_window_size: int = 0):
     """One ``compress_layer`` on dense ``[..., n, D]`` / ``[..., n]`` arrays.
 
-    src/trimkv/cache_utils.py:167-198, strategy "alpha", no sliding window.
+    src/trimkv/cache_utils.py:167-198, strategy "alpha"; the newest ``sliding_window_size`` rows score +inf (:186-187).
     Returns (key, value, log_beta, kv_positions, kept_idx).
     """
     sc = retention_scores(log_beta, kv_positions, q_idx)
+    if sliding_window_size > 0:
+        sc = sc.copy()
+        sc[..., -sliding_window_size:] = np.inf
     keep = canonical_topm(sc, m)
     k2 = np.take_along_axis(key, keep[..., None], axis=-2)
     v2 = np.take_along_axis(value, keep[..., None], axis=-2)
@@ -103,6 +106,7 @@ class OracleTrimKVCache:
         self.kv_positions = []
         self.n_seen_tokens = []
         self.last_kept = {}
+        self.sliding_window_size = 0
 
     def __len__(self):
         return len(self.key_cache)
@@ -168,7 +172,8 @@ class OracleTrimKVCache:
         q_idx = self.get_seq_length(layer_idx) + 1
         k, v, b, p, keep = compress_rows(
             self.key_cache[layer_idx], self.value_cache[layer_idx],
-            self.retention_weights[layer_idx], self.kv_positions[layer_idx], q_idx, memory_size)
+            self.retention_weights[layer_idx], self.kv_positions[layer_idx], q_idx, memory_size,
+            self.sliding_window_size)
         self.key_cache[layer_idx] = k
         self.value_cache[layer_idx] = v
         self.retention_weights[layer_idx] = b
@@ -327,3 +332,130 @@ def dense_gqa_attention(query, key, value, scale=None, causal=True):
     if not causal:
         raise NotImplementedError
     return varlen_gqa_attention(query, kf, vf, cu, b_, hkv, scale)
+
+
+# --------------------------------------------------------------------------
+# budget-sharing eviction of the flat caches
+# --------------------------------------------------------------------------
+def _group_keep_counts(scores, k_total=None, threshold=None, bucketize_attribution=False):
+    """scores: list of 1-D fp32 arrays (the group's segments in concatenated order).  Returns how many rows of
+    each segment are among the group's k_total best (canonical ties: lower concatenated index first), or
+    score >= threshold.
+
+    bucketize_attribution restates src/trimkv/cache_utils.py:495-498: the selected flat indices are attributed to
+    heads with ``torch.bucketize(idx, cumsum(head_lens))`` (right=False), which files an index equal to a boundary
+    -- the first row of the next head -- under the previous head."""
+    lens = [len(s) for s in scores]
+    flat = np.concatenate(scores) if scores else np.zeros((0,), np.float32)
+    if threshold is not None:
+        keep = flat >= np.float32(threshold)
+    else:
+        k = min(int(k_total), flat.shape[0])
+        keep = np.zeros(flat.shape[0], bool)
+        if k > 0:
+            keep[canonical_topm(flat[None], k)[0]] = True
+    out, a = [], 0
+    if bucketize_attribution:
+        bounds = np.cumsum(lens)
+        which = np.searchsorted(bounds, np.nonzero(keep)[0], side="left")
+        return [int((which == j).sum()) for j in range(len(lens))]
+    for n in lens:
+        out.append(int(keep[a:a + n].sum())); a += n
+    return out
+
+
+class OracleFlatBudgetCache(OracleBatchedFlatCache):
+    """``compress`` of the reference's flat caches, with fp32 scores and canonical ties.
+
+    ``batched=True`` restates BatchedDynamicBudgetTrimKVCache.compress (src/trimkv/cache_utils.py:697-945),
+    ``batched=False`` DynamicBudgetTrimKVCache.compress (:334-536, batch size 1).  Keeping a group's top-k equals
+    keeping each segment's own top-c rows for the per-segment counts c, so every variant reduces to counts.
+    """
+
+    def __init__(self, batched=True):
+        super().__init__()
+        self.batched = batched
+
+    def _scores(self, l, seg):
+        a, n = int(self.cu_seqlens_k[l][seg]), int(self.head_lens[l][seg])
+        return retention_scores(self.retention_weights[l][a:a + n, 0], self.kv_positions[l][a:a + n, 0],
+                                self._seen_tokens + 1)
+
+    def _apply(self, counts):
+        """counts[l][seg] rows kept (canonical top-c inside the segment)."""
+        q_idx = self._seen_tokens + 1
+        for l, cl in counts.items():
+            ks, vs, bs, ps, nl = [], [], [], [], []
+            for seg in range(self.head_lens[l].shape[0]):
+                a, n = int(self.cu_seqlens_k[l][seg]), int(self.head_lens[l][seg])
+                k, v = self.key_cache[l][a:a + n], self.value_cache[l][a:a + n]
+                b, p = self.retention_weights[l][a:a + n, 0], self.kv_positions[l][a:a + n, 0]
+                c = min(cl[seg], n)
+                if c < n:
+                    if c == 0:
+                        k, v, b, p = k[:0], v[:0], b[:0], p[:0]
+                    else:
+                        k, v, b, p, _ = compress_rows(k, v, b, p, q_idx, c)
+                ks.append(k); vs.append(v); bs.append(b[:, None]); ps.append(p[:, None]); nl.append(k.shape[0])
+            self.key_cache[l] = np.concatenate(ks, 0); self.value_cache[l] = np.concatenate(vs, 0)
+            self.retention_weights[l] = np.concatenate(bs, 0); self.kv_positions[l] = np.concatenate(ps, 0)
+            self.head_lens[l] = np.asarray(nl, dtype=np.int32)
+            self.cu_seqlens_k[l] = np.concatenate([[0], np.cumsum(nl)]).astype(np.int32)
+
+    def compress(self, strategy="alpha", memory_size=2048, buffer_size=512, floor_budget_ratio=0.0,
+                 alpha_threshold=0.0):
+        L = len(self.key_cache)
+        B = self.batch_size if self.batched else 1
+        H = self.num_kv_heads if self.batched else self.head_lens[0].shape[0]
+        M, Bf = memory_size, buffer_size
+        rows = [self.key_cache[l].shape[0] for l in range(L)]
+        total = sum(rows)
+        thr = "threshold" in strategy
+        log_thr = np.log(np.float32(alpha_threshold)) if thr else None
+        counts = {}
+        if self.batched:
+            if total <= B * H * (M + Bf) * L and not thr:          # :714-717
+                return
+            if "layer_wise" in strategy:                            # :719-729
+                for l in range(L):
+                    if rows[l] <= B * H * (M + Bf):
+                        continue
+                    cl = []
+                    for b in range(B):
+                        sc = [self._scores(l, b * H + h) for h in range(H)]
+                        k = M * H if floor_budget_ratio <= 0 else int(M * H * (1 - floor_budget_ratio))   # :781-783
+                        s = _group_keep_counts(sc, k_total=k)
+                        if floor_budget_ratio > 0:                  # :789-806
+                            fl = int(M * floor_budget_ratio)
+                            s = [max(si, min(fl, len(x))) for si, x in zip(s, sc)]
+                        cl += s
+                    counts[l] = cl
+            else:                                                   # :836-945
+                if total // B <= L * H * (M + Bf) and not thr:
+                    return
+                per = {l: [0] * (B * H) for l in range(L)}
+                for b in range(B):
+                    sc = [self._scores(l, b * H + h) for l in range(L) for h in range(H)]
+                    s = _group_keep_counts(sc, k_total=L * H * M, threshold=log_thr)
+                    for i, c in enumerate(s):
+                        per[i // H][b * H + i % H] = c
+                counts = per
+        else:
+            if "layer_wise" in strategy:                            # :356-369
+                for l in range(L):
+                    if H * (M + Bf) >= rows[l]:
+                        continue
+                    counts[l] = _group_keep_counts([self._scores(l, h) for h in range(H)], k_total=H * M)  # :396-397
+            else:                                                   # :418-536
+                if L * H * (M + Bf) > total and not thr:
+                    return
+                sc = [self._scores(l, h) for l in range(L) for h in range(H)]
+                if floor_budget_ratio == 0:
+                    s = _group_keep_counts(sc, k_total=L * H * M, threshold=log_thr)
+                else:
+                    s = _group_keep_counts(sc, k_total=int(L * H * M * (1 - floor_budget_ratio)),
+                                           bucketize_attribution=True)                                     # :491-498
+                    fl = int(M * floor_budget_ratio)                                                       # :499
+                    s = [min(len(x), si + fl) for si, x in zip(s, sc)]
+                counts = {l: s[l * H:(l + 1) * H] for l in range(L)}
+        self._apply(counts)

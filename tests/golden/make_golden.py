@@ -145,6 +145,61 @@ def flat_layout(cu):
     print("flat_layout: head_lens", kw["head_lens"].tolist())
 
 
+def sliding_window(cu):
+    """TrimKVCache with sliding_window_size: the newest rows are never evicted."""
+    torch.manual_seed(6)
+    Bt, H, D, S, M, B, T, W = 2, 3, 4, 50, 16, 4, 20, 6
+    cache = cu.TrimKVCache(device="cpu")
+    cache.sliding_window_size = W
+    logb = F.logsigmoid(torch.randn(Bt, H, S + T) * 1.5 + 3.0)
+    pos = []
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        k = torch.zeros(Bt, H, hi - lo, D)
+        cache.update(k, k.clone(), logb[:, :, lo:hi].contiguous(), torch.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            pos.append(cache.kv_positions[0].numpy().astype(np.int32).copy())
+    np.savez_compressed(os.path.join(HERE, "sliding_window.npz"), log_beta=logb.numpy(), kept_positions=np.stack(pos),
+                        M=M, B=B, S=S, T=T, W=W)
+    print("sliding_window: evictions", len(pos))
+
+
+def flat_budget(cu):
+    """Budget-sharing compress of the two flat cache classes (fp32 tensors, so scores are fp32 as on the CUDA path)."""
+    L, B, H, D, S, T, M, Bf = 2, 2, 3, 4, 40, 30, 8, 4
+    out = {}
+    cases = [("batched", "alpha", 0.0, 0.0), ("batched", "layer_wise_alpha", 0.0, 0.0),
+             ("batched", "layer_wise_alpha", 0.25, 0.0), ("batched", "alpha_threshold", 0.0, 0.35),
+             ("single", "alpha", 0.0, 0.0), ("single", "alpha", 0.25, 0.0), ("single", "layer_wise_alpha", 0.0, 0.0)]
+    for ci, (kind, strategy, floor, thr) in enumerate(cases):
+        torch.manual_seed(10 + ci)
+        bsz = B if kind == "batched" else 1
+        cls = cu.BatchedDynamicBudgetTrimKVCache if kind == "batched" else cu.DynamicBudgetTrimKVCache
+        cache = cls(device="cpu")
+        logb = F.logsigmoid(torch.randn(L, bsz, H, S + T) * 1.5 + 3.0)
+        lens, poss = [], []
+        for t in range(T + 1):
+            lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+            for l in range(L):
+                k = torch.arange(lo, hi, dtype=torch.float32)[None, None, :, None].expand(bsz, H, hi - lo, D) + 1000 * l
+                cache.update(k.contiguous(), -k.contiguous(), logb[l, :, :, lo:hi].contiguous(), torch.arange(lo, hi), l)
+            cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, floor_budget_ratio=floor,
+                           alpha_threshold=thr, num_layers=L, num_key_value_heads=H)
+            lens.append(torch.stack([cache.head_lens[l] for l in range(L)]).numpy().copy())
+            poss.append([cache.kv_positions[l][:, 0].numpy().astype(np.int32).copy() for l in range(L)])
+        out[f"c{ci}_logb"] = logb.numpy()
+        out[f"c{ci}_lens"] = np.stack(lens)
+        for t in (0, T // 2, T):
+            for l in range(L):
+                out[f"c{ci}_pos_t{t}_l{l}"] = poss[t][l]
+    out["meta"] = np.asarray([L, B, H, D, S, T, M, Bf])
+    out["cases"] = np.asarray([f"{k}|{s}|{f}|{a}" for k, s, f, a in cases])
+    np.savez_compressed(os.path.join(HERE, "flat_budget.npz"), **out)
+    print("flat_budget: ok")
+
+
 def eager_attention(ea):
     """Dense GQA attention from the reference's eager function (fp32), Q=1 and Q=3."""
     torch.manual_seed(3)
@@ -166,4 +221,6 @@ if __name__ == "__main__":
     ties_bf16(cu_)
     ties_single_shot(cu_)
     flat_layout(cu_)
+    sliding_window(cu_)
+    flat_budget(cu_)
     eager_attention(ea_)

@@ -125,3 +125,52 @@ def test_score_is_single_fp32_multiply():
     got = orc.retention_scores(lb, pos, 16777300)
     want = lb * (16777300 - pos).astype(np.float32)
     assert got.dtype == np.float32 and np.array_equal(got, want)
+
+
+def _replay_flat_budget(g, ci, make_cache, step_hook=None):
+    L, B, H, D, S, T, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, floor, thr = str(g["cases"][ci]).split("|")
+    floor, thr = float(floor), float(thr)
+    logb = g[f"c{ci}_logb"]
+    bsz = logb.shape[1]
+    cache = make_cache(kind == "batched")
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        for l in range(L):
+            k = np.broadcast_to(np.arange(lo, hi, dtype=np.float32)[None, None, :, None], (bsz, H, hi - lo, D)) + 1000 * l
+            cache.update(k.copy(), -k.copy(), logb[l, :, :, lo:hi], np.arange(lo, hi), l)
+        cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, floor_budget_ratio=floor, alpha_threshold=thr)
+        yield t, cache, (L, B, H, D, S, T, M, Bf)
+
+
+@pytest.mark.parametrize("ci", range(7))
+def test_flat_budget_compress_matches_reference(golden_dir, ci):
+    """Head lengths after every step and kept positions at three steps, for every strategy of both flat classes."""
+    g = _load(golden_dir, "flat_budget.npz")
+    for t, cache, (L, B, H, D, S, T, M, Bf) in _replay_flat_budget(g, ci, lambda batched: orc.OracleFlatBudgetCache(batched)):
+        got = np.stack([cache.head_lens[l] for l in range(L)])
+        assert np.array_equal(got, g[f"c{ci}_lens"][t]), (ci, t)
+        if t in (0, T // 2, T):
+            for l in range(L):
+                assert np.array_equal(cache.kv_positions[l][:, 0].astype(np.int32), g[f"c{ci}_pos_t{t}_l{l}"]), (ci, t, l)
+                # payload moves with its row: K row value == position + 1000*layer
+                assert np.array_equal(cache.key_cache[l][:, 0], cache.kv_positions[l][:, 0] + 1000.0 * l)
+
+
+def test_sliding_window_protects_newest_rows(golden_dir):
+    g = _load(golden_dir, "sliding_window.npz")
+    M, B, S, T, W = (int(g[k]) for k in "MBSTW")
+    logb = g["log_beta"]
+    cache = orc.OracleTrimKVCache()
+    cache.sliding_window_size = W
+    ev = 0
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        k = np.zeros(logb.shape[:2] + (hi - lo, 2), np.float32)
+        cache.update(k, k, logb[:, :, lo:hi], np.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            assert np.array_equal(cache.kv_positions[0].astype(np.int32), g["kept_positions"][ev])
+            ev += 1
+    assert ev == g["kept_positions"].shape[0] and ev >= 2

@@ -3,11 +3,13 @@
 Host code in Python/PyTorch (device memory, streams), arithmetic in hand-written CUDA behind
 the C ABI of include/trimkv_b200.h.  Importing the package does not need a GPU; using it does.
 """
-from .cache_utils import TrimKVCache
+from .cache_utils import BatchedDynamicBudgetTrimKVCache, DynamicBudgetTrimKVCache, TrimKVCache
+from .ops import update_flatten_view, update_flatten_view_triton
 from .attn import TRIMKV_ATTENTION_IMPLEMENTATIONS, get_attention_interface
 from .modeling_qwen3 import TrimKVQwen3Config, TrimKVQwen3ForCausalLM, TrimKVQwen3Model
 
 __all__ = [
-    "TrimKVCache", "TRIMKV_ATTENTION_IMPLEMENTATIONS", "get_attention_interface",
+    "TrimKVCache", "DynamicBudgetTrimKVCache", "BatchedDynamicBudgetTrimKVCache", "update_flatten_view",
+    "update_flatten_view_triton", "TRIMKV_ATTENTION_IMPLEMENTATIONS", "get_attention_interface",
     "TrimKVQwen3Config", "TrimKVQwen3ForCausalLM", "TrimKVQwen3Model",
 ]

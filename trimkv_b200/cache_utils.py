@@ -23,7 +23,7 @@ import torch
 
 from . import ops
 
-__all__ = ["TrimKVCache"]
+__all__ = ["TrimKVCache", "DynamicBudgetTrimKVCache", "BatchedDynamicBudgetTrimKVCache"]
 
 
 class _LayerViews:
@@ -265,7 +265,7 @@ class TrimKVCache:
             kept_longest = max((m if n >= m + bsz else n) for n in self._cache_len)
             cap = max(m + bsz, kept_longest + extra)
         else:
-            cap = 1 << max(8, (longest + extra + 255).bit_length())
+            cap = (longest + extra + 63) // 64 * 64 if extra >= 64 else 1 << max(8, (longest + extra + 255).bit_length())
         first = self._slab is None
         if first:
             self._cap = cap
@@ -297,12 +297,14 @@ class TrimKVCache:
 
     def _grow(self, need: int):
         """Re-homes every layer in slabs of at least ``need`` rows per segment (rare: no eviction or a large chunk)."""
+        self._rehome(max(need, 2 * self._cap))
+
+    def _rehome(self, new_cap: int):
         old, old_cap = self._slab, self._cap
-        new_cap = max(need, 2 * old_cap)
         self._slab, self._cap = self._alloc(new_cap), new_cap
         nseg = self._batch * self._hkv
         for l in range(len(self)):
-            n = self._cache_len[l]
+            n = min(self._cache_len[l], new_cap)
             if n == 0:
                 continue
             k = old["k"][l].view(self._batch, self._hkv, old_cap, self._dim)[:, :, :n]
@@ -327,16 +329,21 @@ class TrimKVCache:
             if strategy == "knorm_alpha":
                 raise NotImplementedError("compress strategy 'knorm_alpha' is not built on the CUDA path")
             raise ValueError(f"Unknown compression strategy: {strategy}")
-        if self.sliding_window_size:
-            raise NotImplementedError("sliding_window_size > 0 is not built on the CUDA path")
         num_layers = len(self) if num_layers is None else num_layers
         if num_layers == 0:
             return
         if any(p is not None for p in self._pending):
             if skip_layers:
                 raise NotImplementedError("skip_layers with a pending prompt")
-            self._materialise(memory_size=memory_size, buffer_size=buffer_size)
-            return
+            if not self.sliding_window_size:
+                self._materialise(memory_size=memory_size, buffer_size=buffer_size)
+                return
+            # A protected tail is only known to the in-place kernel: home the whole prompt, then evict below.
+            self._hint_m = self._hint_b = None
+            self._materialise(extra=max(64, buffer_size))
+        w = int(self.sliding_window_size)
+        if w >= memory_size and w > 0:
+            raise ValueError("sliding_window_size must be smaller than memory_size")
         trigger = memory_size + buffer_size
         fire = [l for l in range(skip_layers, num_layers) if trigger <= self._cache_len[l]]
         if not fire:
@@ -350,17 +357,17 @@ class TrimKVCache:
             nl, n = len(self), self._cache_len[0]
             if self.record_kept:
                 kept = torch.empty(nl * nseg, memory_size, dtype=torch.int32, device=s["k"].device)
-            ops.evict(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap,
-                      self.n_seen_tokens[0] + 1, memory_size, trigger, n, kept, self._status)
+            ops.evict_ex(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap,
+                         self.n_seen_tokens[0] + 1, n, None, w, memory_size, trigger, kept, 0, self._status)
             if kept is not None:
                 self.last_kept_idx = kept.view(nl, self._batch, self._hkv, memory_size)
         else:
             for l in fire:
                 if self.record_kept:
                     kept = torch.empty(nseg, memory_size, dtype=torch.int32, device=s["k"].device)
-                ops.evict(s["k"][l], s["v"][l], s["beta"][l], s["pos"][l], s["len"][l], s["cu"][l], nseg, nseg,
-                          self._cap, self.n_seen_tokens[l] + 1, memory_size, trigger, self._cache_len[l], kept,
-                          self._status)
+                ops.evict_ex(s["k"][l], s["v"][l], s["beta"][l], s["pos"][l], s["len"][l], s["cu"][l], nseg, nseg,
+                             self._cap, self.n_seen_tokens[l] + 1, self._cache_len[l], None, w, memory_size, trigger,
+                             kept, 0, self._status)
                 if kept is not None:
                     self.last_kept_idx = kept.view(self._batch, self._hkv, memory_size)
         for l in fire:
@@ -417,3 +424,193 @@ class TrimKVCache:
         dense = [(k.to(device).contiguous(), v.to(device).contiguous(), b.to(device).contiguous(),
                   p.to(device).contiguous()) for (k, v, b, p) in self]
         return self._clone_from_dense(dense, device=device)
+
+
+class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
+    """Flat varlen cache whose token budget is shared between heads (and optionally layers) of a request.
+
+    Mirrors ``BatchedDynamicBudgetTrimKVCache`` of the reference (src/trimkv/cache_utils.py:563-971): segments are
+    ordered ``b*Hkv + h``; ``update`` returns ``flash_attn_kwargs`` with ``head_lens`` / ``cu_seqlens_k`` /
+    ``batch_size`` / ``num_kv_heads`` (:682-687); ``compress`` implements ``alpha``, ``layer_wise_alpha``,
+    ``alpha_threshold`` with ``floor_budget_ratio`` exactly as :697-945 decide which rows survive.  The rows stay
+    in the capacity-strided slabs: the top-k over a request's concatenated scores becomes a keep count per segment
+    (``tkv_group_budget``) followed by the in-place per-segment eviction (``tkv_evict_ex``).  Differences: scores
+    are fp32 (the reference multiplies in the stored dtype, :755), ties go to the lower concatenated index, and
+    K/V are handed out as strided ``[B, Hkv, n_max, D]`` views (``packed(layer)`` builds the reference's
+    ``[sum n, D]`` tensors on demand).
+    """
+
+    _batched = True
+
+    def __init__(self, max_seq_len: int = 20480, _distributed_cache_data: Iterable = None, device: str = "cuda") -> None:
+        if _distributed_cache_data is not None:
+            raise NotImplementedError("Distributed cache data is not supported for " + type(self).__name__)
+        super().__init__(max_seq_len=max_seq_len, device=device)
+        self._rows: List[int] = []   # per layer: total live rows (host copy, refreshed after every eviction)
+        self.batch_size: Optional[int] = None
+        self.num_kv_heads: Optional[int] = None
+
+    # ---- update ---------------------------------------------------------------------------------------
+    def update(self, key_states, value_states, retention_weights, cache_positions, layer_idx, cache_kwargs=None):
+        if key_states is not None:
+            bsz, h, s, _ = key_states.shape
+            if not self._batched:
+                assert bsz == 1, "Batch size greater than 1 is not supported for DynamicBudgetTrimKVCache"
+            if self.batch_size is None:
+                self.batch_size, self.num_kv_heads = bsz, h
+            else:
+                assert bsz == self.batch_size, f"Batch size changed: {self.batch_size} -> {bsz}"
+                assert h == self.num_kv_heads, f"Num KV heads changed: {self.num_kv_heads} -> {h}"
+            while len(self._rows) <= layer_idx:
+                self._rows.append(0)
+            self._rows[layer_idx] += bsz * h * s
+        out = super().update(key_states, value_states, retention_weights, cache_positions, layer_idx, cache_kwargs)
+        return out
+
+    def _attn_kwargs(self, l: int) -> Dict[str, Any]:
+        kw = super()._attn_kwargs(l)
+        if kw:
+            kw = dict(kw, batch_size=self._batch, num_kv_heads=self._hkv)
+        return kw
+
+    # ---- bookkeeping ----------------------------------------------------------------------------------
+    def get_total_cached_tokens(self, num_key_value_heads: Optional[int] = None) -> int:
+        return sum(self._rows)
+
+    def get_cache_length(self, layer_idx: int = 0, batch_idx: int = 0, head_idx: int = 0) -> int:
+        if layer_idx >= len(self):
+            return 0
+        if self._pending[layer_idx] is not None or self._slab is None:
+            return self._cache_len[layer_idx]
+        return int(self._slab["len"][layer_idx][batch_idx * self._hkv + head_idx].item())
+
+    def packed(self, layer_idx: int):
+        """``(K [sum n, D], V, log beta [sum n, 1], positions [sum n, 1])`` in the reference's packed order."""
+        k, v, b, p = self[layer_idx]
+        if self._pending[layer_idx] is not None:
+            d = k.shape[-1]
+            return k.reshape(-1, d), v.reshape(-1, d), b.reshape(-1, 1), p.reshape(-1, 1)
+        lens = self._slab["len"][layer_idx].view(self._batch, self._hkv, 1)
+        mask = torch.arange(k.shape[2], device=k.device).view(1, 1, -1) < lens
+        return k[mask], v[mask], b[mask].unsqueeze(-1), p[mask].unsqueeze(-1)
+
+    def log(self):
+        pos = []
+        for l in range(len(self)):
+            p = self.kv_positions[l].to(torch.int64).cpu()
+            lens = self.head_lens[l].cpu().view(self._batch, self._hkv)
+            for b in range(self._batch):
+                for h in range(self._hkv):
+                    pos.append(p[b, h, : int(lens[b, h])])
+        return {"batch_size": self._batch, "num_kv_heads": self._hkv, "head_wise_kv_positions": pos,
+                "flat_head_lens": torch.cat([self.head_lens[l].view(-1) for l in range(len(self))]).cpu().numpy()}
+
+    def copy_to_device(self, device):
+        raise NotImplementedError("copy_to_device not implemented for " + type(self).__name__)
+
+    # ---- compress -------------------------------------------------------------------------------------
+    def _after_eviction(self, memory_hint: int):
+        """One read-back per eviction: true per-layer maxima and totals; shrinks over-sized slabs."""
+        lens = self._slab["len"].to(torch.int64)
+        mx = lens.max(dim=1).values.cpu().tolist()
+        tot = lens.sum(dim=1).cpu().tolist()
+        for l in range(len(self)):
+            self._cache_len[l], self._rows[l] = int(mx[l]), int(tot[l])
+        want = max(self._cache_len) + memory_hint
+        if self._cap > 2 * want and not torch.cuda.is_current_stream_capturing():
+            self._rehome(want)
+
+    def _budget_and_evict(self, layers, groups_per_layer, inner, n_outer, k_total, threshold, floor_mode, floor_cnt,
+                          buffer_size):
+        s, nseg, nl = self._slab, self._batch * self._hkv, len(self)
+        q_idx = self.get_seq_length() + 1
+        keep = torch.empty(nl, nseg, dtype=torch.int32, device=s["k"].device)
+        keep.copy_(s["len"])  # layers that do not fire keep everything
+        if n_outer > 1:       # one group per request spans all layers
+            ops.group_budget(s["beta"], s["pos"], s["len"], self._cap, groups_per_layer, inner, n_outer, nseg, q_idx,
+                             k_total, keep, threshold, floor_mode, floor_cnt, self._status)
+        else:
+            for l in layers:
+                ops.group_budget(s["beta"][l], s["pos"][l], s["len"][l], self._cap, groups_per_layer, inner, 1, nseg,
+                                 q_idx, k_total, keep[l], threshold, floor_mode, floor_cnt, self._status)
+        kept = None
+        if self.record_kept:
+            kept = torch.full((nl * nseg, self._cap), -1, dtype=torch.int32, device=s["k"].device)
+        ops.evict_ex(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap, q_idx,
+                     max(self._cache_len), keep, 0, kept_idx_out=kept, kept_stride=self._cap, status=self._status)
+        if kept is not None:
+            self.last_kept_idx = kept.view(nl, self._batch, self._hkv, self._cap)
+        self._after_eviction(buffer_size)
+
+    def compress(self, strategy: str = "alpha", memory_size: int = 2048, buffer_size: int = 512,
+                 floor_budget_ratio: float = 0.0, alpha_threshold: float = 0.0, num_layers: Optional[int] = None,
+                 num_key_value_heads: Optional[int] = None, skip_layers: int = 0):
+        base = strategy.replace("layer_wise_", "")
+        if base not in ("alpha", "alpha_threshold"):
+            if base in ("knorm_alpha", "knorm_alpha_threshold"):
+                raise NotImplementedError(f"compress strategy {strategy!r} is not built on the CUDA path")
+            raise ValueError(f"Unknown compression strategy: {strategy}")
+        L = len(self) if num_layers is None else num_layers
+        if L == 0 or self.batch_size is None:
+            return
+        if L != len(self):
+            raise NotImplementedError("compress over a subset of the layers")
+        B, H, M, Bf = self._batch, self._hkv, memory_size, buffer_size
+        thr = "threshold" in strategy
+        total = sum(self._rows)
+        import math
+        log_thr = (math.log(alpha_threshold) if alpha_threshold > 0 else float("-inf")) if thr else None
+        if self._batched:
+            # src/trimkv/cache_utils.py:714-738
+            if total <= B * H * (M + Bf) * L and not thr:
+                return
+            if "layer_wise" in strategy:
+                fire = [l for l in range(L) if self._rows[l] > B * H * (M + Bf)]
+                if not fire:
+                    return
+                self._ensure_slab()
+                k = M * H if floor_budget_ratio <= 0 else int(M * H * (1 - floor_budget_ratio))
+                self._budget_and_evict(fire, B, H, 1, k, None, 2 if floor_budget_ratio > 0 else 0,
+                                       int(M * floor_budget_ratio), Bf)
+            else:
+                if total // B <= L * H * (M + Bf) and not thr:
+                    return
+                self._ensure_slab()
+                self._budget_and_evict(range(L), B, H, L, L * H * M, log_thr, 0, 0, Bf)
+        else:
+            # src/trimkv/cache_utils.py:346-369, 418-536 (batch size 1)
+            if "layer_wise" in strategy:
+                fire = [l for l in range(L) if H * (M + Bf) < self._rows[l]]
+                if not fire:
+                    return
+                self._ensure_slab()
+                self._budget_and_evict(fire, 1, H, 1, H * M, None, 0, 0, Bf)
+            else:
+                if L * H * (M + Bf) > total and not thr:
+                    return
+                self._ensure_slab()
+                if floor_budget_ratio == 0:
+                    self._budget_and_evict(range(L), 1, H, L, L * H * M, log_thr, 0, 0, Bf)
+                else:
+                    assert not thr, "Thresholding strategy is not compatible with floor_budget_ratio > 0"
+                    self._budget_and_evict(range(L), 1, H, L, int(L * H * M * (1 - floor_budget_ratio)), None, 1,
+                                           int(M * floor_budget_ratio), Bf)
+
+    def _ensure_slab(self):
+        """Moves a pending prompt into the slabs without evicting (the shared budget is applied afterwards)."""
+        if any(p is not None for p in self._pending):
+            self._hint_m = self._hint_b = None
+            self._materialise(extra=64)
+
+
+class DynamicBudgetTrimKVCache(BatchedDynamicBudgetTrimKVCache):
+    """Batch-size-1 flat cache with a budget shared across heads / layers.
+
+    Mirrors ``DynamicBudgetTrimKVCache`` (src/trimkv/cache_utils.py:226-560): same storage and kernels as the batched
+    class, with the reference's batch-1 trigger rules and its per-head floor arithmetic (:486-536).
+    """
+
+    _batched = False
+
+    def get_cache_length(self, layer_idx: int = 0, head_idx: int = 0) -> int:
+        return super().get_cache_length(layer_idx, 0, head_idx)

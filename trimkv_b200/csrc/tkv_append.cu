@@ -156,3 +156,68 @@ extern "C" int tkv_append(void* k_cache, void* v_cache, float* beta_cache, int32
   append_bump<<<(p.nseg + 255) / 256, 256, 0, st>>>(seg_len, cu_seqlens, p.nseg, s_new, cap);
   return check_launch("tkv_append(bump)");
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Functional append on the reference's packed layout: out = per-head concatenation of old and new rows.
+// Same semantics as update_flatten_view_triton (src/trimkv/triton/db_cache_utils.py:86-186: output segment h
+// starts at cu[h] + h*S, old rows first, then the S new rows), in one launch, without the host sync for the
+// longest head: work is split over OUTPUT rows, and each row finds its head by binary search in the shifted
+// prefix sums, so heads of any length balance.
+namespace tkv {
+
+constexpr int kPackedRows = 64;
+
+template <typename V>
+__global__ void __launch_bounds__(256) flat_append_packed_kernel(const char* cache, const char* state, const int32_t* cu,
+                                                                 char* out, int heads, int s_new, int64_t row_bytes,
+                                                                 int64_t out_rows) {
+  __shared__ int64_t s_src[kPackedRows];   // source row; >= 0: row of cache, < 0: -(row of state) - 1
+  const int64_t r0 = (int64_t)blockIdx.x * kPackedRows;
+  const int rows = (int)min((int64_t)kPackedRows, out_rows - r0);
+  if (threadIdx.x < rows) {
+    const int64_t r = r0 + threadIdx.x;
+    // largest h with cu[h] + h*s_new <= r
+    int lo = 0, hi = heads - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if ((int64_t)cu[mid] + (int64_t)mid * s_new <= r) lo = mid; else hi = mid - 1;
+    }
+    const int64_t off = r - ((int64_t)cu[lo] + (int64_t)lo * s_new);
+    const int64_t old_len = (int64_t)cu[lo + 1] - cu[lo];
+    s_src[threadIdx.x] = off < old_len ? (int64_t)cu[lo] + off : -((int64_t)lo * s_new + (off - old_len)) - 1;
+  }
+  __syncthreads();
+  const int vecs = (int)(row_bytes / sizeof(V));
+  for (int i = threadIdx.x; i < rows * vecs; i += blockDim.x) {
+    const int r = i / vecs, c = i - r * vecs;
+    const int64_t src = s_src[r];
+    const char* sp = src >= 0 ? cache + src * row_bytes : state + (-src - 1) * row_bytes;
+    *reinterpret_cast<V*>(out + (r0 + r) * row_bytes + (int64_t)c * sizeof(V)) =
+        *reinterpret_cast<const V*>(sp + (int64_t)c * sizeof(V));
+  }
+}
+
+}  // namespace tkv
+
+extern "C" int tkv_flat_append_packed(const void* cache, const void* state, const int32_t* cu_headlens, void* out,
+                                      int heads, int s_new, int64_t origin_rows, int64_t row_bytes,
+                                      tkv_stream_t stream) {
+  using namespace tkv;
+  if (!state || !cu_headlens || !out || (origin_rows > 0 && !cache))
+    return fail(TKV_ERR_ARG, "tkv_flat_append_packed: NULL pointer argument");
+  if (heads <= 0 || s_new < 0 || origin_rows < 0 || row_bytes <= 0)
+    return fail(TKV_ERR_ARG, "tkv_flat_append_packed: bad sizes heads=%d s_new=%d rows=%lld row_bytes=%lld", heads, s_new,
+                (long long)origin_rows, (long long)row_bytes);
+  const int64_t out_rows = origin_rows + (int64_t)heads * s_new;
+  if (out_rows == 0) return TKV_OK;
+  const unsigned grid = (unsigned)((out_rows + kPackedRows - 1) / kPackedRows);
+  const uintptr_t bits = (uintptr_t)cache | (uintptr_t)state | (uintptr_t)out | (uintptr_t)row_bytes;
+  cudaStream_t st = (cudaStream_t)stream;
+  const char* c = (const char*)cache; const char* s = (const char*)state; char* o = (char*)out;
+  if ((bits & 15) == 0) flat_append_packed_kernel<uint4><<<grid, 256, 0, st>>>(c, s, cu_headlens, o, heads, s_new, row_bytes, out_rows);
+  else if ((bits & 7) == 0) flat_append_packed_kernel<uint2><<<grid, 256, 0, st>>>(c, s, cu_headlens, o, heads, s_new, row_bytes, out_rows);
+  else if ((bits & 3) == 0) flat_append_packed_kernel<uint32_t><<<grid, 256, 0, st>>>(c, s, cu_headlens, o, heads, s_new, row_bytes, out_rows);
+  else if ((bits & 1) == 0) flat_append_packed_kernel<uint16_t><<<grid, 256, 0, st>>>(c, s, cu_headlens, o, heads, s_new, row_bytes, out_rows);
+  else flat_append_packed_kernel<uint8_t><<<grid, 256, 0, st>>>(c, s, cu_headlens, o, heads, s_new, row_bytes, out_rows);
+  return check_launch("tkv_flat_append_packed");
+}

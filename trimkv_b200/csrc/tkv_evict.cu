@@ -109,6 +109,8 @@ struct EvictParams {
   int32_t* seg_len;
   int nseg; int64_t cap; int row_vecs; int64_t q_idx;
   int m, trigger_len, max_len;
+  const int32_t* keep_cnt;   // per-segment number of rows to keep (NULL: m for every segment at or above trigger_len)
+  int protect_last;          // the newest `protect_last` rows always score +inf (sliding window)
   int32_t* kept_idx_out; int32_t* status;
 };
 
@@ -117,21 +119,27 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
   __shared__ SelectScratch sc;
   const int seg = blockIdx.x;
   const int n = p.seg_len[seg];
-  if (n < p.trigger_len || n <= p.m) return;
+  const int m = p.keep_cnt != nullptr ? p.keep_cnt[seg] : p.m;
+  if (p.keep_cnt == nullptr ? (n < p.trigger_len || n <= m) : (m >= n || m < 0)) return;
   if (n > p.max_len || n > p.cap) {
     if (threadIdx.x == 0) report(p.status, TKV_DEV_LEN_BOUND);
     return;
   }
+  if (m == 0) {
+    if (threadIdx.x == 0) p.seg_len[seg] = 0;
+    return;
+  }
   const int64_t row0 = (int64_t)seg * p.cap;
   for (int i = threadIdx.x; i < n; i += kEvictThreads)
-    keys[i] = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+    keys[i] = i >= n - p.protect_last ? score_key(INFINITY)
+                                      : score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
   __syncthreads();
   uint32_t thresh; int n_eq_keep;
-  radix_select_mth(keys, n, p.m, &sc, &thresh, &n_eq_keep);
+  radix_select_mth(keys, n, m, &sc, &thresh, &n_eq_keep);
   const int j0 = build_kept_list(keys, n, thresh, n_eq_keep, &sc);
   const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
   if (p.kept_idx_out != nullptr)
-    for (int j = threadIdx.x; j < p.m; j += kEvictThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
+    for (int j = threadIdx.x; j < m; j += kEvictThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
 
   // Stable in-place compaction of rows j0..m (rows before the first evicted one stay where they are).
   const int nvec = 2 * p.row_vecs;                       // K vectors then V vectors of one token
@@ -140,8 +148,8 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
   char* kbase = p.k + row0 * row_bytes;
   char* vbase = p.v + row0 * row_bytes;
 #pragma unroll 1
-  for (int jb = j0; jb < p.m; jb += tile_rows) {
-    const int rows = min(tile_rows, p.m - jb);
+  for (int jb = j0; jb < m; jb += tile_rows) {
+    const int rows = min(tile_rows, m - jb);
     const int nv = rows * nvec;
     uint4 reg[kEvictUnroll];
 #pragma unroll
@@ -177,7 +185,7 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
       p.pos[row0 + jb + threadIdx.x] = ps;
     }
   }
-  if (threadIdx.x == 0) p.seg_len[seg] = p.m;
+  if (threadIdx.x == 0) p.seg_len[seg] = m;
 }
 
 struct SelectParams {
@@ -305,17 +313,17 @@ extern "C" int tkv_rebuild_cu_seqlens(const int32_t* seg_len, int32_t* cu_seqlen
   return tkv::launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
 }
 
-extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
-                         int32_t* seg_len, int32_t* cu_seqlens, int group,
-                         int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
-                         int memory_size, int trigger_len, int max_len,
-                         int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                      int32_t* seg_len, int32_t* cu_seqlens, int group,
+                      int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                      int memory_size, int trigger_len, int max_len, const int32_t* keep_cnt, int protect_last,
+                      int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   const int es = elem_size(kv_dtype);
   if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
   if (!k_cache || !v_cache || !beta_cache || !pos_cache || !seg_len)
     return fail(TKV_ERR_ARG, "tkv_evict: NULL pointer argument");
-  if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0)
+  if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0 || protect_last < 0)
     return fail(TKV_ERR_ARG, "tkv_evict: bad sizes nseg=%d cap=%lld head_dim=%d M=%d max_len=%d", nseg,
                 (long long)cap, head_dim, memory_size, max_len);
   if (max_len > kMaxSelectLen)
@@ -329,6 +337,7 @@ extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_
   p.k = (char*)k_cache; p.v = (char*)v_cache; p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len;
   p.nseg = nseg; p.cap = cap; p.row_vecs = (int)(row_bytes / 16); p.q_idx = q_idx;
   p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
+  p.keep_cnt = keep_cnt; p.protect_last = protect_last;
   p.kept_idx_out = kept_idx_out; p.status = status;
   const size_t smem = (size_t)max_len * 4;
   int rc = set_smem(evict_inplace_kernel, smem, "tkv_evict");
@@ -337,6 +346,27 @@ extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_
   rc = check_launch("tkv_evict");
   if (rc != TKV_OK) return rc;
   return launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
+}
+
+extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                         int32_t* seg_len, int32_t* cu_seqlens, int group,
+                         int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                         int memory_size, int trigger_len, int max_len,
+                         int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+  return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
+                    q_idx, memory_size, trigger_len, max_len, nullptr, 0, kept_idx_out, status, stream);
+}
+
+extern "C" int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                            int32_t* seg_len, int32_t* cu_seqlens, int group,
+                            int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                            int memory_size, int trigger_len, int max_len,
+                            const int32_t* keep_cnt, int protect_last, int kept_stride,
+                            int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+  // kept_stride doubles as the row stride of kept_idx_out when keep counts vary per segment.
+  return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
+                    q_idx, keep_cnt != nullptr ? (kept_stride > 0 ? kept_stride : 1) : memory_size, trigger_len, max_len,
+                    keep_cnt, protect_last, kept_idx_out, status, stream);
 }
 
 extern "C" int tkv_evict_select(const float* beta, int64_t beta_stride, const int32_t* pos, int64_t pos_stride,
@@ -400,4 +430,184 @@ extern "C" int tkv_compact(void* k_dst, void* v_dst, float* beta_dst, int32_t* p
   int rc = check_launch("tkv_compact");
   if (rc != TKV_OK) return rc;
   return launch_rebuild(seg_len, cu_seqlens, (int)nseg, group, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Budget sharing: how many rows each segment keeps when a token budget is shared by a group of segments.
+//
+// Replaces the global / layer-wise top-k of the reference's flat caches (src/trimkv/cache_utils.py:371-416
+// _compress_layer, :418-536 _compress_all_layers, :740-834 _compress_layer_batched, :836-945
+// _compress_all_layers_batched): there the scores of a whole layer (or of all layers) of one request are
+// concatenated, torch.topk picks the budget, and Python loops with .item() rebuild the per-head lengths.
+// Here one CTA per group streams the scores of its segments, radix-selects the group's threshold, then
+// counts per segment how many rows clear it (ties go to the lower concatenated index, i.e. to earlier
+// segments first).  Keeping a group's top-k is the same as keeping, in every segment, its own top-c rows for
+// these counts c, which is what tkv_evict_ex then does in place.
+namespace tkv {
+
+constexpr int kBudgetThreads = 1024;
+constexpr int kBudgetMaxSegs = 2048;
+
+struct BudgetParams {
+  const float* beta; const int32_t* pos; const int32_t* seg_len; int64_t cap;
+  int inner, n_outer; int64_t outer_stride;     // group g = segments {g*inner + o*outer_stride + i}
+  int64_t q_idx; int64_t k_total;
+  int use_threshold; float threshold;           // keep score >= threshold instead of the k_total best
+  int floor_mode, floor_cnt;                    // 0: none, 1: c = min(n, s' + floor) with the reference's boundary
+                                                // attribution for s', 2: c = max(s, min(floor, n))
+  int32_t* keep_cnt; int32_t* status;
+};
+
+__global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetParams p) {
+  __shared__ int s_len[kBudgetMaxSegs];
+  __shared__ int s_gt[kBudgetMaxSegs];
+  __shared__ int s_eq[kBudgetMaxSegs];
+  __shared__ int hist[256];
+  __shared__ int warp_sums[kBudgetThreads / 32 + 1];
+  __shared__ int sel_digit, sel_k;
+  __shared__ long long s_total;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int nsegs = p.inner * p.n_outer;
+  const int64_t base = (int64_t)blockIdx.x * p.inner;
+  auto seg_of = [&](int j) { return base + (int64_t)(j / p.inner) * p.outer_stride + (j % p.inner); };
+  if (tid == 0) s_total = 0;
+  __syncthreads();
+  for (int j = tid; j < nsegs; j += kBudgetThreads) {
+    const int n = max(p.seg_len[seg_of(j)], 0);
+    s_len[j] = n; s_gt[j] = 0; s_eq[j] = 0;
+    atomicAdd((unsigned long long*)&s_total, (unsigned long long)n);
+  }
+  __syncthreads();
+  const long long total = s_total;
+  uint32_t thresh = 0; long long n_eq_keep = 0;
+  bool keep_all = false;
+  if (p.use_threshold) {
+    thresh = score_key(p.threshold);
+    n_eq_keep = total;  // every row equal to the threshold is kept
+  } else if (p.k_total >= total) {
+    keep_all = true;
+  } else if (p.k_total <= 0) {
+    thresh = 0xFFFFFFFFu; n_eq_keep = 0;
+  } else {
+    // 4-pass radix select of the k_total-th largest key over all rows of the group.
+    uint32_t prefix = 0, decided = 0;
+    long long k = p.k_total;
+#pragma unroll 1
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      if (tid < 256) hist[tid] = 0;
+      __syncthreads();
+      for (int j = 0; j < nsegs; ++j) {
+        const int n = s_len[j];
+        const int64_t row0 = seg_of(j) * p.cap;
+        const int n_round = (n + kBudgetThreads - 1) / kBudgetThreads * kBudgetThreads;
+        for (int i = tid; i < n_round; i += kBudgetThreads) {
+          bool valid = i < n;
+          uint32_t key = 0;
+          if (valid) {
+            key = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+            valid = (key & decided) == prefix;
+          }
+          const int digit = valid ? (int)((key >> shift) & 255u) : 256 + lane;
+          const unsigned peers = __match_any_sync(0xffffffffu, digit);
+          if (valid && lane == __ffs(peers) - 1) atomicAdd(&hist[digit], __popc(peers));
+        }
+      }
+      __syncthreads();
+      // bins from the top: thread t (< 256) looks at bin 255 - t
+      const int bin = 255 - tid;
+      const int c = tid < 256 ? hist[bin] : 0;
+      int tot;
+      const int above = block_exclusive_scan<kBudgetThreads>(c, warp_sums, &tot);
+      if (tid < 256 && above < k && k <= (long long)above + c) { sel_digit = bin; sel_k = (int)(k - above); }
+      __syncthreads();
+      prefix |= (uint32_t)sel_digit << shift;
+      decided |= 255u << shift;
+      k = sel_k;
+      __syncthreads();
+    }
+    thresh = prefix; n_eq_keep = k;
+  }
+  if (!keep_all) {
+    // Per segment: rows above the threshold and rows equal to it.
+    for (int j = 0; j < nsegs; ++j) {
+      const int n = s_len[j];
+      const int64_t row0 = seg_of(j) * p.cap;
+      const int n_round = (n + 31) / 32 * 32;
+      for (int i = tid; i < n_round; i += kBudgetThreads) {
+        uint32_t key = 0;
+        const bool valid = i < n;
+        if (valid) key = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+        const unsigned gt = __ballot_sync(0xffffffffu, valid && key > thresh);
+        const unsigned eq = __ballot_sync(0xffffffffu, valid && key == thresh);
+        if (lane == 0) {
+          if (gt) atomicAdd(&s_gt[j], __popc(gt));
+          if (eq) atomicAdd(&s_eq[j], __popc(eq));
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // Ties are granted in concatenated order; then the per-head floor is applied.  Few segments: one thread.
+  if (tid == 0) {
+    long long eq_before = 0;
+    for (int j = 0; j < nsegs; ++j) {
+      const int n = s_len[j];
+      int s = n;
+      long long quota = 0;
+      if (!keep_all) {
+        quota = n_eq_keep - eq_before;
+        quota = quota < 0 ? 0 : (quota > s_eq[j] ? s_eq[j] : quota);
+        s = s_gt[j] + (int)quota;
+        eq_before += s_eq[j];
+      }
+      if (p.floor_mode == 1) {
+        // Is the segment's first row among the kept ones?  (needed for the attribution below)
+        int first = 0;
+        if (n > 0) {
+          const int64_t row0 = seg_of(j) * p.cap;
+          const uint32_t key0 = score_key(retention_score(p.beta[row0], p.pos[row0], p.q_idx));
+          first = keep_all || key0 > thresh || (key0 == thresh && quota > 0);
+        }
+        s_eq[j] = first;
+      }
+      s_gt[j] = s;
+    }
+    for (int j = 0; j < nsegs; ++j) {
+      const int n = s_len[j];
+      const int s = s_gt[j];
+      int c = s;
+      if (p.floor_mode == 1) {
+        // src/trimkv/cache_utils.py:495-499 attributes a selected flat index that equals a head boundary (the
+        // first row of the next head) to the previous head, then adds the floor; kept as is for parity.
+        const int attributed = s - (j > 0 ? s_eq[j] : 0) + (j + 1 < nsegs ? s_eq[j + 1] : 0);
+        c = min(n, attributed + p.floor_cnt);
+      } else if (p.floor_mode == 2) {
+        c = max(s, min(p.floor_cnt, n));
+      }
+      p.keep_cnt[seg_of(j)] = c;
+    }
+  }
+}
+
+}  // namespace tkv
+
+extern "C" int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const int32_t* seg_len, int64_t cap,
+                                int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
+                                int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
+                                int32_t* keep_cnt, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!beta_cache || !pos_cache || !seg_len || !keep_cnt) return fail(TKV_ERR_ARG, "tkv_group_budget: NULL pointer argument");
+  if (groups < 0 || inner <= 0 || n_outer <= 0 || cap <= 0 || floor_mode < 0 || floor_mode > 2 || floor_cnt < 0)
+    return fail(TKV_ERR_ARG, "tkv_group_budget: bad sizes groups=%d inner=%d n_outer=%d", groups, inner, n_outer);
+  if ((int64_t)inner * n_outer > kBudgetMaxSegs)
+    return fail(TKV_ERR_UNSUPPORTED, "tkv_group_budget: %lld segments per group (limit %d)", (long long)inner * n_outer,
+                kBudgetMaxSegs);
+  if (groups == 0) return TKV_OK;
+  BudgetParams p;
+  p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len; p.cap = cap;
+  p.inner = inner; p.n_outer = n_outer; p.outer_stride = outer_stride; p.q_idx = q_idx; p.k_total = k_total;
+  p.use_threshold = use_threshold; p.threshold = threshold; p.floor_mode = floor_mode; p.floor_cnt = floor_cnt;
+  p.keep_cnt = keep_cnt; p.status = status;
+  group_budget_kernel<<<groups, kBudgetThreads, 0, (cudaStream_t)stream>>>(p);
+  return check_launch("tkv_group_budget");
 }

@@ -172,3 +172,60 @@ def silu_mul(gate_up, out) -> None:
                             _stream(gate_up))
     check(rc, "tkv_silu_mul")
     _count(1)
+
+
+def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
+             q_idx: int, max_len: int, keep_cnt, protect_last: int = 0, memory_size: int = 1, trigger_len: int = 0,
+             kept_idx_out=None, kept_stride: int = 0, status=None) -> None:
+    """In-place eviction with a keep count per segment (``keep_cnt`` int32 ``[nseg]``) and/or a protected tail."""
+    d = k_cache.shape[-1]
+    rc = lib().tkv_evict_ex(
+        k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
+        seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
+        memory_size, trigger_len, max_len, _ptr(keep_cnt), protect_last, kept_stride, _ptr(kept_idx_out),
+        _ptr(status), _stream(k_cache))
+    check(rc, "tkv_evict_ex")
+    _count(1 if cu_seqlens is None else 2)
+
+
+def group_budget(beta_cache, pos_cache, seg_len, cap: int, groups: int, inner: int, n_outer: int, outer_stride: int,
+                 q_idx: int, k_total: int, keep_cnt, threshold=None, floor_mode: int = 0, floor_cnt: int = 0,
+                 status=None) -> None:
+    """Per-segment keep counts when ``k_total`` rows (or all rows scoring >= ``threshold``) are kept per group."""
+    rc = lib().tkv_group_budget(
+        beta_cache.data_ptr(), pos_cache.data_ptr(), seg_len.data_ptr(), cap, groups, inner, n_outer, outer_stride,
+        q_idx, k_total, 0 if threshold is None else 1, 0.0 if threshold is None else float(threshold),
+        floor_mode, floor_cnt, keep_cnt.data_ptr(), _ptr(status), _stream(beta_cache))
+    check(rc, "tkv_group_budget")
+    _count(1)
+
+
+def update_flatten_view(cache: torch.Tensor, state: torch.Tensor, headlens: torch.Tensor,
+                        cu_headlens: torch.Tensor) -> torch.Tensor:
+    """Functional packed append with the contract of the reference's ``update_flatten_view_triton``
+    (src/trimkv/triton/db_cache_utils.py:86-186): ``cache [origin_len, D]`` + ``state [1, H, S, D]`` ->
+    ``out [origin_len + H*S, D]``; same argument checks, no host synchronisation."""
+    assert cache.is_cuda and state.is_cuda, "Tensors must be on CUDA device"
+    assert headlens.is_cuda and cu_headlens.is_cuda, "Index tensors must be on CUDA"
+    assert headlens.dtype == torch.int32, "headlens must be int32"
+    assert cu_headlens.dtype == torch.int32, "cu_headlens must be int32"
+    assert cache.dtype == state.dtype, "cache/state dtypes must match"
+    assert cache.is_contiguous(), "cache must be contiguous [origin_len, D]"
+    assert headlens.is_contiguous() and cu_headlens.is_contiguous(), "index tensors must be contiguous"
+    assert state.ndim == 4, "state must be [B, H, state_len, D]"
+    b, h, s, d_state = state.shape
+    assert b == 1, "This kernel currently assumes B == 1"
+    origin_len, d = cache.shape
+    assert d == d_state, "cache and state last dim (D) must match"
+    assert headlens.shape[0] == h, "headlens must be length H"
+    assert cu_headlens.numel() == h + 1, "cu_headlens must be length H+1"
+    assert state.is_contiguous(), "state must be contiguous [B, H, state_len, D]"
+    out = torch.empty((origin_len + h * s, d), dtype=cache.dtype, device=cache.device)
+    rc = lib().tkv_flat_append_packed(cache.data_ptr(), state.data_ptr(), cu_headlens.data_ptr(), out.data_ptr(),
+                                      h, s, origin_len, d * cache.element_size(), _stream(cache))
+    check(rc, "tkv_flat_append_packed")
+    _count(1)
+    return out
+
+
+update_flatten_view_triton = update_flatten_view  # the reference's name for the same operation
