@@ -253,6 +253,30 @@ def run_micro(args):
         alg = int(lens.long().sum()) * 4 * D + batch * hq * D * 4
         res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
                          "mean_len": float(lens.float().mean()), "buffers": nbuf, "shape": args.attn_shape}
+    if args.micro in ("evict", "append") and not args.no_cpu_baseline:
+        # The reference's eager ops for the same phase on the host cores, on a sample of the segments
+        # (src/trimkv/cache_utils.py:104-108 for append, :172-198 for eviction), same algorithmic-byte formula.
+        ns, n = min(64, nseg), M + Bf
+        gc = torch.Generator().manual_seed(0)
+        kc = torch.randn(1, ns, n, D, generator=gc).bfloat16(); vc = torch.randn(1, ns, n, D, generator=gc).bfloat16()
+        bc = torch.nn.functional.logsigmoid(torch.randn(1, ns, n, generator=gc) * 1.5 + 3).bfloat16()
+        pc = torch.sort(torch.rand(1, ns, 4 * M, generator=gc).argsort(-1)[..., :n], -1)[0]
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or time.perf_counter() - t0 < 3.0:
+            if args.micro == "evict":
+                sc = bc.to(torch.float32) * (4 * M + 1 - pc)
+                idx, _ = torch.sort(torch.topk(sc, M, dim=-1).indices, dim=-1)
+                _ = (kc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)), vc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)),
+                     bc.gather(-1, idx), pc.gather(-1, idx))
+            else:
+                _ = (torch.cat([kc, kc[:, :, :1]], dim=-2), torch.cat([vc, vc[:, :, :1]], dim=-2),
+                     torch.cat([bc, bc[:, :, :1]], dim=-1), torch.cat([pc, pc[:, :, :1]], dim=-1))
+            reps += 1
+        sec = (time.perf_counter() - t0) / reps
+        cpu_alg = ns * (8 * n + 1032 * M) if args.micro == "evict" else ns * 2 * 520
+        res["cpu_baseline"] = {"value": cpu_alg / sec / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"{ns} of {nseg} segments with n = M+B = {n}, eager torch ops of the reference "
+                                         f"({'score/topk/sort/4 gathers' if args.micro == 'evict' else '4 torch.cat'}), {reps} repetitions"}
     ms = sorted(a.elapsed_time(b) for a, b in times)
     avg = sum(ms) / len(ms)
     res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
@@ -308,7 +332,7 @@ def main():
     B, P, M, Bf = wl["batch"], wl["prompt"], wl["memory_size"], wl["buffer_size"]
     gen = torch.Generator().manual_seed(1000 + rank)
     prompt = torch.randint(0, cfg.vocab_size, (B, P), generator=gen).pin_memory()
-    cache = TrimKVCache(device=dev, memory_size=M, buffer_size=Bf)
+    cache = TrimKVCache(device=dev, memory_size=M, buffer_size=Bf, num_layers=cfg.num_hidden_layers)
     with torch.inference_mode():
         out = model(input_ids=prompt.to(dev, non_blocking=True), past_key_values=cache, logits_to_keep=1)
         first = out.logits[:, -1].argmax(-1, keepdim=True)

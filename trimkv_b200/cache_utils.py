@@ -55,6 +55,7 @@ class TrimKVCache:
         device: str = "cuda",
         memory_size: Optional[int] = None,
         buffer_size: Optional[int] = None,
+        num_layers: Optional[int] = None,
     ) -> None:
         # Same first three arguments as the reference (cache_utils.py:12-33).  memory_size/buffer_size are
         # optional hints: when given, the slabs are sized M+B at the first decode step even if compress()
@@ -69,6 +70,10 @@ class TrimKVCache:
         self.block_mask = None
         self.sliding_window_size = 0
         self._hint_m, self._hint_b = memory_size, buffer_size
+        # With memory_size, buffer_size and num_layers all known up front, each layer's prompt K/V is reduced to its
+        # top-M rows as soon as that layer's update() is called (the caller still attends over its own dense tensors),
+        # instead of keeping the prompt K/V of every layer alive until compress().  Same survivors either way.
+        self._hint_layers = num_layers
 
         self._pending: List[Optional[Tuple[torch.Tensor, ...]]] = []  # per layer: dense prompt (K, V, beta, pos)
         self._cache_len: List[int] = []                               # per layer: live rows per segment
@@ -175,7 +180,17 @@ class TrimKVCache:
                 self._pending.append(None)
                 self._cache_len.append(0)
                 self.n_seen_tokens.append(0)
-            if self._cache_len[layer_idx] == 0 and self._slab is None:
+            if self._cache_len[layer_idx] == 0 and self._eager_handoff(layer_idx):
+                if cache_positions.dim() == 1:
+                    cache_positions = cache_positions[None, None, :].expand_as(retention_weights)
+                self._batch, self._hkv, self._dim = bsz, num_heads, dim
+                self._pending[layer_idx] = (key_states, value_states, retention_weights, cache_positions)
+                self._cache_len[layer_idx] = seq_len
+                self.n_seen_tokens[layer_idx] = seq_len
+                self._materialise(only_layer=layer_idx)
+                # the prompt pass attends over the caller's dense tensors, exactly as with the deferred hand-off
+                return key_states, value_states, retention_weights, cache_positions, {}
+            elif self._cache_len[layer_idx] == 0 and self._slab is None:
                 # First tokens of this layer: keep the caller's tensors, as the reference does (:90-94).
                 if cache_positions.dim() == 1:
                     cache_positions = cache_positions[None, None, :].expand_as(retention_weights)
@@ -224,6 +239,11 @@ class TrimKVCache:
         self.n_seen_tokens[layer_idx] += 1
         return self.key_cache[layer_idx], self.value_cache[layer_idx], self._attn_kwargs(layer_idx)
 
+    def _eager_handoff(self, layer_idx: int) -> bool:
+        return (type(self) is TrimKVCache and self._hint_m is not None and self._hint_b is not None
+                and self._hint_layers is not None and layer_idx < self._hint_layers and not self.sliding_window_size
+                and all(p is None for p in self._pending))
+
     def _attn_kwargs(self, l: int) -> Dict[str, Any]:
         if self._slab is None or self._pending[l] is not None:
             return {}
@@ -232,7 +252,8 @@ class TrimKVCache:
 
     # ------------------------------------------------------------------ storage
     def _alloc(self, cap: int):
-        dev, nl, nseg = self._any_pending_or_slab_device(), len(self), self._batch * self._hkv
+        dev, nseg = self._any_pending_or_slab_device(), self._batch * self._hkv
+        nl = max(len(self), self._hint_layers or 0)
         dt = self._kv_dtype
         slab = {
             "k": torch.empty(nl, nseg * cap, self._dim, dtype=dt, device=dev),
@@ -249,8 +270,9 @@ class TrimKVCache:
             return self._slab["k"].device
         return next(p[0].device for p in self._pending if p is not None)
 
-    def _materialise(self, extra: int = 0, memory_size: Optional[int] = None, buffer_size: Optional[int] = None):
-        """Moves the dense prompt tensors of every layer into the slabs (the prefill hand-off)."""
+    def _materialise(self, extra: int = 0, memory_size: Optional[int] = None, buffer_size: Optional[int] = None,
+                     only_layer: Optional[int] = None):
+        """Moves the dense prompt tensors of every layer (or of ``only_layer``) into the slabs (the prefill hand-off)."""
         pend = [p for p in self._pending if p is not None]
         if not pend:
             return
