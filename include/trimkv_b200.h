@@ -230,6 +230,9 @@ int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
  * log beta = logsigmoid(gate_w2 . SiLU(gate hidden) + gate_bias) and pos to every segment
  * (seg_len += 1, cu_seqlens[i] += i), rounding to the model dtype after every step the eager
  * PyTorch sequence rounds at.
+ * in_splits / in_bias (also on tkv_add_rmsnorm's delta and tkv_silu_mul's gate_up): 0 = the input is in the model
+ * dtype; s > 0 = the input is the fp32 output of tkv_skinny_gemm, s partial sums [s][rows][cols] that the kernel
+ * adds in order, plus in_bias (model dtype, [cols], nullable), rounded once to the model dtype.
  */
 int tkv_decode_prep(const void* qkvg, int64_t row_stride,
                     const void* q_norm_w, const void* k_norm_w, float eps,
@@ -239,6 +242,7 @@ int tkv_decode_prep(const void* qkvg, int64_t row_stride,
                     void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
                     int32_t* seg_len, int32_t* cu_seqlens, int64_t cap,
                     int batch, int hq, int hkv, int head_dim, int dtype,
+                    int in_splits, const void* in_bias,
                     int32_t* status, tkv_stream_t stream);
 
 /*
@@ -247,13 +251,26 @@ int tkv_decode_prep(const void* qkvg, int64_t row_stride,
  * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:414-437).  cols % 8 == 0; out may not alias residual.
  */
 int tkv_add_rmsnorm(void* residual, const void* delta, const void* weight, void* out,
-                    int rows, int cols, float eps, int dtype, tkv_stream_t stream);
+                    int rows, int cols, float eps, int dtype, int in_splits, const void* in_bias,
+                    tkv_stream_t stream);
 
 /*
  * out[r, j] = SiLU(gate_up[r, j]) * gate_up[r, inter + j]: the activation of Qwen3MLP over the output of one
  * GEMM with the concatenated gate/up weights (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:436).
  */
-int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, tkv_stream_t stream);
+int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, int in_splits,
+                 const void* in_bias, tkv_stream_t stream);
+
+/*
+ * Weight-streaming GEMM of the decode step on tcgen05 + TMA: partial[s][m][n] (fp32) such that
+ * sum_s partial[s] = x[m, k] . w[n, k]^T, for m <= 32 rows, k a multiple of 64, x/w bf16 or f16, row-major.
+ * Replaces the nn.Linear calls on one token per request (q/k/v/gate, o_proj, gate/up, down:
+ * src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:328-333,383,436).  s = tkv_skinny_gemm_splits(m, n, k) (0 if the
+ * shape is unsupported); partial must hold s*m*n floats.  The consumers above add the partials.
+ */
+int tkv_skinny_gemm_splits(int m, int n, int k);
+int tkv_skinny_gemm(const void* x, const void* w, float* partial, int m, int n, int k, int dtype,
+                    int32_t* status, tkv_stream_t stream);
 
 /* Blocks until `stream` is idle, then returns *status (a TKV_DEV_* code) and clears it. */
 int tkv_read_status(int32_t* status, tkv_stream_t stream);

@@ -268,3 +268,44 @@ def test_decode_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, d, cap, lens_
                     d ** -0.5, max_len, status)
     # (a different split kernel may serve this layout, so compare with the oracle rather than bit for bit)
     assert np.max(np.abs(out2.float().cpu().numpy() - want)) <= tol
+
+
+# ---------------------------------------------------------------- weight-streaming GEMM and its consumers
+@pytest.mark.parametrize("m,n,k", [(32, 4224, 2048), (32, 2048, 2048), (32, 12288, 2048), (32, 2048, 6144),
+                                   (5, 300, 128), (1, 128, 64), (17, 1000, 4096)])
+def test_skinny_gemm_partials_sum_to_the_product(ops, m, n, k):
+    gen = torch.Generator().manual_seed(m * 1000 + n)
+    x = torch.randn(m, k, generator=gen).bfloat16().to(DEV)
+    w = (torch.randn(n, k, generator=gen) * 0.05).bfloat16().to(DEV)
+    splits = ops.skinny_gemm_splits(m, n, k)
+    assert splits >= 1
+    part = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    status = ops.new_status(DEV)
+    assert ops.skinny_gemm(x, w, part, status) == splits
+    assert ops.read_status(status) == 0
+    got = part.sum(0)
+    want = x.float() @ w.float().t()
+    assert torch.isfinite(got).all()
+    assert float((got - want).abs().max()) <= 1e-3 * max(1.0, float(want.abs().max()))
+
+
+def test_consumers_accept_gemm_partials(ops):
+    """add_rmsnorm and silu_mul fed with fp32 partials + bias equal the same kernels fed with the rounded sum."""
+    gen = torch.Generator().manual_seed(4)
+    rows, cols, splits = 7, 512, 3
+    part = torch.randn(splits, rows, cols, generator=gen).to(DEV)
+    bias = torch.randn(cols, generator=gen).bfloat16().to(DEV)
+    rounded = (part.sum(0) + bias.float()).bfloat16()
+    res1 = torch.randn(rows, cols, generator=gen).bfloat16().to(DEV)
+    res2 = res1.clone()
+    w = torch.randn(cols, generator=gen).bfloat16().to(DEV)
+    o1, o2 = torch.empty_like(res1), torch.empty_like(res1)
+    ops.add_rmsnorm(res1, part, w, o1, 1e-6, splits, bias)
+    ops.add_rmsnorm(res2, rounded, w, o2, 1e-6)
+    assert torch.equal(res1, res2) and torch.equal(o1, o2)
+    gu_part = torch.randn(splits, rows, 2 * cols, generator=gen).to(DEV)
+    a1 = torch.empty(rows, cols, dtype=torch.bfloat16, device=DEV)
+    a2 = torch.empty_like(a1)
+    ops.silu_mul(gu_part, a1, splits)
+    ops.silu_mul(gu_part.sum(0).bfloat16(), a2)
+    assert torch.equal(a1, a2)

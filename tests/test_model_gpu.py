@@ -61,11 +61,12 @@ def test_generate_matches_cpu_restatement():
     assert mismatched_rows <= 6, mismatched_rows  # of 40 steps x 2 layers x 4 segments
 
 
-@pytest.mark.parametrize("use_graph", [False, True])
-def test_fused_decode_step_matches_module_path(use_graph):
+@pytest.mark.parametrize("use_graph,tc_gemm", [(False, False), (True, False), (True, True)])
+def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, monkeypatch):
     """The fused kernels (add+RMSNorm, decode_prep, SiLU*up) against the PyTorch-op layer on the same weights."""
     from trimkv_b200 import TrimKVCache
     from trimkv_b200.decoder import GreedyDecoder
+    monkeypatch.setenv("TKV_TC_GEMM", "1" if tc_gemm else "0")
     model, cfg = _tiny(memory_size=64, buffer_size=8, layers=3)
     model = model.to(DEV)
     gen = torch.Generator().manual_seed(9)

@@ -219,7 +219,7 @@ class TrimKVCache:
                 self.kv_positions[layer_idx], self._attn_kwargs(layer_idx))
 
     def decode_prep(self, layer_idx: int, qkvg, q_norm_w, k_norm_w, eps, cos, sin, gate_w2, gate_bias, pos, q_out,
-                    num_q_heads: int):
+                    num_q_heads: int, in_splits: int = 0, in_bias=None):
         """Fused form of ``update`` for one new token per request: the kernel normalises and rotates q and k,
         finishes the retention gate and appends K, V, log beta and the position in one launch.  Same counter
         updates as ``update``; returns ``(K view, V view, flash_attn_kwargs)``."""
@@ -234,7 +234,8 @@ class TrimKVCache:
         s = self._slab
         ops.decode_prep(qkvg, q_norm_w, k_norm_w, eps, cos, sin, gate_w2, gate_bias, pos, q_out,
                         s["k"][layer_idx], s["v"][layer_idx], s["beta"][layer_idx], s["pos"][layer_idx],
-                        s["len"][layer_idx], s["cu"][layer_idx], self._cap, num_q_heads, self._hkv, self._status)
+                        s["len"][layer_idx], s["cu"][layer_idx], self._cap, num_q_heads, self._hkv, self._status,
+                        in_splits, in_bias)
         self._cache_len[layer_idx] += 1
         self.n_seen_tokens[layer_idx] += 1
         return self.key_cache[layer_idx], self.value_cache[layer_idx], self._attn_kwargs(layer_idx)

@@ -16,6 +16,7 @@
 #include <cuda.h>
 #include "tkv_common.cuh"
 #include "tkv_attn.cuh"
+#include "tkv_tc.cuh"
 
 namespace tkv {
 
@@ -27,7 +28,6 @@ constexpr int kHalfBytes = 16384;
 constexpr int kQBytes = 4096;                 // 16 heads x 128 dims
 constexpr int kPBytes = 4096;                 // 16 heads x 128 tokens
 constexpr int kTmemCols = 64;                 // S tile 0: [0,16)  S tile 1: [16,32)  O: [32,48)
-constexpr uint32_t kSpinLimit = 1u << 24;
 
 struct TcSmem {                               // after the 1024-byte aligned stage buffers
   uint64_t bar_k[2], bar_v[2], bar_s, bar_o;
@@ -37,85 +37,6 @@ struct TcSmem {                               // after the 1024-byte aligned sta
   float red_sum[4][16];
 };
 constexpr int kTcSmemBytes = 3 * kStageBytes + kQBytes + 2 * kPBytes + (int)sizeof(TcSmem) + 1024;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-// Bounded wait on phase `parity`; false if the limit ran out.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-  }
-  return false;
-}
-// Same, but also gives up as soon as another thread of the CTA has raised the abort flag.
-__device__ __forceinline__ bool mbar_wait_or_abort(uint64_t* bar, uint32_t parity, const volatile int* abort_flag) {
-  const uint32_t addr = smem_u32(bar);
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(addr), "r"(parity) : "memory");
-    if (done) return true;
-    if ((it & 63u) == 63u && *abort_flag != 0) return false;
-  }
-  return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(smem_dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-// Shared-memory matrix descriptor (tcgen05): address, leading/stride byte offsets in 16-byte units, version 1,
-// layout type in bits [61,64) (0 = no swizzle, 2 = 128-byte swizzle).
-__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
-  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(lbo_bytes >> 4) << 16) | ((uint64_t)(sbo_bytes >> 4) << 32) |
-         (1ull << 46) | ((uint64_t)layout << 61);
-}
-// Instruction descriptor, kind::f16: D = f32, A/B = bf16 or f16, M = 128, N = 16.
-__device__ __forceinline__ uint32_t make_idesc(int fmt /*0 f16, 1 bf16*/, int a_mn_major) {
-  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)a_mn_major << 15) | (0u << 16) |
-         ((16u >> 3) << 17) | ((128u >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accum) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accum), "r"(0u) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
-  uint32_t r[16];
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
 
 template <int kDtype, int kG>
 __global__ void __launch_bounds__(kTcThreads)
@@ -364,17 +285,17 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-static int make_map(CUtensorMap* map, const void* base, int64_t rows, int kv_dtype) {
+int make_map_2d(CUtensorMap* map, const void* base, int64_t cols, int64_t rows, int box_cols, int box_rows, int kv_dtype) {
   EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn: cuTensorMapEncodeTiled is not available");
-  const cuuint64_t dims[2] = {128, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {256};
-  const cuuint32_t box[2] = {64, 128};
+  if (fn == nullptr) return fail(TKV_ERR_LAUNCH, "cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, kv_dtype == TKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
                   const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn: cuTensorMapEncodeTiled failed with %d", (int)r);
+  if (r != CUDA_SUCCESS) return fail(TKV_ERR_LAUNCH, "cuTensorMapEncodeTiled failed with %d", (int)r);
   return TKV_OK;
 }
 
@@ -413,9 +334,9 @@ static int launch_tc_g(const CUtensorMap& mk, const CUtensorMap& mv, const AttnP
 // Launches the tensor-core split kernel; `rows` = number of rows addressable behind k/v (bounds of the tensor maps).
 int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, int64_t rows, cudaStream_t st) {
   CUtensorMap mk, mv;
-  int rc = make_map(&mk, p.k, rows, kv_dtype);
+  int rc = make_map_2d(&mk, p.k, 128, rows, 64, 128, kv_dtype);
   if (rc != TKV_OK) return rc;
-  rc = make_map(&mv, p.v, rows, kv_dtype);
+  rc = make_map_2d(&mv, p.v, 128, rows, 64, 128, kv_dtype);
   if (rc != TKV_OK) return rc;
   return kv_dtype == TKV_BF16 ? launch_tc_g<TKV_BF16>(mk, mv, p, nseg, G, st) : launch_tc_g<TKV_F16>(mk, mv, p, nseg, G, st);
 }

@@ -45,8 +45,40 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
+// A GEMM result can arrive either in the model dtype or as `splits` fp32 partial sums [splits][rows][cols] of
+// tkv_skinny_gemm; in the second form the consumer adds the partials in order, adds the bias and rounds once, which
+// is what a GEMM with fp32 accumulation and a rounded output does.
+template <typename T>
+__device__ __forceinline__ float gemm_out(const void* base, int splits, int64_t split_stride, const void* bias,
+                                          int64_t idx, int col) {
+  if (splits == 0) return T::ld(base, idx);
+  const float* part = reinterpret_cast<const float*>(base);
+  float a = part[idx];
+  for (int s = 1; s < splits; ++s) a += part[idx + s * split_stride];
+  if (bias != nullptr) a += T::ld(bias, col);
+  return T::round(a);
+}
+template <typename T>
+__device__ __forceinline__ void gemm_out4(const void* base, int splits, int64_t split_stride, const void* bias,
+                                          int64_t idx, int col, float* out) {
+  if (splits == 0) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(reinterpret_cast<const char*>(base) + idx * 2);
+    out[0] = T::lo(raw.x); out[1] = T::hi(raw.x); out[2] = T::lo(raw.y); out[3] = T::hi(raw.y);
+    return;
+  }
+  const float* part = reinterpret_cast<const float*>(base);
+  float4 a = *reinterpret_cast<const float4*>(part + idx);
+  for (int s = 1; s < splits; ++s) {
+    const float4 b = *reinterpret_cast<const float4*>(part + idx + s * split_stride);
+    a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  }
+  if (bias != nullptr) { a.x += T::ld(bias, col); a.y += T::ld(bias, col + 1); a.z += T::ld(bias, col + 2); a.w += T::ld(bias, col + 3); }
+  out[0] = T::round(a.x); out[1] = T::round(a.y); out[2] = T::round(a.z); out[3] = T::round(a.w);
+}
+
 struct PrepParams {
-  const char* qkvg; int64_t row_bytes;       // [B, (Hq + 2 Hkv) * 128 + gate_inter]
+  const void* qkvg; int64_t row_elems;       // [B, (Hq + 2 Hkv) * 128 + gate_inter], or fp32 partials of it
+  int in_splits; int64_t split_stride; const void* in_bias;
   const void* q_norm_w; const void* k_norm_w; float eps;
   const void* cos; const void* sin;          // [128] of the model dtype
   const void* gate_w2; const void* gate_bias; int gate_inter;
@@ -73,10 +105,10 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   const int b = w / heads, head = w - b * heads;
   const bool is_q = head < p.hq;
   const int kvh = head - p.hq;
-  const char* row = p.qkvg + (int64_t)b * p.row_bytes;
-  const char* src = row + (int64_t)(is_q ? head : p.hq + kvh) * 256 + lane * 8;
-  const uint2 raw = *reinterpret_cast<const uint2*>(src);
-  float x[4] = {T::lo(raw.x), T::hi(raw.x), T::lo(raw.y), T::hi(raw.y)};
+  const int64_t row = (int64_t)b * p.row_elems;          // element offset of this request's row
+  const int col = (is_q ? head : p.hq + kvh) * 128 + lane * 4;
+  float x[4];
+  gemm_out4<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + col, col, x);
   // RMSNorm over the head: fp32 statistics, normalised value rounded, then multiplied by the weight.
   const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
   const float rstd = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
@@ -102,10 +134,10 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   const int len = p.seg_len[seg];
   __syncwarp();
   // Retention gate tail: log beta = logsigmoid(linear2(SiLU(hidden)) + bias), rounded after every op.
-  const char* gh = row + (int64_t)(p.hq + 2 * p.hkv) * 256;
+  const int gcol = (p.hq + 2 * p.hkv) * 128;
   float acc = 0.f;
   for (int i = lane; i < p.gate_inter; i += 32) {
-    const float g = T::ld(gh, i);
+    const float g = gemm_out<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + gcol + i, gcol + i);
     const float act = T::round(g / (1.0f + expf(-g)));
     acc = fmaf(act, T::ld(p.gate_w2, (int64_t)kvh * p.gate_inter + i), acc);
   }
@@ -118,8 +150,10 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   }
   const int64_t dst = (int64_t)seg * p.cap + len;
   *reinterpret_cast<uint2*>(p.k_cache + dst * 256 + lane * 8) = packed;
-  *reinterpret_cast<uint2*>(p.v_cache + dst * 256 + lane * 8) =
-      *reinterpret_cast<const uint2*>(row + (int64_t)(p.hq + p.hkv + kvh) * 256 + lane * 8);
+  float vv[4];
+  const int vcol = (p.hq + p.hkv + kvh) * 128 + lane * 4;
+  gemm_out4<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + vcol, vcol, vv);
+  *reinterpret_cast<uint2*>(p.v_cache + dst * 256 + lane * 8) = make_uint2(T::pack(vv[0], vv[1]), T::pack(vv[2], vv[3]));
   if (lane == 0) {
     p.beta_cache[dst] = log_beta;
     p.pos_cache[dst] = (int32_t)p.pos[0];
@@ -131,7 +165,8 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
 // residual[r] += delta[r] (if delta), out[r] = weight * round(residual[r] * rstd).  One CTA per row.
 template <int kDtype>
 __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const char* delta, const void* weight,
-                                                          char* out, int cols, float eps) {
+                                                          char* out, int cols, float eps, int in_splits,
+                                                          int64_t split_stride, const void* in_bias) {
   using T = T16<kDtype>;
   __shared__ float red[8];
   grid_dependency_wait();
@@ -141,7 +176,17 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
   // Pass 1: update the residual stream and accumulate the sum of squares.
   for (int i = threadIdx.x; i < nvec; i += 256) {
     uint4 r = ld16(residual + off + (int64_t)i * 16);
-    if (delta != nullptr) {
+    if (delta != nullptr && in_splits > 0) {
+      float d[8];
+      const int64_t e0 = (int64_t)blockIdx.x * cols + (int64_t)i * 8;
+      gemm_out4<T>(delta, in_splits, split_stride, in_bias, e0, i * 8, d);
+      gemm_out4<T>(delta, in_splits, split_stride, in_bias, e0 + 4, i * 8 + 4, d + 4);
+      r.x = T::pack(T::lo(r.x) + d[0], T::hi(r.x) + d[1]);
+      r.y = T::pack(T::lo(r.y) + d[2], T::hi(r.y) + d[3]);
+      r.z = T::pack(T::lo(r.z) + d[4], T::hi(r.z) + d[5]);
+      r.w = T::pack(T::lo(r.w) + d[6], T::hi(r.w) + d[7]);
+      st16(residual + off + (int64_t)i * 16, r);
+    } else if (delta != nullptr) {
       const uint4 d = ld16(delta + off + (int64_t)i * 16);
       r.x = T::pack(T::lo(r.x) + T::lo(d.x), T::hi(r.x) + T::hi(d.x));
       r.y = T::pack(T::lo(r.y) + T::lo(d.y), T::hi(r.y) + T::hi(d.y));
@@ -175,20 +220,33 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
 
 // out[r, j] = round(round(SiLU(gu[r, j])) * gu[r, inter + j]).
 template <int kDtype>
-__global__ void __launch_bounds__(256) silu_mul_kernel(const char* gu, char* out, int rows, int inter) {
+__global__ void __launch_bounds__(256) silu_mul_kernel(const char* gu, char* out, int rows, int inter, int in_splits,
+                                                       int64_t split_stride, const void* in_bias) {
   using T = T16<kDtype>;
   const int nvec = inter / 8;
   const int64_t total = (int64_t)rows * nvec;
   grid_dependency_wait();
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const int64_t r = i / nvec, c = i - r * nvec;
-    const uint4 g = ld16(gu + (r * 2 * inter) * 2 + c * 16);
-    const uint4 u = ld16(gu + (r * 2 * inter + inter) * 2 + c * 16);
     auto f = [](float gg, float uu) {
       const float act = T::round(gg / (1.0f + expf(-gg)));
       return act * uu;
     };
     uint4 o;
+    if (in_splits > 0) {
+      float g8[8], u8[8];
+      const int64_t e0 = r * 2 * inter + c * 8;
+      gemm_out4<T>(gu, in_splits, split_stride, in_bias, e0, (int)(c * 8), g8);
+      gemm_out4<T>(gu, in_splits, split_stride, in_bias, e0 + 4, (int)(c * 8 + 4), g8 + 4);
+      gemm_out4<T>(gu, in_splits, split_stride, in_bias, e0 + inter, (int)(inter + c * 8), u8);
+      gemm_out4<T>(gu, in_splits, split_stride, in_bias, e0 + inter + 4, (int)(inter + c * 8 + 4), u8 + 4);
+      o.x = T::pack(f(g8[0], u8[0]), f(g8[1], u8[1])); o.y = T::pack(f(g8[2], u8[2]), f(g8[3], u8[3]));
+      o.z = T::pack(f(g8[4], u8[4]), f(g8[5], u8[5])); o.w = T::pack(f(g8[6], u8[6]), f(g8[7], u8[7]));
+      st16(out + (r * inter) * 2 + c * 16, o);
+      continue;
+    }
+    const uint4 g = ld16(gu + (r * 2 * inter) * 2 + c * 16);
+    const uint4 u = ld16(gu + (r * 2 * inter + inter) * 2 + c * 16);
     o.x = T::pack(f(T::lo(g.x), T::lo(u.x)), f(T::hi(g.x), T::hi(u.x)));
     o.y = T::pack(f(T::lo(g.y), T::lo(u.y)), f(T::hi(g.y), T::hi(u.y)));
     o.z = T::pack(f(T::lo(g.z), T::lo(u.z)), f(T::hi(g.z), T::hi(u.z)));
@@ -207,6 +265,7 @@ extern "C" int tkv_decode_prep(const void* qkvg, int64_t row_stride,
                                void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
                                int32_t* seg_len, int32_t* cu_seqlens, int64_t cap,
                                int batch, int hq, int hkv, int head_dim, int dtype,
+                               int in_splits, const void* in_bias,
                                int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   if (!qkvg || !q_norm_w || !k_norm_w || !cos || !sin || !gate_w2 || !gate_bias || !pos || !q_out || !k_cache ||
@@ -215,14 +274,17 @@ extern "C" int tkv_decode_prep(const void* qkvg, int64_t row_stride,
   if (head_dim != 128) return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_prep: head_dim=%d (only 128)", head_dim);
   if (dtype != TKV_BF16 && dtype != TKV_F16) return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_prep: dtype %d", dtype);
   if (batch < 0 || hq <= 0 || hkv <= 0 || gate_inter <= 0 || cap <= 0) return fail(TKV_ERR_ARG, "tkv_decode_prep: bad sizes");
-  if (row_stride < (int64_t)(hq + 2 * hkv) * 128 + gate_inter || (row_stride * 2) % 8)
+  if (row_stride < (int64_t)(hq + 2 * hkv) * 128 + gate_inter || (row_stride * 2) % 8 || in_splits < 0)
     return fail(TKV_ERR_ARG, "tkv_decode_prep: row_stride=%lld too small or misaligned", (long long)row_stride);
+  if (in_splits > 0 && (row_stride % 4 || (reinterpret_cast<uintptr_t>(qkvg) & 15u)))
+    return fail(TKV_ERR_ARG, "tkv_decode_prep: fp32 partial input must be 16-byte aligned with row_stride %% 4 == 0");
   if ((reinterpret_cast<uintptr_t>(qkvg) | reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_cache) |
        reinterpret_cast<uintptr_t>(v_cache)) & 7u)
     return fail(TKV_ERR_ARG, "tkv_decode_prep: pointers must be 8-byte aligned");
   if (batch == 0) return TKV_OK;
   PrepParams p;
-  p.qkvg = (const char*)qkvg; p.row_bytes = row_stride * 2;
+  p.qkvg = qkvg; p.row_elems = row_stride;
+  p.in_splits = in_splits; p.split_stride = (int64_t)batch * row_stride; p.in_bias = in_bias;
   p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.eps = eps; p.cos = cos; p.sin = sin;
   p.gate_w2 = gate_w2; p.gate_bias = gate_bias; p.gate_inter = gate_inter; p.pos = pos;
   p.q_out = (char*)q_out; p.k_cache = (char*)k_cache; p.v_cache = (char*)v_cache;
@@ -238,7 +300,8 @@ extern "C" int tkv_decode_prep(const void* qkvg, int64_t row_stride,
 }
 
 extern "C" int tkv_add_rmsnorm(void* residual, const void* delta, const void* weight, void* out,
-                               int rows, int cols, float eps, int dtype, tkv_stream_t stream) {
+                               int rows, int cols, float eps, int dtype, int in_splits, const void* in_bias,
+                               tkv_stream_t stream) {
   using namespace tkv;
   if (!residual || !weight || !out) return fail(TKV_ERR_ARG, "tkv_add_rmsnorm: NULL pointer argument");
   if (dtype != TKV_BF16 && dtype != TKV_F16) return fail(TKV_ERR_UNSUPPORTED, "tkv_add_rmsnorm: dtype %d", dtype);
@@ -248,14 +311,15 @@ extern "C" int tkv_add_rmsnorm(void* residual, const void* delta, const void* we
   if (rows == 0) return TKV_OK;
   cudaError_t e = dtype == TKV_BF16
       ? launch_pdl(add_rmsnorm_kernel<TKV_BF16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (char*)residual,
-                   (const char*)delta, weight, (char*)out, cols, eps)
+                   (const char*)delta, weight, (char*)out, cols, eps, in_splits, (int64_t)rows * cols, in_bias)
       : launch_pdl(add_rmsnorm_kernel<TKV_F16>, dim3(rows), dim3(256), 0, (cudaStream_t)stream, (char*)residual,
-                   (const char*)delta, weight, (char*)out, cols, eps);
+                   (const char*)delta, weight, (char*)out, cols, eps, in_splits, (int64_t)rows * cols, in_bias);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_add_rmsnorm: %s", cudaGetErrorString(e));
   return check_launch("tkv_add_rmsnorm");
 }
 
-extern "C" int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, tkv_stream_t stream) {
+extern "C" int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter, int dtype, int in_splits,
+                            const void* in_bias, tkv_stream_t stream) {
   using namespace tkv;
   if (!gate_up || !out) return fail(TKV_ERR_ARG, "tkv_silu_mul: NULL pointer argument");
   if (dtype != TKV_BF16 && dtype != TKV_F16) return fail(TKV_ERR_UNSUPPORTED, "tkv_silu_mul: dtype %d", dtype);
@@ -265,8 +329,10 @@ extern "C" int tkv_silu_mul(const void* gate_up, void* out, int rows, int inter,
   const int64_t total = (int64_t)rows * (inter / 8);
   const int grid = (int)((total + 255) / 256 < 148 * 8 ? (total + 255) / 256 : 148 * 8);
   cudaError_t e = dtype == TKV_BF16
-      ? launch_pdl(silu_mul_kernel<TKV_BF16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out, rows, inter)
-      : launch_pdl(silu_mul_kernel<TKV_F16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out, rows, inter);
+      ? launch_pdl(silu_mul_kernel<TKV_BF16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out,
+                   rows, inter, in_splits, (int64_t)rows * 2 * inter, in_bias)
+      : launch_pdl(silu_mul_kernel<TKV_F16>, dim3(grid), dim3(256), 0, (cudaStream_t)stream, (const char*)gate_up, (char*)out,
+                   rows, inter, in_splits, (int64_t)rows * 2 * inter, in_bias);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_silu_mul: %s", cudaGetErrorString(e));
   return check_launch("tkv_silu_mul");
 }

@@ -7,6 +7,7 @@ eviction (`cache.compress`) stays outside the graph because the host decides whe
 """
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -51,6 +52,26 @@ class FusedDecodeStep:
                 mlp.gate_proj.weight.data, mlp.up_proj.weight.data = gu[:inter], gu[inter:]
                 self.layers.append((layer, w, bias, gu))
         self.hq, self.hkv, self.eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps
+        # tkv_skinny_gemm for the four per-layer projections.  Off by default: at 32 rows these GEMMs are bound by
+        # launch and pipeline-fill latency, and the tensor-core kernel only matches cuBLAS (5-12 us per call either
+        # way on B200) while its fp32 partials make the consumers slower; TKV_TC_GEMM=1 switches it on.
+        self.use_tc_gemm = os.environ.get("TKV_TC_GEMM", "0") == "1"
+        self._partials = {}
+
+    def _gemm(self, x, w, tag):
+        """x [B, K] @ w [N, K].T through the weight-streaming tensor-core kernel; returns (partials, splits), or
+        (None, 0) when the shape is outside its envelope (then the caller uses the library GEMM)."""
+        m, k = x.shape
+        n = w.shape[0]
+        splits = ops.skinny_gemm_splits(m, n, k) if self.use_tc_gemm else 0
+        if splits == 0:
+            return None, 0
+        buf = self._partials.get((tag, m))
+        if buf is None:
+            buf = torch.empty(splits, m, n, dtype=torch.float32, device=x.device)
+            self._partials[(tag, m)] = buf
+        ops.skinny_gemm(x, w, buf, self.cache._status)
+        return buf, splits
 
     def __call__(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         """ids [B,1] int64, pos [1] int64 (device) -> logits [B, vocab]."""
@@ -63,21 +84,30 @@ class FusedDecodeStep:
         cos, sin = cos.reshape(-1), sin.reshape(-1)
         h = torch.empty_like(x)
         q_out = torch.empty(bsz, self.hq, 1, 128, dtype=x.dtype, device=x.device)
-        delta = None
+        delta, d_splits = None, 0
         for l, (layer, w_qkvg, b_qkvg, w_gu) in enumerate(self.layers):
             at = layer.self_attn
-            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps)
-            qkvg = F.linear(h, w_qkvg, b_qkvg)
+            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps, d_splits)
+            qkvg, s1 = self._gemm(h, w_qkvg, "qkvg")
+            if s1 == 0:
+                qkvg = F.linear(h, w_qkvg, b_qkvg)
             k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin,
-                                         at.retention_gate.linear2.weight, at.retention_gate.bias, pos, q_out, self.hq)
+                                         at.retention_gate.linear2.weight, at.retention_gate.bias, pos, q_out, self.hq,
+                                         s1, b_qkvg if s1 else None)
             o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
-            a = F.linear(o.view(bsz, -1), at.o_proj.weight, at.o_proj.bias)
-            ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps)
-            gu = F.linear(h, w_gu)
+            a, s2 = self._gemm(o.view(bsz, -1), at.o_proj.weight, "o")
+            if s2 == 0:
+                a = F.linear(o.view(bsz, -1), at.o_proj.weight, at.o_proj.bias)
+            ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps, s2, at.o_proj.bias if s2 else None)
+            gu, s3 = self._gemm(h, w_gu, "gu")
+            if s3 == 0:
+                gu = F.linear(h, w_gu)
             act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
-            ops.silu_mul(gu, act)
-            delta = F.linear(act, layer.mlp.down_proj.weight)
-        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps)
+            ops.silu_mul(gu, act, s3)
+            delta, d_splits = self._gemm(act, layer.mlp.down_proj.weight, "down")
+            if d_splits == 0:
+                delta = F.linear(act, layer.mlp.down_proj.weight)
+        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps, d_splits)
         return F.linear(h, self.model.lm_head.weight)
 
 

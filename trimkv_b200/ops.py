@@ -145,33 +145,52 @@ def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspac
 
 def decode_prep(qkvg, q_norm_w, k_norm_w, eps: float, cos, sin, gate_w2, gate_bias, pos, q_out,
                 k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, cap: int, hq: int, hkv: int,
-                status=None) -> None:
-    """Fused q/k-norm + RoPE + retention-gate tail + append for one new token per request (head_dim 128)."""
-    b = qkvg.shape[0]
+                status=None, in_splits: int = 0, in_bias=None) -> None:
+    """Fused q/k-norm + RoPE + retention-gate tail + append for one new token per request (head_dim 128).
+    ``qkvg`` is ``[B, cols]`` in the model dtype, or (``in_splits`` > 0) the fp32 ``[splits, B, cols]`` of skinny_gemm."""
+    b, cols = qkvg.shape[-2], qkvg.shape[-1]
     rc = lib().tkv_decode_prep(
-        qkvg.data_ptr(), qkvg.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), float(eps),
+        qkvg.data_ptr(), cols if in_splits else qkvg.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), float(eps),
         cos.data_ptr(), sin.data_ptr(), gate_w2.data_ptr(), gate_bias.data_ptr(), gate_w2.shape[1],
         pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(),
         pos_cache.data_ptr(), seg_len.data_ptr(), _ptr(cu_seqlens), cap, b, hq, hkv, 128,
-        dtype_code(qkvg.dtype), _ptr(status), _stream(qkvg))
+        dtype_code(q_out.dtype), in_splits, _ptr(in_bias), _ptr(status), _stream(qkvg))
     check(rc, "tkv_decode_prep")
     _count(1)
 
 
-def add_rmsnorm(residual, delta, weight, out, eps: float) -> None:
+def add_rmsnorm(residual, delta, weight, out, eps: float, in_splits: int = 0, in_bias=None) -> None:
     rows, cols = residual.shape
     rc = lib().tkv_add_rmsnorm(residual.data_ptr(), _ptr(delta), weight.data_ptr(), out.data_ptr(), rows, cols,
-                               float(eps), dtype_code(residual.dtype), _stream(residual))
+                               float(eps), dtype_code(residual.dtype), in_splits, _ptr(in_bias), _stream(residual))
     check(rc, "tkv_add_rmsnorm")
     _count(1)
 
 
-def silu_mul(gate_up, out) -> None:
-    rows, two_inter = gate_up.shape
-    rc = lib().tkv_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two_inter // 2, dtype_code(gate_up.dtype),
-                            _stream(gate_up))
+def silu_mul(gate_up, out, in_splits: int = 0, in_bias=None) -> None:
+    rows, two_inter = gate_up.shape[-2], gate_up.shape[-1]
+    rc = lib().tkv_silu_mul(gate_up.data_ptr(), out.data_ptr(), rows, two_inter // 2, dtype_code(out.dtype),
+                            in_splits, _ptr(in_bias), _stream(gate_up))
     check(rc, "tkv_silu_mul")
     _count(1)
+
+
+def skinny_gemm_splits(m: int, n: int, k: int) -> int:
+    """Number of fp32 partial sums tkv_skinny_gemm produces for this shape; 0 = shape not supported."""
+    return int(lib().tkv_skinny_gemm_splits(m, n, k))
+
+
+def skinny_gemm(x, w, partial, status=None) -> int:
+    """``partial [splits, M, N]`` fp32 with ``sum(partial, 0) == x [M, K] @ w [N, K].T``; returns ``splits``."""
+    m, k = x.shape
+    n = w.shape[0]
+    if not (x.is_contiguous() and w.is_contiguous() and partial.is_contiguous() and partial.dtype == torch.float32):
+        raise ValueError("skinny_gemm wants contiguous x, w and an fp32 contiguous partial buffer")
+    rc = lib().tkv_skinny_gemm(x.data_ptr(), w.data_ptr(), partial.data_ptr(), m, n, k, dtype_code(x.dtype),
+                               _ptr(status), _stream(x))
+    check(rc, "tkv_skinny_gemm")
+    _count(1)
+    return skinny_gemm_splits(m, n, k)
 
 
 def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
