@@ -298,6 +298,9 @@ def main():
     ap.add_argument("--workload", default="qwen3-1.7b-decode", choices=sorted(WORKLOADS))
     ap.add_argument("--no-graph", action="store_true", help="dispatch every decode step from Python (no CUDA graph)")
     ap.add_argument("--no-fused", action="store_true", help="run the layer as separate PyTorch ops around the cache kernels")
+    ap.add_argument("--head-sharded", action="store_true",
+                    help="N > 1: all ranks decode the same requests, each owning Hkv/N KV heads (all-gather of attention "
+                         "outputs per layer) instead of the default batch partition")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-batch", type=int, default=2, help="requests in the host-core baseline sample")
     ap.add_argument("--cpu-steps", type=int, default=12)
@@ -338,7 +341,12 @@ def main():
         first = out.logits[:, -1].argmax(-1, keepdim=True)
         del out
         torch.cuda.empty_cache()
-        dec = GreedyDecoder(model, cache, use_graph=not args.no_graph, fused=not args.no_fused)
+        sharded = args.head_sharded and world > 1
+        if sharded:
+            cache = cache.head_shard(rank, world)   # the prompt pass was replicated; keep this rank's KV heads only
+            torch.cuda.empty_cache()
+        dec = GreedyDecoder(model, cache, use_graph=not args.no_graph, fused=not args.no_fused,
+                            head_shard_group=dist.group.WORLD if sharded else None)
         dec.ids.copy_(first)
         for _ in range(args.warmup):  # eager warm-up steps (allocate workspaces before any capture)
             dec.step(eager=True)
@@ -419,13 +427,15 @@ def main():
         ms_e2e = max_over_ranks(f0.elapsed_time(f1))
         cache.check_status()
 
-    tokens = B * args.steps * world
+    tokens = B * args.steps * (1 if sharded else world)
     value = tokens / (ms_total * 1e-3)
     e2e = tokens / (ms_e2e * 1e-3)
 
     # ---- roofline of the dominant kernel (decode attention: reads every cached K/V row once per step)
     peak, peak_src = measured_peaks()
     Hq, Hkv, D, L = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.num_hidden_layers
+    if sharded:  # per-rank kernels see this rank's heads only
+        Hq, Hkv = Hq // world, Hkv // world
     ach = []
     for evs, n in zip(attn_events, lens_at_sample):
         bytes_per_launch = B * Hkv * n * 4 * D + B * Hq * D * 2 * 2
@@ -461,10 +471,11 @@ def main():
     if rank == 0:
         line = {
             "metric": "decode_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "warmup": args.warmup, "ms_per_step": ms_total / args.steps, "higher_is_better": True,
+            "scaling": "strong" if sharded else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": args.workload, "global_batch": B * world, "batch_per_gpu": B, "prompt_len": P,
-                       "memory_size": M, "buffer_size": Bf, "parallelism": f"batch-partition x{world}",
+            "config": {"workload": args.workload, "global_batch": B * (1 if sharded else world), "batch_per_gpu": B, "prompt_len": P,
+                       "memory_size": M, "buffer_size": Bf, "parallelism": (f"kv-head-shard x{world}" if sharded else f"batch-partition x{world}"),
                        "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
                        "l2": "per-step working set (weights + 15 GB of K/V) exceeds L2; no explicit flush"},
             "roofline": roofline, "evict": evict, "cpu_baseline": cpu,
@@ -474,6 +485,13 @@ def main():
         }
         print(json.dumps(line))
     if world > 1:
+        if sharded:
+            # NCCL collectives live inside the captured decode graph; communicator teardown with such a graph alive
+            # did not return on this stack, so the sharded mode synchronises and leaves without it.
+            sys.stdout.flush()
+            torch.cuda.synchronize()
+            dist.barrier()
+            os._exit(0)
         dist.destroy_process_group()
 
 

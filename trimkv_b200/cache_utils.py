@@ -277,6 +277,9 @@ class TrimKVCache:
         pend = [p for p in self._pending if p is not None]
         if not pend:
             return
+        # Rows are only evicted here when compress() asked for it (or in the per-layer hand-off, which stands for it);
+        # the constructor hints alone just size the slabs.
+        do_select = memory_size is not None or only_layer is not None
         m = memory_size if memory_size is not None else self._hint_m
         bsz = buffer_size if buffer_size is not None else self._hint_b
         self._kv_dtype = pend[0][0].dtype
@@ -285,7 +288,7 @@ class TrimKVCache:
             self._status = ops.new_status(dev)
         longest = max(self._cache_len)
         if m is not None and bsz is not None:
-            kept_longest = max((m if n >= m + bsz else n) for n in self._cache_len)
+            kept_longest = max((m if (do_select and n >= m + bsz) else n) for n in self._cache_len)
             cap = max(m + bsz, kept_longest + extra)
         else:
             cap = (longest + extra + 63) // 64 * 64 if extra >= 64 else 1 << max(8, (longest + extra + 255).bit_length())
@@ -304,7 +307,7 @@ class TrimKVCache:
             beta32 = beta.to(torch.float32).reshape(nseg, n).contiguous()
             pos32 = pos.to(torch.int32).reshape(nseg, n).contiguous()
             kept_idx = kept_cnt = None
-            if m is not None and bsz is not None and n >= m + bsz:
+            if do_select and m is not None and bsz is not None and n >= m + bsz:
                 kept_idx = torch.empty(nseg, m, dtype=torch.int32, device=dev)
                 kept_cnt = torch.empty(nseg, dtype=torch.int32, device=dev)
                 ops.evict_select(beta32, pos32, None, n, nseg, self.n_seen_tokens[l] + 1, m, m + bsz, n,
@@ -426,6 +429,21 @@ class TrimKVCache:
             new.n_seen_tokens.append(self.n_seen_tokens[l])
             new._batch, new._hkv, new._dim = k.shape[0], k.shape[1], k.shape[3]
         return new
+
+    def head_shard(self, rank: int, world_size: int) -> "TrimKVCache":
+        """A cache holding only KV heads ``[rank*Hkv/world, (rank+1)*Hkv/world)`` of every layer and request: the
+        per-rank cache of the KV-head-sharded decode (segments are independent, so nothing else changes)."""
+        if self._hkv % world_size:
+            raise ValueError(f"{self._hkv} KV heads cannot be split over {world_size} ranks")
+        hl = self._hkv // world_size
+        lo, hi = rank * hl, (rank + 1) * hl
+        n = None
+        dense = []
+        for l, (k, v, b, p) in enumerate(self):
+            n = self._cache_len[l]
+            dense.append((k[:, lo:hi, :n].contiguous(), v[:, lo:hi, :n].contiguous(), b[:, lo:hi, :n].contiguous(),
+                          p[:, lo:hi, :n].contiguous()))
+        return self._clone_from_dense(dense)
 
     def batch_select_indices(self, indices: torch.Tensor):
         dense = [(k[indices, ...].contiguous(), v[indices, ...].contiguous(), b[indices, ...].contiguous(),

@@ -118,10 +118,12 @@ class GreedyDecoder:
     previous step's argmax without leaving the device.  Returns the device tensor holding the new ids.
     """
 
-    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True):
+    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True, head_shard_group=None):
         self.model, self.cache, self.cfg = model, cache, model.config
         self.fused = None
-        if fused and model.config.head_dim == 128 and model.config.retention_gate == "rg" \
+        if head_shard_group is not None:
+            self.fused = HeadShardedDecodeStep(model, cache, head_shard_group)
+        elif fused and model.config.head_dim == 128 and model.config.retention_gate == "rg" \
                 and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
             self.fused = FusedDecodeStep(model, cache)
         dev = model.device
@@ -185,3 +187,72 @@ class GreedyDecoder:
                 strategy=self.cfg.compress_strategy, memory_size=self.cfg.memory_size, buffer_size=self.cfg.buffer_size,
                 num_layers=self.cfg.num_hidden_layers, num_key_value_heads=self.cfg.num_key_value_heads)
         return self.next_ids
+
+
+class HeadShardedDecodeStep(FusedDecodeStep):
+    """Decode step with the KV heads (and their query heads, cache segments and attention) split across ranks.
+
+    Rank r of N owns KV heads ``[r*Hkv/N, (r+1)*Hkv/N)``: its slice of the q/k/v projections and of the gate's second
+    layer, the cache segments of those heads for every request, and their attention.  After attention one all-gather
+    of ``[B, Hq/N * D]`` per layer (NCCL over NVLink) rebuilds ``[B, Hq * D]``; o_proj, the MLP and the LM head are
+    replicated, so every rank ends the step with the same logits.  Nothing on the cache path is exchanged: a segment
+    is appended to, evicted and attended on the rank that owns it.  The reference has no counterpart (it is single
+    process); per head the arithmetic is that of the unsharded step.
+    """
+
+    def __init__(self, model, cache: TrimKVCache, group=None):
+        import torch.distributed as dist
+        super().__init__(model, cache)
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        cfg = model.config
+        if cfg.num_key_value_heads % self.world:
+            raise ValueError(f"{cfg.num_key_value_heads} KV heads cannot be split over {self.world} ranks")
+        self.hkv_l = cfg.num_key_value_heads // self.world
+        self.hq_l = cfg.num_attention_heads // self.world
+        if cache._hkv != self.hkv_l:
+            raise ValueError("the cache must hold this rank's KV heads only (see TrimKVCache.head_shard)")
+        d, hq, hkv = 128, cfg.num_attention_heads, cfg.num_key_value_heads
+        q0, k0 = self.rank * self.hq_l * d, self.rank * self.hkv_l * d
+        self.local = []
+        with torch.no_grad():
+            for layer, w, bias, _ in self.layers:
+                rows = torch.cat([torch.arange(q0, q0 + self.hq_l * d), hq * d + torch.arange(k0, k0 + self.hkv_l * d),
+                                  (hq + hkv) * d + torch.arange(k0, k0 + self.hkv_l * d),
+                                  torch.arange((hq + 2 * hkv) * d, w.shape[0])]).to(w.device)
+                g = layer.self_attn.retention_gate
+                h0 = self.rank * self.hkv_l
+                self.local.append((w[rows].contiguous(), None if bias is None else bias[rows].contiguous(),
+                                   g.linear2.weight[h0:h0 + self.hkv_l].contiguous(), g.bias[h0:h0 + self.hkv_l].contiguous()))
+
+    def __call__(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+        import torch.nn.functional as F
+        from .attn import tkv_attention_forward
+        m, cache = self.model.model, self.cache
+        bsz = ids.shape[0]
+        x = F.embedding(ids.view(bsz), m.embed_tokens.weight)
+        cos, sin = m.rotary_emb(x, pos.view(1, 1))
+        cos, sin = cos.reshape(-1), sin.reshape(-1)
+        h = torch.empty_like(x)
+        q_out = torch.empty(bsz, self.hq_l, 1, 128, dtype=x.dtype, device=x.device)
+        gathered = torch.empty(self.world, bsz, self.hq_l * 128, dtype=x.dtype, device=x.device)
+        delta = None
+        for l, (layer, _, _, w_gu) in enumerate(self.layers):
+            at = layer.self_attn
+            w_l, b_l, g2_l, gb_l = self.local[l]
+            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps)
+            qkvg = F.linear(h, w_l, b_l)
+            k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin, g2_l, gb_l,
+                                         pos, q_out, self.hq_l)
+            o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
+            dist.all_gather_into_tensor(gathered, o.view(bsz, -1), group=self.group)
+            full = gathered.permute(1, 0, 2).reshape(bsz, -1)      # rank-major head blocks = head order
+            a = F.linear(full, at.o_proj.weight, at.o_proj.bias)
+            ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps)
+            gu = F.linear(h, w_gu)
+            act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
+            ops.silu_mul(gu, act)
+            delta = F.linear(act, layer.mlp.down_proj.weight)
+        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps)
+        return F.linear(h, self.model.lm_head.weight)
