@@ -309,3 +309,35 @@ def test_consumers_accept_gemm_partials(ops):
     ops.silu_mul(gu_part, a1, splits)
     ops.silu_mul(gu_part.sum(0).bfloat16(), a2)
     assert torch.equal(a1, a2)
+
+
+def test_full_size_attention_cross_check(ops):
+    """BASELINE configs[3] sizes (batch 64, 32/8 heads, lognormal lengths in [64, 8192]): the tensor-core kernel on the
+    capacity-strided layout against the CUDA-core kernel on the packed copy of the same cache, plus two properties that
+    need no second implementation (constant V gives that constant; the output is a convex combination of V rows)."""
+    gen = torch.Generator(device=DEV).manual_seed(0)
+    bsz, hq, hkv, d, cap = 64, 32, 8, 128, 8192
+    nseg = bsz * hkv
+    lens = torch.exp(torch.randn(nseg, generator=gen, device=DEV) + 7.6246).clamp(64, 8192).round().to(torch.int32)
+    q = torch.randn(bsz, hq, d, generator=gen, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(nseg * cap, d, generator=gen, device=DEV, dtype=torch.bfloat16)
+    v = torch.randn(nseg * cap, d, generator=gen, device=DEV, dtype=torch.bfloat16)
+    out = torch.empty(bsz, hq, d, dtype=torch.bfloat16, device=DEV)
+    ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, cap), dtype=torch.uint8, device=DEV)
+    status = ops.new_status(DEV)
+    ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, d ** -0.5, cap, status)
+    mask = (torch.arange(cap, device=DEV)[None, :] < lens[:, None]).view(-1)
+    kp, vp = k[mask].contiguous(), v[mask].contiguous()
+    cu = torch.zeros(nseg + 1, dtype=torch.int32, device=DEV)
+    cu[1:] = lens.cumsum(0)
+    out2 = torch.empty_like(out)
+    ops.decode_attn(q, kp, vp, lens, cu[:-1].contiguous(), 0, out2, ws, hkv, d ** -0.5, cap, status)
+    assert ops.read_status(status) == 0
+    assert float((out.float() - out2.float()).abs().max()) <= 2e-2
+    vmax = v.view(nseg, cap, d).float().masked_fill(~mask.view(nseg, cap, 1), -1e30).amax(1)   # per segment, per dim
+    vmin = v.view(nseg, cap, d).float().masked_fill(~mask.view(nseg, cap, 1), 1e30).amin(1)
+    o = out.float().view(bsz, hkv, hq // hkv, d)
+    assert bool((o <= vmax.view(bsz, hkv, 1, d) + 2e-2).all()) and bool((o >= vmin.view(bsz, hkv, 1, d) - 2e-2).all())
+    v.fill_(0.75)
+    ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, d ** -0.5, cap, status)
+    assert float((out.float() - 0.75).abs().max()) <= 4e-3

@@ -63,6 +63,9 @@ def tkv_attention_forward(
     if head_lens is None or ql != 1:
         if key.dim() != 4:
             raise NotImplementedError("multi-token queries over a packed flat cache")
+        if head_lens is not None and not flash_attn_kwargs.get("uniform_lengths", False):
+            raise NotImplementedError("multi-token queries over a cache whose segments differ in length "
+                                      "(chunked prefill over the flat budget-sharing caches is not built)")
         return _dense_causal(query, key, value, scaling), None, None
 
     q3 = query[:, :, 0, :]
