@@ -108,6 +108,8 @@ CASES = [
     (1, 130, 128, 129, 130, "full", torch.bfloat16, _bf16_logbeta),      # evict exactly one token
     (3, 77, 128, 1, 2, "full", torch.float16, _coarse_logbeta),          # keep a single token
     (2, 4224, 128, 4096, 4224, "full", torch.bfloat16, _bf16_logbeta),   # config-2 steady state
+    (2, 16512, 128, 16384, 16512, "full", torch.bfloat16, _bf16_logbeta),  # long segments: the 512-thread variant
+    (3, 20000, 64, 15000, 15001, "ragged", torch.bfloat16, _coarse_logbeta),
 ]
 
 

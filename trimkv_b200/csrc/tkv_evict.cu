@@ -19,9 +19,10 @@ constexpr int kEvictThreads = 256;
 constexpr int kEvictUnroll = 8;              // 16-byte vectors in flight per thread and tile
 constexpr int kMaxSelectLen = 57000;         // keys must fit in 227 KB of shared memory
 
+constexpr int kEvictThreadsWide = 512;       // for long segments, whose key array allows fewer CTAs per SM
 struct SelectScratch {
   int hist[256];
-  int warp_sums[kEvictThreads / 32 + 1];
+  int warp_sums[kEvictThreadsWide / 32 + 1];
   int sel_digit;
   int sel_k;
   int first_evicted;
@@ -29,17 +30,18 @@ struct SelectScratch {
 
 // Finds T = key of the m-th largest element and r = how many elements equal to T are kept.
 // All threads of the block call this; keys[0..n) are in shared memory.
+template <int kThreads>
 __device__ __forceinline__ void radix_select_mth(const uint32_t* keys, int n, int m, SelectScratch* sc,
                                                  uint32_t* thresh, int* n_eq_keep) {
   const int lane = threadIdx.x & 31;
   uint32_t prefix = 0, decided = 0;
   int k = m;
-  const int n_round = (n + kEvictThreads - 1) / kEvictThreads * kEvictThreads;
+  const int n_round = (n + kThreads - 1) / kThreads * kThreads;
 #pragma unroll 1
   for (int shift = 24; shift >= 0; shift -= 8) {
-    sc->hist[threadIdx.x] = 0;
+    if (threadIdx.x < 256) sc->hist[threadIdx.x] = 0;
     __syncthreads();
-    for (int i = threadIdx.x; i < n_round; i += kEvictThreads) {
+    for (int i = threadIdx.x; i < n_round; i += kThreads) {
       uint32_t key = i < n ? keys[i] : 0u;
       const bool valid = i < n && (key & decided) == prefix;
       const int digit = valid ? (int)((key >> shift) & 255u) : 256 + lane;
@@ -50,11 +52,11 @@ __device__ __forceinline__ void radix_select_mth(const uint32_t* keys, int n, in
     }
     __syncthreads();
     // Thread t looks at bin 255 - t: an exclusive scan in this order is the count of strictly larger digits.
-    const int bin = 255 - threadIdx.x;
-    const int c = sc->hist[bin];
+    const int bin = 255 - (int)threadIdx.x;
+    const int c = threadIdx.x < 256 ? sc->hist[bin] : 0;
     int total;
-    const int above = block_exclusive_scan<kEvictThreads>(c, sc->warp_sums, &total);
-    if (above < k && k <= above + c) { sc->sel_digit = bin; sc->sel_k = k - above; }
+    const int above = block_exclusive_scan<kThreads>(c, sc->warp_sums, &total);
+    if (threadIdx.x < 256 && above < k && k <= above + c) { sc->sel_digit = bin; sc->sel_k = k - above; }
     __syncthreads();
     prefix |= (uint32_t)sc->sel_digit << shift;
     decided |= 255u << shift;
@@ -66,10 +68,11 @@ __device__ __forceinline__ void radix_select_mth(const uint32_t* keys, int n, in
 }
 
 // Overwrites keys[0..m) with the ascending indices of the kept elements; returns the first evicted index.
+template <int kThreads>
 __device__ __forceinline__ int build_kept_list(uint32_t* keys, int n, uint32_t thresh, int n_eq_keep,
                                                SelectScratch* sc) {
   constexpr int kItems = 4;
-  constexpr int kChunk = kEvictThreads * kItems;
+  constexpr int kChunk = kThreads * kItems;
   if (threadIdx.x == 0) sc->first_evicted = n;
   int eq_base = 0, gt_base = 0;
 #pragma unroll 1
@@ -84,7 +87,7 @@ __device__ __forceinline__ int build_kept_list(uint32_t* keys, int n, uint32_t t
       if (i < n) packed += (key[u] == thresh) ? 1 : (key[u] > thresh ? (1 << 16) : 0);
     }
     int total;
-    const int excl = block_exclusive_scan<kEvictThreads>(packed, sc->warp_sums, &total);  // syncs inside
+    const int excl = block_exclusive_scan<kThreads>(packed, sc->warp_sums, &total);  // syncs inside
     int eq = eq_base + (excl & 0xffff), gt = gt_base + (excl >> 16);
     int my_first_evicted = n;
 #pragma unroll
@@ -114,7 +117,8 @@ struct EvictParams {
   int32_t* kept_idx_out; int32_t* status;
 };
 
-__global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParams p) {
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) {
   extern __shared__ __align__(16) uint32_t keys[];
   __shared__ SelectScratch sc;
   const int seg = blockIdx.x;
@@ -130,20 +134,20 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
     return;
   }
   const int64_t row0 = (int64_t)seg * p.cap;
-  for (int i = threadIdx.x; i < n; i += kEvictThreads)
+  for (int i = threadIdx.x; i < n; i += kThreads)
     keys[i] = i >= n - p.protect_last ? score_key(INFINITY)
                                       : score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
   __syncthreads();
   uint32_t thresh; int n_eq_keep;
-  radix_select_mth(keys, n, m, &sc, &thresh, &n_eq_keep);
-  const int j0 = build_kept_list(keys, n, thresh, n_eq_keep, &sc);
+  radix_select_mth<kThreads>(keys, n, m, &sc, &thresh, &n_eq_keep);
+  const int j0 = build_kept_list<kThreads>(keys, n, thresh, n_eq_keep, &sc);
   const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
   if (p.kept_idx_out != nullptr)
-    for (int j = threadIdx.x; j < m; j += kEvictThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
+    for (int j = threadIdx.x; j < m; j += kThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
 
   // Stable in-place compaction of rows j0..m (rows before the first evicted one stay where they are).
   const int nvec = 2 * p.row_vecs;                       // K vectors then V vectors of one token
-  const int tile_rows = min(kEvictThreads, (kEvictThreads * kEvictUnroll) / nvec);
+  const int tile_rows = min(kThreads, (kThreads * kEvictUnroll) / nvec);
   const int64_t row_bytes = (int64_t)p.row_vecs * 16;
   char* kbase = p.k + row0 * row_bytes;
   char* vbase = p.v + row0 * row_bytes;
@@ -154,7 +158,7 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
     uint4 reg[kEvictUnroll];
 #pragma unroll
     for (int u = 0; u < kEvictUnroll; ++u) {
-      const int i = threadIdx.x + u * kEvictThreads;
+      const int i = threadIdx.x + u * kThreads;
       if (i < nv) {
         const int r = i / nvec, c = i - r * nvec;
         const int src = kept[jb + r];
@@ -172,7 +176,7 @@ __global__ void __launch_bounds__(kEvictThreads) evict_inplace_kernel(EvictParam
     __syncthreads();  // every load of this tile is performed before any of its stores
 #pragma unroll
     for (int u = 0; u < kEvictUnroll; ++u) {
-      const int i = threadIdx.x + u * kEvictThreads;
+      const int i = threadIdx.x + u * kThreads;
       if (i < nv) {
         const int r = i / nvec, c = i - r * nvec;
         char* ptr = (c < p.row_vecs ? kbase + (int64_t)c * 16 : vbase + (int64_t)(c - p.row_vecs) * 16) +
@@ -214,8 +218,8 @@ __global__ void __launch_bounds__(kEvictThreads) evict_select_kernel(SelectParam
     keys[i] = score_key(retention_score(beta[i], pos[i], p.q_idx));
   __syncthreads();
   uint32_t thresh; int n_eq_keep;
-  radix_select_mth(keys, n, p.m, &sc, &thresh, &n_eq_keep);
-  build_kept_list(keys, n, thresh, n_eq_keep, &sc);
+  radix_select_mth<kEvictThreads>(keys, n, p.m, &sc, &thresh, &n_eq_keep);
+  build_kept_list<kEvictThreads>(keys, n, thresh, n_eq_keep, &sc);
   const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
   for (int j = threadIdx.x; j < p.m; j += kEvictThreads) p.kept_idx[(int64_t)seg * p.m + j] = kept[j];
   if (threadIdx.x == 0) p.kept_cnt[seg] = p.m;
@@ -329,7 +333,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   if (max_len > kMaxSelectLen)
     return fail(TKV_ERR_UNSUPPORTED, "tkv_evict: max_len=%d exceeds %d", max_len, kMaxSelectLen);
   const int64_t row_bytes = (int64_t)head_dim * es;
-  if (row_bytes % 16 != 0 || 2 * (row_bytes / 16) > kEvictThreads * kEvictUnroll)
+  if (row_bytes % 16 != 0 || 2 * (row_bytes / 16) > kEvictThreads * kEvictUnroll)  // one token must fit a tile
     return fail(TKV_ERR_ARG, "tkv_evict: unsupported row of %lld bytes", (long long)row_bytes);
   if (!aligned16(k_cache) || !aligned16(v_cache)) return fail(TKV_ERR_ARG, "tkv_evict: K/V must be 16-byte aligned");
   if (nseg == 0) return TKV_OK;
@@ -340,9 +344,14 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.keep_cnt = keep_cnt; p.protect_last = protect_last;
   p.kept_idx_out = kept_idx_out; p.status = status;
   const size_t smem = (size_t)max_len * 4;
-  int rc = set_smem(evict_inplace_kernel, smem, "tkv_evict");
+  // Long segments: the key array leaves room for at most 3 CTAs per SM, so each CTA gets twice the threads (and
+  // twice the rows in flight per tile) to keep the memory system as busy as 4 narrow CTAs do.
+  const bool wide = smem > 56 * 1024;
+  int rc = wide ? set_smem(evict_inplace_kernel<kEvictThreadsWide>, smem, "tkv_evict")
+                : set_smem(evict_inplace_kernel<kEvictThreads>, smem, "tkv_evict");
   if (rc != TKV_OK) return rc;
-  evict_inplace_kernel<<<nseg, kEvictThreads, smem, (cudaStream_t)stream>>>(p);
+  if (wide) evict_inplace_kernel<kEvictThreadsWide><<<nseg, kEvictThreadsWide, smem, (cudaStream_t)stream>>>(p);
+  else evict_inplace_kernel<kEvictThreads><<<nseg, kEvictThreads, smem, (cudaStream_t)stream>>>(p);
   rc = check_launch("tkv_evict");
   if (rc != TKV_OK) return rc;
   return launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
