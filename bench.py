@@ -27,12 +27,12 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE configs[1]: Qwen3-1.7B architecture, batch 32, 8192-token prompt, M=4096, B=128.
+    # benchmark-spec configs[1]: Qwen3-1.7B architecture, batch 32, 8192-token prompt, M=4096, B=128.
     "qwen3-1.7b-decode": dict(
         hidden_size=2048, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8, head_dim=128,
         intermediate_size=6144, vocab_size=151936, rope_theta=1e6, retention_gate_intermediate_size=128,
         retention_gate_bias_init=3.0, memory_size=4096, buffer_size=128, batch=32, prompt=8192),
-    # BASELINE configs[4] per GPU at 8 GPUs: Qwen3-14B architecture, 16 of the 128 requests, M=8192, B=256.  The prompt is
+    # benchmark-spec configs[4] per GPU at 8 GPUs: Qwen3-14B architecture, 16 of the 128 requests, M=8192, B=256.  The prompt is
     # lengthened from 1024 to M+B tokens so that the cache is saturated when decoding starts (the configured run only
     # saturates after 7424 decode steps); the timed window then covers steady-state steps and their evictions.
     "qwen3-14b-decode": dict(
@@ -184,7 +184,7 @@ def run_reference(args, wl_name, wl):
 
 
 def run_micro(args):
-    """Kernel microbenchmarks on BASELINE's kernel-level shapes (configs[2] and configs[3]); one JSON line each.
+    """Kernel microbenchmarks on the kernel-level shapes of the benchmark specification (its configs[2] and configs[3]); one JSON line each.
 
     evict : nseg segments, live lengths uniform in [M, M+B], keep top-M on every segment (forced), bf16, D=128.
     attn  : one layer of decode attention, batch x 8 KV heads, lengths lognormal(median 2048, sigma 1) in [64, 8192].
@@ -455,7 +455,7 @@ def main():
         tot_b, tot_t = sum(x for x, _ in ach), sum(t for _, t in ach)
         gbs = tot_b / tot_t / 1e9
         # dram__bytes_read+write of one ncu capture of the same two kernels at this shape (batch 32, n = 4160):
-        # 561.2 MB against 545.5 MB algorithmic (profiles/decode_attn_tc_kernel_G2_config2.md); scaled by the bytes.
+        # 561.2 MB against 545.5 MB algorithmic; scaled by the bytes.
         traffic = tot_b / len(ach) * (561.19 / 545.52) if args.workload == "qwen3-1.7b-decode" else None
         roofline = {"bound": "hbm", "kernel": "decode_attn_tc_kernel+decode_attn_combine_kernel", "achieved": gbs,
                     "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": traffic,

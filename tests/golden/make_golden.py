@@ -46,7 +46,7 @@ def import_reference(src_dir):
 
 
 def config1(cu):
-    """BASELINE config 1: batch 1, 8 KV heads, D 128, fp32, M 512, B 128, 4096 prefill + 256 steps."""
+    """Benchmark-spec configs[0]: batch 1, 8 KV heads, D 128, fp32, M 512, B 128, 4096 prefill + 256 steps."""
     torch.manual_seed(0)
     H, D, S, M, B, T = 8, 128, 4096, 512, 128, 256
     cache = cu.TrimKVCache(device="cpu")

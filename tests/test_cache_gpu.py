@@ -13,7 +13,7 @@ DEV = "cuda:0"
 
 @pytest.mark.parametrize("eager_handoff", [False, True])
 def test_config1_lockstep(golden_dir, eager_handoff):
-    """BASELINE configs[0]: batch 1, 8 KV heads, D 128, fp32, M 512, B 128, 4096-token prefill + 256 steps.
+    """benchmark-spec configs[0]: batch 1, 8 KV heads, D 128, fp32, M 512, B 128, 4096-token prefill + 256 steps.
     Kept positions at every eviction and the length after every step equal the reference's own run; K/V rows and
     log beta follow their positions."""
     from trimkv_b200 import TrimKVCache

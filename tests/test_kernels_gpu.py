@@ -193,7 +193,7 @@ def test_select_then_compact_from_dense_prompt(ops):
 
 
 def test_full_size_eviction_properties(ops):
-    """BASELINE config-3 sizes (2048 segments, M=4096, B=128): properties that need no oracle."""
+    """Benchmark-spec configs[2] sizes (2048 segments, M=4096, B=128): properties that need no oracle."""
     gen = torch.Generator(device=DEV).manual_seed(0)
     nseg, m, bsz, d = 2048, 4096, 128, 128
     cap = m + bsz
@@ -314,7 +314,7 @@ def test_consumers_accept_gemm_partials(ops):
 
 
 def test_full_size_attention_cross_check(ops):
-    """BASELINE configs[3] sizes (batch 64, 32/8 heads, lognormal lengths in [64, 8192]): the tensor-core kernel on the
+    """benchmark-spec configs[3] sizes (batch 64, 32/8 heads, lognormal lengths in [64, 8192]): the tensor-core kernel on the
     capacity-strided layout against the CUDA-core kernel on the packed copy of the same cache, plus two properties that
     need no second implementation (constant V gives that constant; the output is a convex combination of V rows)."""
     gen = torch.Generator(device=DEV).manual_seed(0)
