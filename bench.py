@@ -258,6 +258,32 @@ def run_micro(args):
                 times.append((e0, e1))
         torch.cuda.synchronize()
         alg = int(lens.long().sum()) * 4 * D + batch * hq * D * 4
+        # The library kernel the reference calls for this step (flash_attn_varlen_func on the packed cache, every
+        # (request, KV head) pair one sequence), timed the same way on the same lengths, for comparison.
+        try:
+            from flash_attn.flash_attn_interface import flash_attn_varlen_func
+            mask = (torch.arange(cap, device=dev)[None, :] < lens[:, None]).view(-1)
+            packs = [(kk[mask].unsqueeze(1).contiguous(), vv[mask].unsqueeze(1).contiguous()) for kk, vv in bufs]
+            cu_k = torch.zeros(nseg + 1, dtype=torch.int32, device=dev); cu_k[1:] = lens.cumsum(0)
+            cu_q = torch.arange(0, nseg + 1, dtype=torch.int32, device=dev)
+            pq = q.view(batch, hkv, hq // hkv, D).reshape(nseg, hq // hkv, D).contiguous()
+            mk = int(lens.max())
+            fa = []
+            for i in range(args.warmup + args.steps):
+                kp, vp = packs[i % nbuf]
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                flash_attn_varlen_func(pq, kp, vp, cu_q, cu_k, max_seqlen_q=1, max_seqlen_k=mk, causal=True)
+                e1.record()
+                if i >= args.warmup:
+                    fa.append((e0, e1))
+            torch.cuda.synchronize()
+            fa_ms = sum(a.elapsed_time(b) for a, b in fa) / len(fa)
+            res["flash_attn_varlen"] = {"avg_ms": fa_ms, "achieved_gbs": alg / (fa_ms * 1e-3) / 1e9,
+                                        "note": "kernel call only, Q already packed, max_seqlen_k precomputed"}
+            del packs
+        except Exception as e:  # wheel missing or not runnable on this GPU
+            res["flash_attn_varlen"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
                          "mean_len": float(lens.float().mean()), "buffers": nbuf, "shape": args.attn_shape}
     if args.micro in ("evict", "append") and not args.no_cpu_baseline:

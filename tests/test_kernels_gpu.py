@@ -343,3 +343,39 @@ def test_full_size_attention_cross_check(ops):
     v.fill_(0.75)
     ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, d ** -0.5, cap, status)
     assert float((out.float() - 0.75).abs().max()) <= 4e-3
+
+
+def test_decode_attention_vs_flash_attn_varlen(ops):
+    """Same-box cross-check against the library the reference calls: flash_attn_varlen_func with every
+    (request, KV head) pair as one varlen sequence of an MQA problem, causal, default softmax scale
+    (src/trimkv/attn/flash_attn.py:104-151).  Skipped where the installed wheel cannot run on this GPU."""
+    try:
+        from flash_attn.flash_attn_interface import flash_attn_varlen_func
+    except Exception as e:  # not installed / not importable
+        pytest.skip(f"flash_attn unavailable: {e}")
+    gen = torch.Generator().manual_seed(12)
+    bsz, hq, hkv, d, cap = 4, 16, 8, 128, 1500
+    g, nseg = hq // hkv, bsz * hkv
+    lens = [int(x) for x in torch.randint(1, cap + 1, (nseg,), generator=gen)]
+    q = torch.randn(bsz, hq, d, generator=gen).bfloat16().to(DEV)
+    k = torch.randn(nseg, cap, d, generator=gen).bfloat16().to(DEV)
+    v = torch.randn(nseg, cap, d, generator=gen).bfloat16().to(DEV)
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.empty(bsz, hq, d, dtype=torch.bfloat16, device=DEV)
+    ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, cap), dtype=torch.uint8, device=DEV)
+    ops.decode_attn(q, k, v, ln, None, cap, out, ws, hkv, d ** -0.5, max(lens), None)
+    # the reference's packing: sequence s = b*Hkv + h holds the G query heads of KV head h as G "heads" of one query token
+    packed_q = q.view(bsz, hkv, g, d).reshape(nseg, g, d).contiguous()
+    kp = torch.cat([k[s, :lens[s]] for s in range(nseg)]).unsqueeze(1).contiguous()
+    vp = torch.cat([v[s, :lens[s]] for s in range(nseg)]).unsqueeze(1).contiguous()
+    cu_k = torch.zeros(nseg + 1, dtype=torch.int32, device=DEV)
+    cu_k[1:] = ln.cumsum(0)
+    cu_q = torch.arange(0, nseg + 1, dtype=torch.int32, device=DEV)
+    try:
+        ref = flash_attn_varlen_func(packed_q, kp, vp, cu_q, cu_k, max_seqlen_q=1, max_seqlen_k=max(lens), dropout_p=0.0,
+                                     causal=True)
+        torch.cuda.synchronize()
+    except Exception as e:
+        pytest.skip(f"flash_attn cannot run here: {type(e).__name__}: {e}")
+    want = ref.view(bsz, hkv, g, d).reshape(bsz, hq, d)
+    assert float((out.float() - want.float()).abs().max()) <= 2e-2
