@@ -44,6 +44,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   extern __shared__ uint8_t smem_raw[];
   const int seg = blockIdx.x / p.nchunks, chunk = blockIdx.x - seg * p.nchunks;
   grid_dependency_wait();  // the lengths and the newest rows come from the preceding kernel of the stream
+  grid_launch_dependents();  // the merge kernel may be scheduled; it waits for this grid before reading partials
   const int len = min(p.seg_len[seg], p.max_len);
   const int t0 = chunk * kTcChunk;
   if (t0 >= len) {

@@ -50,6 +50,9 @@ __device__ __forceinline__ uint4 ld16_stream(const void* p) {
 // Programmatic dependent launch: a kernel launched with launch_pdl() may be scheduled while its predecessor in
 // the stream is still draining; it must call grid_dependency_wait() before touching anything the predecessor wrote.
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Lets the next kernel of the stream (if launched with launch_pdl) be scheduled now; its own grid_dependency_wait()
+// still holds it until this whole grid has finished and its writes are visible, so only its launch latency overlaps.
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args... args) {

@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   const int heads = p.hq + p.hkv;
   if (w >= p.batch * heads) return;
   grid_dependency_wait();
+  grid_launch_dependents();  // the attention kernel may be scheduled early; it waits for this grid before reading
   const int b = w / heads, head = w - b * heads;
   const bool is_q = head < p.hq;
   const int kvh = head - p.hq;
