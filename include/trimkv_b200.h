@@ -133,13 +133,16 @@ int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cach
  * keep_cnt (nullable, [nseg]): segment s keeps its keep_cnt[s] best rows (untouched if keep_cnt[s] >= its
  * length); with keep_cnt == NULL it behaves as tkv_evict.  protect_last: the newest rows always score +inf
  * (TrimKVCache.sliding_window_size, src/trimkv/cache_utils.py:186-187).  kept_stride: row stride of
- * kept_idx_out when keep counts vary.  Used after tkv_group_budget for the budget-sharing strategies.
+ * kept_idx_out when keep counts vary.  strategy: TKV_STRATEGY_ALPHA, or TKV_STRATEGY_KNORM_ALPHA to add log ||k|| to
+ * the score (src/trimkv/cache_utils.py:176-180; norm and log rounded to K's dtype as torch does).
+ * Used after tkv_group_budget for the budget-sharing strategies.
  */
+enum { TKV_STRATEGY_ALPHA = 0, TKV_STRATEGY_KNORM_ALPHA = 1 };
 int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
                  int32_t* seg_len, int32_t* cu_seqlens, int group,
                  int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                  int memory_size, int trigger_len, int max_len,
-                 const int32_t* keep_cnt, int protect_last, int kept_stride,
+                 const int32_t* keep_cnt, int protect_last, int kept_stride, int strategy,
                  int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
 
 /*

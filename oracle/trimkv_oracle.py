@@ -72,13 +72,20 @@ def canonical_topm(scores: np.ndarray, m: int) -> np.ndarray:
     return out.reshape(s.shape[:-1] + (m,))
 
 
-def compress_rows(key, value, log_beta, kv_positions, q_idx: int, m: int, sliding_window_size: int = 0):
+def compress_rows(key, value, log_beta, kv_positions, q_idx: int, m: int, sliding_window_size: int = 0,
+                  strategy: str = "alpha"):
     """One ``compress_layer`` on dense ``[..., n, D]`` / ``[..., n]`` arrays.
 
     src/trimkv/cache_utils.py:167-198, strategy "alpha"; the newest ``sliding_window_size`` rows score +inf (:186-187).
     Returns (key, value, log_beta, kv_positions, kept_idx).
     """
     sc = retention_scores(log_beta, kv_positions, q_idx)
+    if strategy == "knorm_alpha":
+        # :176-180: scores = log_alpha + log(||k||_2); fp32 keys only here (16-bit keys round norm and log to that dtype)
+        kn = np.sqrt(np.sum(np.asarray(key, np.float32) ** 2, axis=-1, dtype=np.float32))
+        sc = (sc + np.log(kn).astype(np.float32)).astype(np.float32)
+    elif strategy != "alpha":
+        raise ValueError(f"Unknown compression strategy: {strategy}")
     if sliding_window_size > 0:
         sc = sc.copy()
         sc[..., -sliding_window_size:] = np.inf
@@ -161,19 +168,19 @@ class OracleTrimKVCache:
 
     def compress(self, strategy="alpha", memory_size=2048, buffer_size=512, skip_layers=0, **_ignored):
         # cache_utils.py:140-158: trigger is evaluated per layer, after the forward.
-        if strategy != "alpha":
+        if strategy not in ("alpha", "knorm_alpha"):
             raise ValueError(f"Unknown compression strategy: {strategy}")
         for layer_idx in range(skip_layers, len(self.key_cache)):
             if memory_size + buffer_size <= self.get_cache_length(layer_idx):
-                self.compress_layer(layer_idx, memory_size)
+                self.compress_layer(layer_idx, memory_size, strategy)
 
-    def compress_layer(self, layer_idx, memory_size):
+    def compress_layer(self, layer_idx, memory_size, strategy="alpha"):
         # cache_utils.py:160-198
         q_idx = self.get_seq_length(layer_idx) + 1
         k, v, b, p, keep = compress_rows(
             self.key_cache[layer_idx], self.value_cache[layer_idx],
             self.retention_weights[layer_idx], self.kv_positions[layer_idx], q_idx, memory_size,
-            self.sliding_window_size)
+            self.sliding_window_size, strategy)
         self.key_cache[layer_idx] = k
         self.value_cache[layer_idx] = v
         self.retention_weights[layer_idx] = b

@@ -166,6 +166,27 @@ def sliding_window(cu):
     print("sliding_window: evictions", len(pos))
 
 
+def knorm_alpha(cu):
+    """TrimKVCache with strategy "knorm_alpha" on fp32 keys of widely varying norm."""
+    torch.manual_seed(8)
+    Bt, H, D, S, M, B, T = 2, 2, 32, 60, 20, 5, 15
+    cache = cu.TrimKVCache(device="cpu")
+    logb = F.logsigmoid(torch.randn(Bt, H, S + T) * 1.5 + 3.0)
+    keys = torch.randn(Bt, H, S + T, D) * torch.exp(torch.randn(Bt, H, S + T, 1))
+    pos = []
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        cache.update(keys[:, :, lo:hi].contiguous(), keys[:, :, lo:hi].contiguous() * 0.5, logb[:, :, lo:hi].contiguous(),
+                     torch.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(strategy="knorm_alpha", memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            pos.append(cache.kv_positions[0].numpy().astype(np.int32).copy())
+    np.savez_compressed(os.path.join(HERE, "knorm_alpha.npz"), log_beta=logb.numpy(), keys=keys.numpy(),
+                        kept_positions=np.stack(pos), M=M, B=B, S=S, T=T)
+    print("knorm_alpha: evictions", len(pos))
+
+
 def flat_budget(cu):
     """Budget-sharing compress of the two flat cache classes (fp32 tensors, so scores are fp32 as on the CUDA path)."""
     L, B, H, D, S, T, M, Bf = 2, 2, 3, 4, 40, 30, 8, 4
@@ -222,5 +243,6 @@ if __name__ == "__main__":
     ties_single_shot(cu_)
     flat_layout(cu_)
     sliding_window(cu_)
+    knorm_alpha(cu_)
     flat_budget(cu_)
     eager_attention(ea_)

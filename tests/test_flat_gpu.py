@@ -114,3 +114,26 @@ def test_group_budget_large_group_vs_oracle():
     want = orc._group_keep_counts(sc, k_total=k_total)
     assert keep.cpu().view(-1).tolist() == want
     assert sum(want) == k_total
+
+
+def test_knorm_alpha_matches_reference(golden_dir):
+    """strategy="knorm_alpha" on fp32 keys: kept positions equal the reference's at every eviction."""
+    from trimkv_b200 import TrimKVCache
+    g = _g(golden_dir, "knorm_alpha.npz")
+    M, B, S, T = (int(g[k]) for k in "MBST")
+    logb, keys = torch.from_numpy(g["log_beta"]).to(DEV), torch.from_numpy(g["keys"]).to(DEV)
+    cache = TrimKVCache(device=DEV)
+    ev = 0
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        cache.update(keys[:, :, lo:hi].contiguous(), (keys[:, :, lo:hi] * 0.5).contiguous(), logb[:, :, lo:hi].contiguous(),
+                     torch.arange(lo, hi, device=DEV), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(strategy="knorm_alpha", memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            pos = cache.kv_positions[0]
+            assert np.array_equal(pos.cpu().numpy(), g["kept_positions"][ev]), t
+            assert torch.equal(cache.key_cache[0], torch.gather(keys, 2, pos.long().unsqueeze(-1).expand(-1, -1, -1, keys.shape[-1])))
+            ev += 1
+    cache.check_status()
+    assert ev == g["kept_positions"].shape[0]

@@ -174,3 +174,20 @@ def test_sliding_window_protects_newest_rows(golden_dir):
             assert np.array_equal(cache.kv_positions[0].astype(np.int32), g["kept_positions"][ev])
             ev += 1
     assert ev == g["kept_positions"].shape[0] and ev >= 2
+
+
+def test_knorm_alpha_strategy(golden_dir):
+    g = _load(golden_dir, "knorm_alpha.npz")
+    M, B, S, T = (int(g[k]) for k in "MBST")
+    logb, keys = g["log_beta"], g["keys"]
+    cache = orc.OracleTrimKVCache()
+    ev = 0
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        cache.update(keys[:, :, lo:hi], keys[:, :, lo:hi] * 0.5, logb[:, :, lo:hi], np.arange(lo, hi), 0)
+        before = cache.get_cache_length(0)
+        cache.compress(strategy="knorm_alpha", memory_size=M, buffer_size=B)
+        if cache.get_cache_length(0) != before:
+            assert np.array_equal(cache.kv_positions[0].astype(np.int32), g["kept_positions"][ev])
+            ev += 1
+    assert ev == g["kept_positions"].shape[0] and ev >= 2

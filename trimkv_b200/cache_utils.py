@@ -74,6 +74,7 @@ class TrimKVCache:
         # top-M rows as soon as that layer's update() is called (the caller still attends over its own dense tensors),
         # instead of keeping the prompt K/V of every layer alive until compress().  Same survivors either way.
         self._hint_layers = num_layers
+        self.defer_handoff = False   # set when compress() will be called with a strategy that needs the keys (knorm_alpha)
 
         self._pending: List[Optional[Tuple[torch.Tensor, ...]]] = []  # per layer: dense prompt (K, V, beta, pos)
         self._cache_len: List[int] = []                               # per layer: live rows per segment
@@ -241,7 +242,7 @@ class TrimKVCache:
         return self.key_cache[layer_idx], self.value_cache[layer_idx], self._attn_kwargs(layer_idx)
 
     def _eager_handoff(self, layer_idx: int) -> bool:
-        return (type(self) is TrimKVCache and self._hint_m is not None and self._hint_b is not None
+        return (type(self) is TrimKVCache and not self.defer_handoff and self._hint_m is not None and self._hint_b is not None
                 and self._hint_layers is not None and layer_idx < self._hint_layers and not self.sliding_window_size
                 and all(p is None for p in self._pending))
 
@@ -351,20 +352,20 @@ class TrimKVCache:
         num_key_value_heads: Optional[int] = None,
         skip_layers: int = 0,
     ):
-        if strategy != "alpha":
-            if strategy == "knorm_alpha":
-                raise NotImplementedError("compress strategy 'knorm_alpha' is not built on the CUDA path")
+        if strategy not in ("alpha", "knorm_alpha"):
             raise ValueError(f"Unknown compression strategy: {strategy}")
+        knorm = strategy == "knorm_alpha"
         num_layers = len(self) if num_layers is None else num_layers
         if num_layers == 0:
             return
         if any(p is not None for p in self._pending):
             if skip_layers:
                 raise NotImplementedError("skip_layers with a pending prompt")
-            if not self.sliding_window_size:
+            if not self.sliding_window_size and not knorm:
                 self._materialise(memory_size=memory_size, buffer_size=buffer_size)
                 return
-            # A protected tail is only known to the in-place kernel: home the whole prompt, then evict below.
+            # A protected tail and the key norms are only known to the in-place kernel: home the whole prompt, then
+            # evict below.
             self._hint_m = self._hint_b = None
             self._materialise(extra=max(64, buffer_size))
         w = int(self.sliding_window_size)
@@ -384,7 +385,7 @@ class TrimKVCache:
             if self.record_kept:
                 kept = torch.empty(nl * nseg, memory_size, dtype=torch.int32, device=s["k"].device)
             ops.evict_ex(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap,
-                         self.n_seen_tokens[0] + 1, n, None, w, memory_size, trigger, kept, 0, self._status)
+                         self.n_seen_tokens[0] + 1, n, None, w, memory_size, trigger, kept, 0, self._status, knorm)
             if kept is not None:
                 self.last_kept_idx = kept.view(nl, self._batch, self._hkv, memory_size)
         else:
@@ -393,7 +394,7 @@ class TrimKVCache:
                     kept = torch.empty(nseg, memory_size, dtype=torch.int32, device=s["k"].device)
                 ops.evict_ex(s["k"][l], s["v"][l], s["beta"][l], s["pos"][l], s["len"][l], s["cu"][l], nseg, nseg,
                              self._cap, self.n_seen_tokens[l] + 1, self._cache_len[l], None, w, memory_size, trigger,
-                             kept, 0, self._status)
+                             kept, 0, self._status, knorm)
                 if kept is not None:
                     self.last_kept_idx = kept.view(self._batch, self._hkv, memory_size)
         for l in fire:

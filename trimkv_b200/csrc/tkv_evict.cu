@@ -114,6 +114,7 @@ struct EvictParams {
   int m, trigger_len, max_len;
   const int32_t* keep_cnt;   // per-segment number of rows to keep (NULL: m for every segment at or above trigger_len)
   int protect_last;          // the newest `protect_last` rows always score +inf (sliding window)
+  int knorm, kv_dtype;       // knorm: score += log ||k||  (strategy "knorm_alpha")
   int32_t* kept_idx_out; int32_t* status;
 };
 
@@ -134,9 +135,47 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
     return;
   }
   const int64_t row0 = (int64_t)seg * p.cap;
-  for (int i = threadIdx.x; i < n; i += kThreads)
-    keys[i] = i >= n - p.protect_last ? score_key(INFINITY)
-                                      : score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+  if (p.knorm) {
+    // strategy "knorm_alpha" (src/trimkv/cache_utils.py:176-180): score = log_alpha + log(||k||), the norm and its
+    // log taken in the dtype of K as torch does (fp32 accumulation, one rounding each for 16-bit K).  A warp per
+    // row: lanes stride over the row's 16-byte vectors.
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const char* kb = p.k + row0 * (int64_t)p.row_vecs * 16;
+    for (int i = warp; i < n; i += kThreads / 32) {
+      float ss = 0.f;
+      for (int c = lane; c < p.row_vecs; c += 32) {
+        const uint4 v = ld16(kb + ((int64_t)i * p.row_vecs + c) * 16);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (p.kv_dtype == TKV_F32) { const float a = __uint_as_float(w[j]); ss = fmaf(a, a, ss); }
+          else if (p.kv_dtype == TKV_BF16) {
+            const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+            ss = fmaf(a, a, ss); ss = fmaf(b, b, ss);
+          } else {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+            ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+          }
+        }
+      }
+#pragma unroll
+      for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      if (lane == 0) {
+        float nrm = sqrtf(ss);
+        if (p.kv_dtype == TKV_BF16) nrm = __bfloat162float(__float2bfloat16_rn(nrm));
+        else if (p.kv_dtype == TKV_F16) nrm = __half2float(__float2half_rn(nrm));
+        float lg = logf(nrm);
+        if (p.kv_dtype == TKV_BF16) lg = __bfloat162float(__float2bfloat16_rn(lg));
+        else if (p.kv_dtype == TKV_F16) lg = __half2float(__float2half_rn(lg));
+        const float sc_ = __fadd_rn(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx), lg);
+        keys[i] = i >= n - p.protect_last ? score_key(INFINITY) : score_key(sc_);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < n; i += kThreads)
+      keys[i] = i >= n - p.protect_last ? score_key(INFINITY)
+                                        : score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+  }
   __syncthreads();
   uint32_t thresh; int n_eq_keep;
   radix_select_mth<kThreads>(keys, n, m, &sc, &thresh, &n_eq_keep);
@@ -321,12 +360,13 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
                       int32_t* seg_len, int32_t* cu_seqlens, int group,
                       int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                       int memory_size, int trigger_len, int max_len, const int32_t* keep_cnt, int protect_last,
-                      int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+                      int strategy, int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   const int es = elem_size(kv_dtype);
   if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
   if (!k_cache || !v_cache || !beta_cache || !pos_cache || !seg_len)
     return fail(TKV_ERR_ARG, "tkv_evict: NULL pointer argument");
+  if (strategy != 0 && strategy != 1) return fail(TKV_ERR_ARG, "tkv_evict: unknown strategy %d", strategy);
   if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0 || protect_last < 0)
     return fail(TKV_ERR_ARG, "tkv_evict: bad sizes nseg=%d cap=%lld head_dim=%d M=%d max_len=%d", nseg,
                 (long long)cap, head_dim, memory_size, max_len);
@@ -341,7 +381,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.k = (char*)k_cache; p.v = (char*)v_cache; p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len;
   p.nseg = nseg; p.cap = cap; p.row_vecs = (int)(row_bytes / 16); p.q_idx = q_idx;
   p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
-  p.keep_cnt = keep_cnt; p.protect_last = protect_last;
+  p.keep_cnt = keep_cnt; p.protect_last = protect_last; p.knorm = strategy; p.kv_dtype = kv_dtype;
   p.kept_idx_out = kept_idx_out; p.status = status;
   const size_t smem = (size_t)max_len * 4;
   // Long segments: the key array leaves room for at most 3 CTAs per SM, so each CTA gets twice the threads (and
@@ -363,19 +403,19 @@ extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_
                          int memory_size, int trigger_len, int max_len,
                          int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
   return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
-                    q_idx, memory_size, trigger_len, max_len, nullptr, 0, kept_idx_out, status, stream);
+                    q_idx, memory_size, trigger_len, max_len, nullptr, 0, 0, kept_idx_out, status, stream);
 }
 
 extern "C" int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
                             int32_t* seg_len, int32_t* cu_seqlens, int group,
                             int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                             int memory_size, int trigger_len, int max_len,
-                            const int32_t* keep_cnt, int protect_last, int kept_stride,
+                            const int32_t* keep_cnt, int protect_last, int kept_stride, int strategy,
                             int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
   // kept_stride doubles as the row stride of kept_idx_out when keep counts vary per segment.
   return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
                     q_idx, keep_cnt != nullptr ? (kept_stride > 0 ? kept_stride : 1) : memory_size, trigger_len, max_len,
-                    keep_cnt, protect_last, kept_idx_out, status, stream);
+                    keep_cnt, protect_last, strategy, kept_idx_out, status, stream);
 }
 
 extern "C" int tkv_evict_select(const float* beta, int64_t beta_stride, const int32_t* pos, int64_t pos_stride,

@@ -269,7 +269,8 @@ class TrimKVQwen3ForCausalLM(nn.Module):
         """Greedy decoding; returns ``[B, prompt + new]`` token ids like HF ``generate``."""
         if past_key_values is None:
             hints = dict(memory_size=self.config.memory_size, buffer_size=self.config.buffer_size,
-                         num_layers=self.config.num_hidden_layers) if self.config.compress_memory else {}
+                         num_layers=self.config.num_hidden_layers) \
+                if (self.config.compress_memory and self.config.compress_strategy == "alpha") else {}
             past_key_values = TrimKVCache(max_seq_len=self.config.max_seq_len, device=input_ids.device, **hints)
         out = self(input_ids=input_ids, past_key_values=past_key_values, logits_to_keep=1)
         tokens = [input_ids]

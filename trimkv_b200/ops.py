@@ -195,13 +195,14 @@ def skinny_gemm(x, w, partial, status=None) -> int:
 
 def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
              q_idx: int, max_len: int, keep_cnt, protect_last: int = 0, memory_size: int = 1, trigger_len: int = 0,
-             kept_idx_out=None, kept_stride: int = 0, status=None) -> None:
+             kept_idx_out=None, kept_stride: int = 0, status=None, knorm: bool = False) -> None:
     """In-place eviction with a keep count per segment (``keep_cnt`` int32 ``[nseg]``) and/or a protected tail."""
     d = k_cache.shape[-1]
     rc = lib().tkv_evict_ex(
         k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
         seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
-        memory_size, trigger_len, max_len, _ptr(keep_cnt), protect_last, kept_stride, _ptr(kept_idx_out),
+        memory_size, trigger_len, max_len, _ptr(keep_cnt), protect_last, kept_stride, 1 if knorm else 0,
+        _ptr(kept_idx_out),
         _ptr(status), _stream(k_cache))
     check(rc, "tkv_evict_ex")
     _count(1 if cu_seqlens is None else 2)
