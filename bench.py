@@ -362,8 +362,12 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
-    from trimkv_b200 import TrimKVCache, attn as tkv_attn, ops
+    from trimkv_b200 import TrimKVCache, attn as tkv_attn, build as tkv_build, ops
     from trimkv_b200.decoder import GreedyDecoder
+    if not os.path.exists(tkv_build.LIB) and local == 0:
+        tkv_build.build()      # the library normally ships prebuilt; compile it where only the sources arrived
+    if world > 1:
+        dist.barrier()
     ops.lib()
 
     model, cfg = build_model(wl, dev)
