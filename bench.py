@@ -199,6 +199,40 @@ def run_micro(args):
     D, M, Bf, nseg = 128, args.M, 128, args.nseg
     res = {"micro": args.micro, "steps": args.steps, "warmup": args.warmup, "peak": peak, "peak_source": peak_src}
     times = []
+    if args.micro == "steady":
+        # Triggered steady state: every step appends one token to every segment, then evicts only the segments that
+        # reached M+B (lengths start uniform in [M, M+B), so about 1/B of them fire per step).  Amortised per step.
+        cap = M + Bf
+        k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        beta = torch.nn.functional.logsigmoid(torch.randn(nseg * cap, generator=g, device=dev) * 1.5 + 3).bfloat16().float()
+        pos = torch.sort(torch.rand(nseg, 4 * M, generator=g, device=dev).argsort(-1)[:, :cap], -1)[0].to(torch.int32).view(-1)
+        ln = torch.randint(M, cap, (nseg,), generator=g, device=dev, dtype=torch.int32)
+        cu = torch.zeros(nseg + 1, dtype=torch.int32, device=dev)
+        ops.rebuild_cu_seqlens(ln, cu, nseg, nseg)
+        status = ops.new_status(dev)
+        kn = torch.randn(nseg // 8, 8, 1, D, generator=g, device=dev, dtype=torch.bfloat16)
+        bn = torch.full((nseg // 8, 8, 1), -0.05, device=dev, dtype=torch.bfloat16)
+        fired_t = torch.zeros((), dtype=torch.int64, device=dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for i in range(args.warmup + args.steps):
+            if i == args.warmup:
+                torch.cuda.synchronize(); e0.record()
+            pn = torch.full((1,), 4 * M + i, device=dev, dtype=torch.int64)
+            ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
+            if i >= args.warmup:
+                fired_t += (ln >= cap).sum()         # counted on the device; read once after the loop
+            ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + i + 1, M, cap, cap, None, status)
+        e1.record(); torch.cuda.synchronize()
+        assert ops.read_status(status) == 0
+        ms = e0.elapsed_time(e1) / args.steps
+        fired = int(fired_t)
+        alg = nseg * 2 * 520 + fired / args.steps * (8 * cap + 1032 * M)
+        res.update({"config": {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16"},
+                    "segments_evicted_per_step": fired / args.steps, "algorithmic_bytes_per_step": alg, "avg_ms_per_step": ms,
+                    "achieved_gbs": alg / (ms * 1e-3) / 1e9, "frac_of_peak": alg / (ms * 1e-3) / 1e9 / peak})
+        print(json.dumps(res))
+        return
     if args.micro in ("evict", "append"):
         cap = M + Bf
         nbuf = max(2, min(4, int(2e9 // (nseg * cap * 512)) or 2)) if args.micro == "evict" else 1
@@ -319,7 +353,7 @@ def run_micro(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append"],
+    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
