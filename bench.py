@@ -21,6 +21,7 @@ import sys
 import threading
 import time
 
+import numpy as np
 import torch
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -199,6 +200,8 @@ def run_micro(args):
     D, M, Bf, nseg = 128, args.M, 128, args.nseg
     res = {"micro": args.micro, "steps": args.steps, "warmup": args.warmup, "peak": peak, "peak_source": peak_src}
     times = []
+    ws = ops.evict_multi_workspace(nseg, M, args.ctas, dev) if args.ctas > 1 else None
+    res["ctas_per_segment"] = args.ctas
     if args.micro == "steady":
         # Triggered steady state: every step appends one token to every segment, then evicts only the segments that
         # reached M+B (lengths start uniform in [M, M+B), so about 1/B of them fire per step).  Amortised per step.
@@ -213,20 +216,28 @@ def run_micro(args):
         status = ops.new_status(dev)
         kn = torch.randn(nseg // 8, 8, 1, D, generator=g, device=dev, dtype=torch.bfloat16)
         bn = torch.full((nseg // 8, 8, 1), -0.05, device=dev, dtype=torch.bfloat16)
-        fired_t = torch.zeros((), dtype=torch.int64, device=dev)
+        # The firing pattern is known on the host (every length grows by one and falls back to M at M+B), so the timed
+        # loop holds nothing but the two launches per step.
+        ln_host, fired = ln.cpu().numpy().astype(np.int64), 0
+        pns = [torch.full((1,), 4 * M + i, device=dev, dtype=torch.int64) for i in range(args.warmup + args.steps)]
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         for i in range(args.warmup + args.steps):
             if i == args.warmup:
                 torch.cuda.synchronize(); e0.record()
-            pn = torch.full((1,), 4 * M + i, device=dev, dtype=torch.int64)
-            ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
+            ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pns[i], cap, status)
+            ln_host += 1
             if i >= args.warmup:
-                fired_t += (ln >= cap).sum()         # counted on the device; read once after the loop
-            ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + i + 1, M, cap, cap, None, status)
+                fired += int((ln_host >= cap).sum())
+            ln_host[ln_host >= cap] = M
+            if args.ctas > 1:
+                ops.evict_multi(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + i + 1, M, cap, cap, args.ctas, ws,
+                                status=status)
+            else:
+                ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + i + 1, M, cap, cap, None, status)
         e1.record(); torch.cuda.synchronize()
         assert ops.read_status(status) == 0
+        assert np.array_equal(ln.cpu().numpy(), ln_host)
         ms = e0.elapsed_time(e1) / args.steps
-        fired = int(fired_t)
         alg = nseg * 2 * 520 + fired / args.steps * (8 * cap + 1032 * M)
         res.update({"config": {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16"},
                     "segments_evicted_per_step": fired / args.steps, "algorithmic_bytes_per_step": alg, "avg_ms_per_step": ms,
@@ -256,7 +267,11 @@ def run_micro(args):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             if args.micro == "evict":
-                ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, None, status)
+                if args.ctas > 1:
+                    ops.evict_multi(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, args.ctas, ws,
+                                    status=status)
+                else:
+                    ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, None, status)
             else:
                 ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
             e1.record()
@@ -358,6 +373,7 @@ def main():
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--nseg", type=int, default=2048)
+    ap.add_argument("--ctas", type=int, default=1, help="CTAs sharing one segment in the eviction microbenchmarks")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)

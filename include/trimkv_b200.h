@@ -146,6 +146,23 @@ int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_c
                  int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
 
 /*
+ * tkv_evict with ctas_per_segment CTAs sharing the rows of each evicting segment (same result, bit for bit).
+ * For calls in which few segments evict at once (one request, or a steady state in which each segment fires once
+ * every buffer_size steps), where one CTA per segment would leave most SMs idle; same reference code as tkv_evict
+ * (src/trimkv/cache_utils.py:140-198).  Requires max_len - memory_size rows of K+V to fit in shared memory
+ * (<= 200 KB) and ctas_per_segment <= 32.  workspace: device scratch of tkv_evict_multi_workspace_bytes() bytes,
+ * contents irrelevant before and after the call; one workspace serves one stream at a time.
+ * ctas_per_segment == 1 is tkv_evict_ex without keep counts.
+ */
+int64_t tkv_evict_multi_workspace_bytes(int nseg, int memory_size, int ctas_per_segment);
+int tkv_evict_multi(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                    int32_t* seg_len, int32_t* cu_seqlens, int group,
+                    int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                    int memory_size, int trigger_len, int max_len, int protect_last, int strategy,
+                    int ctas_per_segment, void* workspace, int64_t workspace_bytes,
+                    int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
+
+/*
  * Keep counts under a shared token budget.  Group g consists of the segments
  * {g*inner + o*outer_stride + i : o < n_outer, i < inner}; among all rows of a group the k_total best scores are
  * kept (ties: lower index in that concatenated order), or, with use_threshold, every row whose score is

@@ -113,8 +113,38 @@ CASES = [
 ]
 
 
+def _tail_heavy_logbeta(gen, *shape):
+    """The newest rows score lowest: the kept rows are a prefix and nothing has to move."""
+    b = torch.full(shape, -0.001)
+    b[..., -40:] = -50.0
+    return b
+
+
+MULTI_CASES = [
+    # nseg, cap, d, M, trigger, lens-spec, dtype, beta generator, CTAs per segment
+    (8, 640, 128, 512, 640, "full", torch.float32, _logbeta, 4),
+    (6, 384, 128, 256, 320, "ragged", torch.bfloat16, _bf16_logbeta, 3),
+    (5, 133, 64, 100, 101, "ragged", torch.bfloat16, _coarse_logbeta, 8),     # ranges shorter than a tile
+    (1, 130, 128, 129, 130, "full", torch.bfloat16, _bf16_logbeta, 2),
+    (2, 4224, 128, 4096, 4224, "full", torch.bfloat16, _bf16_logbeta, 16),
+    (3, 4224, 128, 4096, 4224, "full", torch.bfloat16, _coarse_logbeta, 5),
+    (3, 2100, 64, 2000, 2001, "ragged", torch.float16, _coarse_logbeta, 7),
+    (4, 1064, 128, 1024, 1064, "full", torch.bfloat16, _tail_heavy_logbeta, 4),  # kept rows are a prefix
+    (2, 16512, 128, 16384, 16512, "full", torch.bfloat16, _bf16_logbeta, 32),
+]
+
+
+@pytest.mark.parametrize("nseg,cap,d,m,trigger,spec,dtype,beta_fn,ctas", MULTI_CASES)
+def test_evict_with_several_ctas_per_segment_bit_exact(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn, ctas):
+    _evict_case(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn, ctas)
+
+
 @pytest.mark.parametrize("nseg,cap,d,m,trigger,spec,dtype,beta_fn", CASES)
 def test_evict_inplace_bit_exact(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn):
+    _evict_case(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn, 1)
+
+
+def _evict_case(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn, ctas):
     gen = torch.Generator().manual_seed(11)
     if spec == "full":
         lens = [cap] * nseg
@@ -126,7 +156,13 @@ def test_evict_inplace_bit_exact(ops, nseg, cap, d, m, trigger, spec, dtype, bet
     status = ops.new_status(DEV)
     kept = torch.full((nseg, m), -1, dtype=torch.int32, device=DEV)
     q_idx = step + 1
-    ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, trigger, cap, kept, status)
+    if ctas == 1:
+        ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, trigger, cap, kept, status)
+    else:
+        ws = ops.evict_multi_workspace(nseg, m, ctas, DEV)
+        ws.fill_(0x5a5a5a5a)                       # the call must not depend on what the scratch holds
+        ops.evict_multi(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, trigger, cap, ctas, ws,
+                        kept_idx_out=kept, status=status)
     assert ops.read_status(status) == 0
     new_len = ln.cpu().numpy()
     kk = k.view(nseg, cap, d).float().cpu().numpy()

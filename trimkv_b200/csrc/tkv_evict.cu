@@ -17,12 +17,15 @@ namespace tkv {
 
 constexpr int kEvictThreads = 256;
 constexpr int kEvictUnroll = 8;              // 16-byte vectors in flight per thread and tile
+constexpr int kEvictMaxCtas = 32;            // CTAs sharing one segment's rows (tkv_evict_multi)
 constexpr int kMaxSelectLen = 57000;         // keys must fit in 227 KB of shared memory
 
 constexpr int kEvictThreadsWide = 512;       // for long segments, whose key array allows fewer CTAs per SM
+constexpr int kMoveThreads = 256;            // evict_move_kernel: its staging area limits CTAs per SM, so each is wide
+constexpr int kEvictThreadsPlan = 1024;      // selection only (plan mode): few segments, so each gets a full CTA
 struct SelectScratch {
   int hist[256];
-  int warp_sums[kEvictThreadsWide / 32 + 1];
+  int warp_sums[kEvictThreadsPlan / 32 + 1];
   int sel_digit;
   int sel_k;
   int first_evicted;
@@ -107,6 +110,50 @@ __device__ __forceinline__ int build_kept_list(uint32_t* keys, int n, uint32_t t
   return sc->first_evicted;
 }
 
+// Which (row of the tile, 16-byte column of the K|V row pair) vector number u of this thread is.  Vector i = tid +
+// u*kThreads of a tile is row i / nvec, column i % nvec; when nvec divides the block size the column is fixed per
+// thread and the row advances by a constant, which saves two integer divisions per 16 bytes moved.
+struct TileMap {
+  int r0, col0, rstep, nvec, regular;
+  const char* cbase;   // address of this thread's column in row 0 of the segment (regular case)
+};
+template <int kThreads>
+__device__ __forceinline__ TileMap make_tile_map(int nvec, int row_vecs, const char* kbase, const char* vbase) {
+  TileMap t;
+  t.nvec = nvec; t.regular = (kThreads % nvec) == 0;
+  t.r0 = threadIdx.x / nvec; t.col0 = threadIdx.x - t.r0 * nvec; t.rstep = kThreads / nvec;
+  t.cbase = t.col0 < row_vecs ? kbase + (int64_t)t.col0 * 16 : vbase + (int64_t)(t.col0 - row_vecs) * 16;
+  return t;
+}
+template <int kThreads>
+__device__ __forceinline__ int tile_row(const TileMap& t, int u) {
+  return t.regular ? t.r0 + u * t.rstep : (int)(threadIdx.x + u * kThreads) / t.nvec;
+}
+template <int kThreads>
+__device__ __forceinline__ int tile_col(const TileMap& t, int u, int r) {
+  return t.regular ? t.col0 : (int)(threadIdx.x + u * kThreads) - r * t.nvec;
+}
+template <int kThreads>
+__device__ __forceinline__ char* tile_ptr(const TileMap& t, int u, int r, int row, int64_t row_bytes, int row_vecs,
+                                          const char* kbase, const char* vbase) {
+  if (t.regular) return const_cast<char*>(t.cbase) + (int64_t)row * row_bytes;
+  const int col = (int)(threadIdx.x + u * kThreads) - r * t.nvec;
+  return const_cast<char*>(col < row_vecs ? kbase + (int64_t)col * 16 : vbase + (int64_t)(col - row_vecs) * 16) +
+         (int64_t)row * row_bytes;
+}
+
+// Destination rows [lo, hi) of CTA c when `ctas` CTAs share rows [j0, m) of a segment.  A range is a whole number of
+// tiles and at least as long as the largest displacement (<= tail_max, which the host derives from max_len - M), so
+// that no CTA reads beyond its right neighbour's range; short segments simply use fewer of the CTAs.
+__device__ __forceinline__ void move_range(int m, int j0, int ctas, int tail_max, int tile_rows, int c, int* lo, int* hi,
+                                           int* per_out) {
+  const int total = max(m - j0, 0);
+  const int per = max(((total + ctas - 1) / ctas + tile_rows - 1) / tile_rows, (tail_max + tile_rows - 1) / tile_rows) * tile_rows;
+  *lo = min(m, j0 + c * per);
+  *hi = min(m, *lo + per);
+  *per_out = per;
+}
+
 struct EvictParams {
   char* k; char* v; float* beta; int32_t* pos;
   int32_t* seg_len;
@@ -116,6 +163,10 @@ struct EvictParams {
   int protect_last;          // the newest `protect_last` rows always score +inf (sliding window)
   int knorm, kv_dtype;       // knorm: score += log ||k||  (strategy "knorm_alpha")
   int32_t* kept_idx_out; int32_t* status;
+  // Plan mode (several CTAs per segment move the rows afterwards): the kept list and {rows kept, first row that
+  // moves} go to global memory and nothing is moved here.
+  int32_t* plan; int32_t* plan_kept; int64_t plan_stride;
+  int32_t* plan_tail; int ctas, tail_max;   // plan_tail[seg, c]: first row of CTA c's range that it must stage
 };
 
 template <int kThreads>
@@ -183,6 +234,23 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
   const int32_t* kept = reinterpret_cast<const int32_t*>(keys);
   if (p.kept_idx_out != nullptr)
     for (int j = threadIdx.x; j < m; j += kThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
+  if (p.plan != nullptr) {
+    for (int j = j0 + threadIdx.x; j < m; j += kThreads) p.plan_kept[(int64_t)seg * p.plan_stride + j] = kept[j];
+    if (threadIdx.x == 0) { p.plan[2 * seg] = m; p.plan[2 * seg + 1] = min(j0, m); }
+    if ((int)threadIdx.x < p.ctas) {
+      // First row of the range whose source the right neighbour may overwrite (kept is ascending).  The last CTA
+      // with rows has no such neighbour: sources at or beyond m are written by nobody.
+      const int nvec2 = 2 * p.row_vecs;
+      int lo, hi, per;
+      move_range(m, min(j0, m), p.ctas, p.tail_max, min(kMoveThreads, (kMoveThreads * kEvictUnroll) / nvec2),
+                 threadIdx.x, &lo, &hi, &per);
+      int a = lo, b = hi;
+      if (hi < m) while (a < b) { const int mid = (a + b) >> 1; if (kept[mid] >= hi) b = mid; else a = mid + 1; }
+      else a = hi;
+      p.plan_tail[(int64_t)seg * p.ctas + threadIdx.x] = a;
+    }
+    return;
+  }
 
   // Stable in-place compaction of rows j0..m (rows before the first evicted one stay where they are).
   const int nvec = 2 * p.row_vecs;                       // K vectors then V vectors of one token
@@ -190,21 +258,15 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
   const int64_t row_bytes = (int64_t)p.row_vecs * 16;
   char* kbase = p.k + row0 * row_bytes;
   char* vbase = p.v + row0 * row_bytes;
+  const TileMap tm = make_tile_map<kThreads>(nvec, p.row_vecs, kbase, vbase);
 #pragma unroll 1
   for (int jb = j0; jb < m; jb += tile_rows) {
     const int rows = min(tile_rows, m - jb);
-    const int nv = rows * nvec;
     uint4 reg[kEvictUnroll];
 #pragma unroll
     for (int u = 0; u < kEvictUnroll; ++u) {
-      const int i = threadIdx.x + u * kThreads;
-      if (i < nv) {
-        const int r = i / nvec, c = i - r * nvec;
-        const int src = kept[jb + r];
-        const char* ptr = (c < p.row_vecs ? kbase + (int64_t)c * 16 : vbase + (int64_t)(c - p.row_vecs) * 16) +
-                          (int64_t)src * row_bytes;
-        reg[u] = ld16(ptr);
-      }
+      const int r = tile_row<kThreads>(tm, u);
+      if (r < rows) reg[u] = ld16(tile_ptr<kThreads>(tm, u, r, kept[jb + r], row_bytes, p.row_vecs, kbase, vbase));
     }
     float bt = 0.f; int32_t ps = 0;
     if (threadIdx.x < rows) {
@@ -215,13 +277,8 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
     __syncthreads();  // every load of this tile is performed before any of its stores
 #pragma unroll
     for (int u = 0; u < kEvictUnroll; ++u) {
-      const int i = threadIdx.x + u * kThreads;
-      if (i < nv) {
-        const int r = i / nvec, c = i - r * nvec;
-        char* ptr = (c < p.row_vecs ? kbase + (int64_t)c * 16 : vbase + (int64_t)(c - p.row_vecs) * 16) +
-                    (int64_t)(jb + r) * row_bytes;
-        st16(ptr, reg[u]);
-      }
+      const int r = tile_row<kThreads>(tm, u);
+      if (r < rows) st16(tile_ptr<kThreads>(tm, u, r, jb + r, row_bytes, p.row_vecs, kbase, vbase), reg[u]);
     }
     if (threadIdx.x < rows) {
       p.beta[row0 + jb + threadIdx.x] = bt;
@@ -229,6 +286,156 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
     }
   }
   if (threadIdx.x == 0) p.seg_len[seg] = m;
+}
+
+// ---- Several CTAs per segment -------------------------------------------------------------------------------------
+// When few segments evict at once (one request, or the steady state where a segment fires every B steps), one CTA
+// per segment leaves most SMs idle while each firing segment moves megabytes alone.  Here the selection runs first
+// (evict_inplace_kernel in plan mode) and `ctas` CTAs then share the rows of one segment: CTA c owns destination
+// rows [lo_c, hi_c).  Row j comes from kept[j] >= j, and kept[j] - j never exceeds the rows evicted, so CTA c reads
+// rows in [lo_c, hi_c + E) and writes [lo_c, hi_c): the only conflict is with its right neighbour, whose
+// destinations cover the last sources of CTA c.  Order of work in each CTA:
+//   1. stage the "tail" (rows whose source lies at or beyond hi_c; at most E of them) in shared memory;
+//   2. raise flag[c] (release): the neighbour may now overwrite those sources;
+//   3. wait for flag[c-1] (acquire, bounded);
+//   4. move the remaining rows tile by tile exactly as the one-CTA kernel does, then store the tail.
+// A CTA only waits for a lower-numbered one that raises its flag before waiting itself, so the chain cannot
+// dead-lock as long as blocks are dispatched in index order; the wait is bounded anyway and reports a timeout.
+struct MoveParams {
+  char* k; char* v; float* beta; int32_t* pos; int32_t* seg_len;
+  int64_t cap; int row_vecs; int ctas; int tail_max;
+  const int32_t* plan; const int32_t* plan_tail; const int32_t* kept; int64_t kept_stride;
+  int32_t* flags; int32_t* status;
+};
+
+__device__ __forceinline__ int ld_acquire(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release(int32_t* p, int v) {
+  asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(kMoveThreads) evict_move_kernel(MoveParams p) {
+  constexpr int kThreads = kMoveThreads;
+  extern __shared__ __align__(16) uint4 tail_kv[];   // [tail_max][2 * row_vecs], then beta[tail_max], pos[tail_max]
+  __shared__ int s_ok;
+  const int seg = blockIdx.y, c = blockIdx.x;
+  const int m = p.plan[2 * seg];
+  if (m < 0) return;                                  // this segment keeps everything
+  const int j0 = p.plan[2 * seg + 1];
+  const int nvec = 2 * p.row_vecs;
+  const int tile_rows = min(kThreads, (kThreads * kEvictUnroll) / nvec);
+  int lo, hi, per;
+  move_range(m, j0, p.ctas, p.tail_max, tile_rows, c, &lo, &hi, &per);
+  int32_t* flag = p.flags + (int64_t)seg * p.ctas + c;
+  if (lo >= hi) {
+    if (threadIdx.x == 0) { st_release(flag, 1); if (c == 0) p.seg_len[seg] = m; }
+    return;
+  }
+  const int32_t* kept = p.kept + (int64_t)seg * p.kept_stride;
+  const int64_t row0 = (int64_t)seg * p.cap;
+  const int64_t row_bytes = (int64_t)p.row_vecs * 16;
+  char* kbase = p.k + row0 * row_bytes;
+  char* vbase = p.v + row0 * row_bytes;
+  const TileMap tm = make_tile_map<kThreads>(nvec, p.row_vecs, kbase, vbase);
+  const int jt = min(max(p.plan_tail[(int64_t)seg * p.ctas + c], lo), hi);   // first row to stage (selection kernel)
+  const int ntail = hi - jt;
+  float* tail_beta = reinterpret_cast<float*>(tail_kv + (int64_t)p.tail_max * nvec);
+  int32_t* tail_pos = reinterpret_cast<int32_t*>(tail_beta + p.tail_max);
+  const bool tail_fits = ntail <= p.tail_max && kept[hi - 1] - (hi - 1) <= per;
+  if (tail_fits) {
+    // A tile at a time: all index loads, then all row loads, then the shared-memory stores.
+#pragma unroll 1
+    for (int rb = 0; rb < ntail; rb += tile_rows) {
+      int src[kEvictUnroll]; uint4 val[kEvictUnroll];
+#pragma unroll
+      for (int u = 0; u < kEvictUnroll; ++u) {
+        const int r = rb + tile_row<kThreads>(tm, u);
+        src[u] = r < ntail ? kept[jt + r] : 0;   // (rows past the tile are fetched again by the next round: harmless)
+      }
+#pragma unroll
+      for (int u = 0; u < kEvictUnroll; ++u) {
+        const int r = tile_row<kThreads>(tm, u);
+        if (rb + r < ntail) val[u] = ld16(tile_ptr<kThreads>(tm, u, r, src[u], row_bytes, p.row_vecs, kbase, vbase));
+      }
+#pragma unroll
+      for (int u = 0; u < kEvictUnroll; ++u) {
+        const int r = tile_row<kThreads>(tm, u);
+        if (rb + r < ntail) tail_kv[(rb + r) * nvec + tile_col<kThreads>(tm, u, r)] = val[u];
+      }
+    }
+    for (int r = threadIdx.x; r < ntail; r += kThreads) {
+      const int src = kept[jt + r];
+      tail_beta[r] = p.beta[row0 + src]; tail_pos[r] = p.pos[row0 + src];
+    }
+  }
+  __syncthreads();                                    // the staged values have arrived: the loads are performed
+  if (threadIdx.x == 0) {
+    st_release(flag, 1);
+    int ok = tail_fits ? 1 : 0;
+    if (!tail_fits) report(p.status, TKV_DEV_CAPACITY);
+    if (ok && c > 0) {
+      int spins = 0;
+      while (ld_acquire(flag - 1) != 1) {
+        if (++spins > (1 << 21)) { ok = 0; report(p.status, TKV_DEV_TIMEOUT); break; }
+        __nanosleep(100);
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;                                  // nothing of this range was written
+
+  // Source rows of the next tile are fetched while this tile's rows are in flight, so that the dependent
+  // index -> row loads do not add up.
+  int src_row[kEvictUnroll], src_meta = 0;
+  auto fetch_indices = [&](int jb) {
+    const int rows = min(tile_rows, jt - jb);
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int r = tile_row<kThreads>(tm, u);
+      src_row[u] = r < rows ? kept[jb + r] : 0;
+    }
+    src_meta = (int)threadIdx.x < rows ? kept[jb + threadIdx.x] : 0;
+  };
+  if (lo < jt) fetch_indices(lo);
+#pragma unroll 1
+  for (int jb = lo; jb < jt; jb += tile_rows) {
+    const int rows = min(tile_rows, jt - jb);
+    uint4 reg[kEvictUnroll];
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int r = tile_row<kThreads>(tm, u);
+      if (r < rows) reg[u] = ld16(tile_ptr<kThreads>(tm, u, r, src_row[u], row_bytes, p.row_vecs, kbase, vbase));
+    }
+    float bt = 0.f; int32_t ps = 0;
+    if (threadIdx.x < rows) { bt = p.beta[row0 + src_meta]; ps = p.pos[row0 + src_meta]; }
+    if (jb + tile_rows < jt) fetch_indices(jb + tile_rows);
+    __syncthreads();  // every load of this tile is performed before any of its stores
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int r = tile_row<kThreads>(tm, u);
+      if (r < rows) st16(tile_ptr<kThreads>(tm, u, r, jb + r, row_bytes, p.row_vecs, kbase, vbase), reg[u]);
+    }
+    if (threadIdx.x < rows) { p.beta[row0 + jb + threadIdx.x] = bt; p.pos[row0 + jb + threadIdx.x] = ps; }
+  }
+  __syncthreads();    // the last tile's loads may have read rows of the tail's destination
+#pragma unroll 1
+  for (int rb = 0; rb < ntail; rb += tile_rows) {
+#pragma unroll
+    for (int u = 0; u < kEvictUnroll; ++u) {
+      const int r = tile_row<kThreads>(tm, u);
+      if (rb + r < ntail)
+        st16(tile_ptr<kThreads>(tm, u, r, jt + rb + r, row_bytes, p.row_vecs, kbase, vbase),
+             tail_kv[(rb + r) * nvec + tile_col<kThreads>(tm, u, r)]);
+    }
+  }
+  for (int r = threadIdx.x; r < ntail; r += kThreads) {
+    p.beta[row0 + jt + r] = tail_beta[r]; p.pos[row0 + jt + r] = tail_pos[r];
+  }
+  if (c == 0 && threadIdx.x == 0) p.seg_len[seg] = m;
 }
 
 struct SelectParams {
@@ -360,7 +567,8 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
                       int32_t* seg_len, int32_t* cu_seqlens, int group,
                       int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                       int memory_size, int trigger_len, int max_len, const int32_t* keep_cnt, int protect_last,
-                      int strategy, int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+                      int strategy, int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream,
+                      int ctas = 1, void* workspace = nullptr, int64_t workspace_bytes = 0) {
   using namespace tkv;
   const int es = elem_size(kv_dtype);
   if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
@@ -383,6 +591,31 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
   p.keep_cnt = keep_cnt; p.protect_last = protect_last; p.knorm = strategy; p.kv_dtype = kv_dtype;
   p.kept_idx_out = kept_idx_out; p.status = status;
+  p.plan = nullptr; p.plan_kept = nullptr; p.plan_stride = 0; p.plan_tail = nullptr; p.ctas = 1; p.tail_max = 0;
+  MoveParams mp;
+  size_t move_smem = 0;
+  if (ctas > 1) {
+    // Workspace: flags [nseg, ctas] | plan [nseg, 2] | plan_tail [nseg, ctas] | kept [nseg, memory_size], all int32.
+    if (keep_cnt != nullptr) return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: per-segment keep counts are not supported");
+    if (ctas > kEvictMaxCtas || nseg > 65535)
+      return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: ctas_per_segment=%d (limit %d), nseg=%d (limit 65535)", ctas, kEvictMaxCtas, nseg);
+    const int64_t need = tkv_evict_multi_workspace_bytes(nseg, memory_size, ctas);
+    if (workspace == nullptr || workspace_bytes < need || ((uintptr_t)workspace & 3))
+      return fail(TKV_ERR_ARG, "tkv_evict_multi: workspace of %lld bytes, %lld needed", (long long)workspace_bytes, (long long)need);
+    mp.tail_max = max_len - memory_size;               // no row moves further than the rows evicted before it
+    move_smem = (size_t)mp.tail_max * (2 * row_bytes + 8);
+    if (mp.tail_max <= 0 || move_smem > 200 * 1024)
+      return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: max_len - memory_size = %d rows do not fit the staging area", mp.tail_max);
+    int32_t* w = (int32_t*)workspace;
+    mp.flags = w; p.plan = w + (int64_t)nseg * ctas; p.plan_tail = p.plan + 2 * (int64_t)nseg;
+    p.plan_kept = p.plan_tail + (int64_t)nseg * ctas; p.plan_stride = memory_size;
+    p.ctas = ctas; p.tail_max = mp.tail_max; mp.plan_tail = p.plan_tail;
+    mp.k = p.k; mp.v = p.v; mp.beta = p.beta; mp.pos = p.pos; mp.seg_len = seg_len; mp.cap = cap; mp.row_vecs = p.row_vecs;
+    mp.ctas = ctas; mp.plan = p.plan; mp.kept = p.plan_kept; mp.kept_stride = memory_size; mp.status = status;
+    // flags = -1 (not raised), plan = -1 (segment keeps everything) until the selection says otherwise
+    cudaError_t e = cudaMemsetAsync(workspace, 0xFF, ((size_t)nseg * ctas + 2 * (size_t)nseg) * 4, (cudaStream_t)stream);
+    if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_evict_multi: memset: %s", cudaGetErrorString(e));
+  }
   const size_t smem = (size_t)max_len * 4;
   // Long segments: the key array leaves room for at most 3 CTAs per SM, so each CTA gets twice the threads (and
   // twice the rows in flight per tile) to keep the memory system as busy as 4 narrow CTAs do.
@@ -390,11 +623,39 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   int rc = wide ? set_smem(evict_inplace_kernel<kEvictThreadsWide>, smem, "tkv_evict")
                 : set_smem(evict_inplace_kernel<kEvictThreads>, smem, "tkv_evict");
   if (rc != TKV_OK) return rc;
-  if (wide) evict_inplace_kernel<kEvictThreadsWide><<<nseg, kEvictThreadsWide, smem, (cudaStream_t)stream>>>(p);
+  if (ctas > 1) {
+    rc = set_smem(evict_inplace_kernel<kEvictThreadsPlan>, smem, "tkv_evict_multi");
+    if (rc != TKV_OK) return rc;
+    evict_inplace_kernel<kEvictThreadsPlan><<<nseg, kEvictThreadsPlan, smem, (cudaStream_t)stream>>>(p);
+  } else if (wide) evict_inplace_kernel<kEvictThreadsWide><<<nseg, kEvictThreadsWide, smem, (cudaStream_t)stream>>>(p);
   else evict_inplace_kernel<kEvictThreads><<<nseg, kEvictThreads, smem, (cudaStream_t)stream>>>(p);
   rc = check_launch("tkv_evict");
   if (rc != TKV_OK) return rc;
+  if (ctas > 1) {
+    rc = set_smem(evict_move_kernel, move_smem, "tkv_evict_multi");
+    if (rc != TKV_OK) return rc;
+    evict_move_kernel<<<dim3((unsigned)ctas, (unsigned)nseg), kMoveThreads, move_smem, (cudaStream_t)stream>>>(mp);
+    rc = check_launch("tkv_evict_multi");
+    if (rc != TKV_OK) return rc;
+  }
   return launch_rebuild(seg_len, cu_seqlens, nseg, group, (cudaStream_t)stream);
+}
+
+extern "C" int64_t tkv_evict_multi_workspace_bytes(int nseg, int memory_size, int ctas_per_segment) {
+  if (nseg < 0 || memory_size <= 0 || ctas_per_segment <= 0) return 0;
+  return (2 * (int64_t)nseg * ctas_per_segment + 2 * (int64_t)nseg + (int64_t)nseg * memory_size) * 4;
+}
+
+extern "C" int tkv_evict_multi(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
+                               int32_t* seg_len, int32_t* cu_seqlens, int group,
+                               int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
+                               int memory_size, int trigger_len, int max_len, int protect_last, int strategy,
+                               int ctas_per_segment, void* workspace, int64_t workspace_bytes,
+                               int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+  if (ctas_per_segment < 1) return tkv::fail(TKV_ERR_ARG, "tkv_evict_multi: ctas_per_segment=%d", ctas_per_segment);
+  return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
+                    q_idx, memory_size, trigger_len, max_len, nullptr, protect_last, strategy, kept_idx_out, status, stream,
+                    ctas_per_segment, workspace, workspace_bytes);
 }
 
 extern "C" int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,

@@ -208,6 +208,28 @@ def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group
     _count(1 if cu_seqlens is None else 2)
 
 
+def evict_multi_workspace(nseg: int, memory_size: int, ctas_per_segment: int, device) -> torch.Tensor:
+    """Scratch for :func:`evict_multi` (contents irrelevant between calls; one stream at a time)."""
+    nbytes = lib().tkv_evict_multi_workspace_bytes(nseg, memory_size, ctas_per_segment)
+    return torch.empty(max(nbytes, 4) // 4, dtype=torch.int32, device=device)
+
+
+def evict_multi(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
+                q_idx: int, memory_size: int, trigger_len: int, max_len: int, ctas_per_segment: int, workspace,
+                protect_last: int = 0, knorm: bool = False, kept_idx_out=None, status=None) -> None:
+    """:func:`evict` with ``ctas_per_segment`` CTAs sharing each evicting segment (identical result)."""
+    d = k_cache.shape[-1]
+    rc = lib().tkv_evict_multi(
+        k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
+        seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
+        memory_size, trigger_len, max_len, protect_last, 1 if knorm else 0, ctas_per_segment,
+        _ptr(workspace), 0 if workspace is None else workspace.numel() * workspace.element_size(),
+        _ptr(kept_idx_out), _ptr(status), _stream(k_cache))
+    check(rc, "tkv_evict_multi")
+    n = 1 if ctas_per_segment <= 1 else 2
+    _count(n if cu_seqlens is None else n + 1)
+
+
 def group_budget(beta_cache, pos_cache, seg_len, cap: int, groups: int, inner: int, n_outer: int, outer_stride: int,
                  q_idx: int, k_total: int, keep_cnt, threshold=None, floor_mode: int = 0, floor_cnt: int = 0,
                  status=None) -> None:
