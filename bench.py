@@ -296,12 +296,17 @@ def run_micro(args):
                  torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)) for _ in range(nbuf)]
         q = torch.randn(batch, hq, D, generator=g, device=dev, dtype=torch.bfloat16)
         out = torch.empty_like(q)
-        ws = torch.empty(ops.decode_attn_workspace_bytes(batch, hq, hkv, D, cap), dtype=torch.uint8, device=dev)
+        # With --token-bound the grid is sized by the total number of cached tokens (which the flat caches know on the
+        # host) instead of by nseg * max_len.
+        bound = int(lens.long().sum()) if args.token_bound else None
+        res["token_bound"] = bound
+        ws = torch.empty(ops.decode_attn_workspace_bytes(batch, hq, hkv, D, cap) if bound is None else
+                         ops.decode_attn_workspace_bytes_ragged(batch, hq, hkv, D, cap, bound), dtype=torch.uint8, device=dev)
         for i in range(args.warmup + args.steps):
             k, v = bufs[i % nbuf]
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, D ** -0.5, cap, None)
+            ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, D ** -0.5, cap, None, total_len_bound=bound)
             e1.record()
             if i >= args.warmup:
                 times.append((e0, e1))
@@ -373,6 +378,8 @@ def main():
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--nseg", type=int, default=2048)
+    ap.add_argument("--token-bound", action="store_true",
+                    help="attention microbenchmark: size the grid by the total token count (ragged lengths)")
     ap.add_argument("--ctas", type=int, default=1, help="CTAs sharing one segment in the eviction microbenchmarks")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)

@@ -216,6 +216,25 @@ int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
                     float scale, int max_len, int32_t* status, tkv_stream_t stream);
 
 /*
+ * tkv_decode_attn for ragged lengths.  total_len_bound: an upper bound on the sum of seg_len over all segments that
+ * the host knows without reading device memory (the flat budget-sharing caches keep it: head_lens sums to at most
+ * budget + buffer per layer, src/trimkv/cache_utils.py:346-369, 714-738).  The split kernel's grid is then sized
+ * by total_len_bound / 256 + nseg work items instead of nseg * ceil(max_len / 256), most of which would find no
+ * tokens; a one-CTA kernel builds the item list from seg_len first.  Same result as tkv_decode_attn.  If the true
+ * total exceeds the bound the surplus chunks are skipped and the status word reports TKV_DEV_LEN_BOUND.
+ * The workspace is larger by the item list: tkv_decode_attn_ragged_workspace_bytes().
+ */
+size_t tkv_decode_attn_ragged_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len,
+                                              int64_t total_len_bound);
+int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
+                           const void* k_cache, const void* v_cache,
+                           const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                           void* out, void* workspace, size_t workspace_bytes,
+                           int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                           float scale, int max_len, int64_t total_len_bound,
+                           int32_t* status, tkv_stream_t stream);
+
+/*
  * tkv_decode_attn for callers that cannot allocate device memory.  (No counterpart in the reference: its
  * attention always runs inside PyTorch, whose allocator provides flash-attn's temporaries.)
  * Meant for hosts that cannot hand the library a workspace: a server whose block arena already owns the whole

@@ -137,3 +137,39 @@ def test_knorm_alpha_matches_reference(golden_dir):
             ev += 1
     cache.check_status()
     assert ev == g["kept_positions"].shape[0]
+
+
+def test_decode_attention_over_a_budget_sharing_cache():
+    """Decode attention through the registry entry over head lengths that differ widely (one head holds most of the
+    shared budget): the cache hands its host-side token total to the kernel, which sizes its grid by it."""
+    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache
+    from trimkv_b200.attn import TRIMKV_ATTENTION_IMPLEMENTATIONS
+    attn = TRIMKV_ATTENTION_IMPLEMENTATIONS["db_attn_flash_batched"]
+    gen = torch.Generator().manual_seed(5)
+    L, B, H, G, D, S, M, Bf = 2, 2, 8, 2, 128, 3000, 512, 32
+    dt = torch.bfloat16
+    # retention close to 1 for head 0 (it keeps nearly everything), fast decay for the others
+    mean = torch.tensor([9.0, 2.0, 1.0, 0.5, 0.0, 0.0, -0.5, -1.0]).view(1, H, 1)
+    cache = BatchedDynamicBudgetTrimKVCache(device=DEV)
+    for t in range(4):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        for l in range(L):
+            k = torch.randn(B, H, hi - lo, D, generator=gen).to(dt).to(DEV)
+            v = torch.randn(B, H, hi - lo, D, generator=gen).to(dt).to(DEV)
+            logb = torch.nn.functional.logsigmoid(torch.randn(B, H, hi - lo, generator=gen) + mean).to(dt).to(DEV)
+            kk, vv, _, _, kw = cache.update(k, v, logb, torch.arange(lo, hi, device=DEV), l)
+            if t == 0:
+                continue
+            assert kw["total_len_bound"] == int(cache.head_lens[l].sum())
+            q = torch.randn(B, H * G, 1, D, generator=gen).to(dt).to(DEV)
+            out, _, _ = attn(None, q, kk, vv, None, flash_attn_kwargs=kw)
+            kp, vp, _, _ = cache.packed(l)
+            lens = cache.head_lens[l].cpu().numpy()
+            want = orc.varlen_gqa_attention(q.float().cpu().numpy(), kp.float().cpu().numpy(), vp.float().cpu().numpy(),
+                                            np.concatenate([[0], np.cumsum(lens)]), B, H)
+            assert np.max(np.abs(out.float().cpu().numpy() - want)) <= 2e-2
+        cache.compress(strategy="alpha", memory_size=M, buffer_size=Bf, num_layers=L, num_key_value_heads=H)
+        if t == 0:
+            lens = cache.head_lens[0].cpu().numpy()
+            assert lens.max() > 4 * lens.min()          # the case is ragged
+    cache.check_status()

@@ -308,6 +308,41 @@ def test_decode_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, d, cap, lens_
     assert np.max(np.abs(out2.float().cpu().numpy() - want)) <= tol
 
 
+@pytest.mark.parametrize("bsz,hq,hkv,cap", [(4, 16, 8, 2100), (2, 32, 8, 4200), (1, 8, 8, 1030)])
+def test_decode_attention_ragged_work_list(ops, bsz, hq, hkv, cap):
+    """Grid sized by a bound on the total tokens: same partials, so the same bits as the dense grid; an insufficient
+    bound is reported through the status word."""
+    gen = torch.Generator().manual_seed(23)
+    d, dtype, nseg = 128, torch.bfloat16, bsz * hkv
+    lens = [int(x) for x in torch.randint(1, cap // 3, (nseg,), generator=gen)]
+    lens[0], lens[1], lens[2], lens[-1] = 0, 256, 257, cap      # empty, exactly one chunk, one token more, the longest
+    q = torch.randn(bsz, hq, d, generator=gen).to(dtype).to(DEV)
+    k = torch.randn(nseg * cap, d, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(nseg * cap, d, generator=gen).to(dtype).to(DEV)
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    dense = torch.empty_like(q)
+    ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, cap), dtype=torch.uint8, device=DEV)
+    ops.decode_attn(q, k, v, ln, None, cap, dense, ws, hkv, d ** -0.5, cap, status)
+    total = sum(lens)
+    for bound in (total, total + 1000):
+        out = torch.full_like(q, float("nan"))
+        wsr = torch.empty(ops.decode_attn_workspace_bytes_ragged(bsz, hq, hkv, d, cap, bound), dtype=torch.uint8, device=DEV)
+        wsr.fill_(0xA5)
+        ops.decode_attn(q, k, v, ln, None, cap, out, wsr, hkv, d ** -0.5, cap, status, total_len_bound=bound)
+        assert ops.read_status(status) == 0
+        assert torch.equal(out, dense)
+    kf = torch.cat([k.view(nseg, cap, d)[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    vf = torch.cat([v.view(nseg, cap, d)[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    want = orc.varlen_gqa_attention(q[:, :, None].float().cpu().numpy(), kf, vf, np.concatenate([[0], np.cumsum(lens)]), bsz, hkv)[:, 0]
+    assert np.max(np.abs(dense.float().cpu().numpy() - want)) <= 2e-2
+    # a bound below the true total: the surplus work items are dropped and the status word says so
+    small = total // 2
+    wsr = torch.empty(ops.decode_attn_workspace_bytes_ragged(bsz, hq, hkv, d, cap, small), dtype=torch.uint8, device=DEV)
+    ops.decode_attn(q, k, v, ln, None, cap, torch.empty_like(q), wsr, hkv, d ** -0.5, cap, status, total_len_bound=small)
+    assert ops.read_status(status) == 2
+
+
 # ---------------------------------------------------------------- weight-streaming GEMM and its consumers
 @pytest.mark.parametrize("m,n,k", [(32, 4224, 2048), (32, 2048, 2048), (32, 12288, 2048), (32, 2048, 6144),
                                    (5, 300, 128), (1, 128, 64), (17, 1000, 4096)])

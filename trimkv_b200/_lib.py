@@ -32,6 +32,8 @@ SIGNATURES = {
     "tkv_rebuild_cu_seqlens": (I, [P, P, I, I, P]),
     "tkv_decode_attn_workspace_bytes": (c_size_t, [I, I, I, I, I]),
     "tkv_decode_attn": (I, [P, L, L, P, P, P, P, L, P, P, c_size_t, I, I, I, I, I, F, I, P, P]),
+    "tkv_decode_attn_ragged_workspace_bytes": (c_size_t, [I, I, I, I, I, L]),
+    "tkv_decode_attn_ragged": (I, [P, L, L, P, P, P, P, L, P, P, c_size_t, I, I, I, I, I, F, I, L, P, P]),
     "tkv_decode_attn_static": (I, [P, L, L, P, P, P, P, L, P, I, I, I, I, I, F, I, P, P]),
     "tkv_decode_prep": (I, [P, L, P, P, F, P, P, P, P, I, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P, P, P]),
     "tkv_add_rmsnorm": (I, [P, P, P, P, I, I, F, I, I, P, P]),

@@ -82,12 +82,14 @@ def tkv_attention_forward(
         seg_start = flash_attn_kwargs["cu_seqlens_k"]
         max_len = flash_attn_kwargs.get("max_seqlen_k") or int(head_lens.max().item())
         cap = 0
-    ws = _workspace(query.device, ops.decode_attn_workspace_bytes(bsz, hq, hkv, dim, max_len))
+    bound = flash_attn_kwargs.get("total_len_bound") if seg_start is None else None
+    ws = _workspace(query.device, ops.decode_attn_workspace_bytes(bsz, hq, hkv, dim, max_len) if bound is None else
+                    ops.decode_attn_workspace_bytes_ragged(bsz, hq, hkv, dim, max_len, bound))
     if event_log is not None:
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
     ops.decode_attn(q3, key, value, head_lens, seg_start, cap, out, ws, hkv, scaling, max_len,
-                    flash_attn_kwargs.get("status"))
+                    flash_attn_kwargs.get("status"), total_len_bound=bound)
     if event_log is not None:
         e1.record()
         event_log.append((e0, e1))

@@ -529,6 +529,10 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
         kw = super()._attn_kwargs(l)
         if kw:
             kw = dict(kw, batch_size=self._batch, num_kv_heads=self._hkv)
+            if l < len(self._rows):
+                # Head lengths differ under a shared budget; their sum is known here without a device read, which
+                # lets the attention size its grid by tokens instead of by the longest head.
+                kw["total_len_bound"] = self._rows[l]
         return kw
 
     # ---- bookkeeping ----------------------------------------------------------------------------------

@@ -333,26 +333,45 @@ extern "C" size_t tkv_decode_attn_workspace_bytes(int batch, int hq, int hkv, in
   return (size_t)(items * G * (head_dim + 2) * sizeof(float) + 256);
 }
 
-extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
-                               const void* k_cache, const void* v_cache,
-                               const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
-                               void* out, void* workspace, size_t workspace_bytes,
-                               int batch, int hq, int hkv, int head_dim, int kv_dtype,
-                               float scale, int max_len, int32_t* status, tkv_stream_t stream) {
+namespace tkv {
+// Work items the ragged entry point sizes its grid for: every segment has at least one, and a segment of n tokens
+// has ceil(n / chunk) <= n / chunk + 1.
+static int64_t ragged_items(int nseg, int max_len, int64_t total_len_bound) {
+  const int chunk = attn_tc_chunk_tokens();
+  const int64_t dense = (int64_t)nseg * ((max_len + chunk - 1) / chunk);
+  const int64_t bound = total_len_bound / chunk + nseg;
+  return bound < dense ? bound : dense;
+}
+}  // namespace tkv
+
+extern "C" size_t tkv_decode_attn_ragged_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len,
+                                                         int64_t total_len_bound) {
+  const size_t base = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  if (base == 0 || total_len_bound < 0) return 0;
+  return ((base + 255) / 256) * 256 + 256 + (size_t)tkv::ragged_items(batch * hkv, max_len, total_len_bound) * sizeof(int2);
+}
+
+static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_t q_sh,
+                            const void* k_cache, const void* v_cache,
+                            const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                            void* out, void* workspace, size_t workspace_bytes,
+                            int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                            float scale, int max_len, int64_t total_len_bound, int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
-  if (!q || !k_cache || !v_cache || !seg_len || !out) return fail(TKV_ERR_ARG, "tkv_decode_attn: NULL pointer argument");
+  if (!q || !k_cache || !v_cache || !seg_len || !out) return fail(TKV_ERR_ARG, "%s: NULL pointer argument", who);
   if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || head_dim <= 0 || max_len <= 0)
-    return fail(TKV_ERR_ARG, "tkv_decode_attn: bad sizes batch=%d hq=%d hkv=%d head_dim=%d max_len=%d", batch, hq, hkv,
+    return fail(TKV_ERR_ARG, "%s: bad sizes batch=%d hq=%d hkv=%d head_dim=%d max_len=%d", who, batch, hq, hkv,
                 head_dim, max_len);
-  if (seg_start == nullptr && cap <= 0) return fail(TKV_ERR_ARG, "tkv_decode_attn: cap=%lld without seg_start", (long long)cap);
+  if (seg_start == nullptr && cap <= 0) return fail(TKV_ERR_ARG, "%s: cap=%lld without seg_start", who, (long long)cap);
   if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
-    return fail(TKV_ERR_ARG, "tkv_decode_attn: pointers must be 16-byte aligned");
-  if ((q_sb * 2) % 16 || (q_sh * 2) % 16) return fail(TKV_ERR_ARG, "tkv_decode_attn: q strides must be multiples of 16 bytes");
+    return fail(TKV_ERR_ARG, "%s: pointers must be 16-byte aligned", who);
+  if ((q_sb * 2) % 16 || (q_sh * 2) % 16) return fail(TKV_ERR_ARG, "%s: q strides must be multiples of 16 bytes", who);
   if (batch == 0) return TKV_OK;
-  const size_t need = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  const bool ragged = total_len_bound >= 0;
+  const size_t base = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  const size_t need = ragged ? tkv_decode_attn_ragged_workspace_bytes(batch, hq, hkv, head_dim, max_len, total_len_bound) : base;
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
-    return fail(TKV_ERR_ARG, "tkv_decode_attn: workspace of %zu bytes (256-byte aligned) required, got %zu", need,
-                workspace_bytes);
+    return fail(TKV_ERR_ARG, "%s: workspace of %zu bytes (256-byte aligned) required, got %zu", who, need, workspace_bytes);
   const int nseg = batch * hkv, G = hq / hkv;
   AttnParams p;
   p.q = (const char*)q; p.q_sb = q_sb; p.q_sh = q_sh;
@@ -367,10 +386,46 @@ extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
   p.hq = hq; p.hkv = hkv; p.max_len = max_len;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.work = nullptr; p.work_count = nullptr; p.work_capacity = 0;
   if (!tc) return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+  if (ragged && p.nchunks < 256) {
+    const int64_t items = ragged_items(nseg, max_len, total_len_bound);
+    // Only worth the extra launch when it removes a good part of the grid.
+    if (items * 4 <= (int64_t)nseg * p.nchunks * 3 && items < INT32_MAX) {
+      char* w = reinterpret_cast<char*>(workspace) + ((base + 255) / 256) * 256;
+      p.work_count = reinterpret_cast<const int32_t*>(w);
+      p.work = reinterpret_cast<const int2*>(w + 256);
+      p.work_capacity = (int)items;
+      int rc = launch_attn_worklist(p, nseg, (cudaStream_t)stream);
+      if (rc != TKV_OK) return rc;
+    }
+  }
   int rc = launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
   if (rc != TKV_OK) return rc;
   return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
+                               const void* k_cache, const void* v_cache,
+                               const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                               void* out, void* workspace, size_t workspace_bytes,
+                               int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                               float scale, int max_len, int32_t* status, tkv_stream_t stream) {
+  return decode_attn_impl("tkv_decode_attn", q, q_sb, q_sh, k_cache, v_cache, seg_len, seg_start, cap, out, workspace,
+                          workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, -1, status, stream);
+}
+
+extern "C" int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
+                                      const void* k_cache, const void* v_cache,
+                                      const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                                      void* out, void* workspace, size_t workspace_bytes,
+                                      int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                                      float scale, int max_len, int64_t total_len_bound,
+                                      int32_t* status, tkv_stream_t stream) {
+  if (total_len_bound < 0) return tkv::fail(TKV_ERR_ARG, "tkv_decode_attn_ragged: total_len_bound=%lld", (long long)total_len_bound);
+  return decode_attn_impl("tkv_decode_attn_ragged", q, q_sb, q_sh, k_cache, v_cache, seg_len, seg_start, cap, out,
+                          workspace, workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, total_len_bound,
+                          status, stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -442,5 +497,6 @@ extern "C" int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
   p.hq = hq; p.hkv = hkv; p.max_len = max_len;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
+  p.work = nullptr; p.work_count = nullptr; p.work_capacity = 0;
   return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
 }

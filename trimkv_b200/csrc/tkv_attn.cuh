@@ -16,6 +16,9 @@ struct AttnParams {
   int hq, hkv, max_len;
   float scale_log2;                       // softmax scale * log2(e)
   int32_t* status;
+  // Optional compact work list (ragged lengths): item i = {segment << 8 | chunk, clamped length of the segment};
+  // *work_count items are valid.  NULL: the grid covers every (segment, chunk) pair and absent chunks exit.
+  const int2* work; const int32_t* work_count; int work_capacity;
 };
 
 // Tokens per work item, a pure function of the problem size (the workspace size depends on it).
@@ -25,6 +28,8 @@ int attn_chunk_tokens(int nseg, int max_len);
 // Tensor-core (tcgen05 + TMA) split kernel: fixed chunk, needs the capacity-strided layout and head_dim 128.
 int attn_tc_chunk_tokens();
 int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, int64_t rows, cudaStream_t st);
+// Builds the compact work list of the tensor-core split kernel from the lengths (one small kernel).
+int launch_attn_worklist(const AttnParams& p, int nseg, cudaStream_t st);
 // Merge kernel shared by both split kernels.
 int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st);
 

@@ -42,10 +42,17 @@ template <int kDtype, int kG>
 __global__ void __launch_bounds__(kTcThreads)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
-  const int seg = blockIdx.x / p.nchunks, chunk = blockIdx.x - seg * p.nchunks;
   grid_dependency_wait();  // the lengths and the newest rows come from the preceding kernel of the stream
   grid_launch_dependents();  // the merge kernel may be scheduled; it waits for this grid before reading partials
-  const int len = min(p.seg_len[seg], p.max_len);
+  int seg, chunk, len;
+  if (p.work != nullptr) {
+    if ((int)blockIdx.x >= *p.work_count) return;
+    const int2 item = p.work[blockIdx.x];
+    seg = item.x >> 8; chunk = item.x & 255; len = item.y;
+  } else {
+    seg = blockIdx.x / p.nchunks; chunk = blockIdx.x - seg * p.nchunks;
+    len = min(p.seg_len[seg], p.max_len);
+  }
   const int t0 = chunk * kTcChunk;
   if (t0 >= len) {
     if (chunk == 0) {  // empty segment: its query heads get zeros
@@ -311,7 +318,8 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnPar
     if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
     configured = true;
   }
-  cudaError_t e = launch_pdl(decode_attn_tc_kernel<kDtype, kG>, dim3((unsigned)((int64_t)nseg * p.nchunks)), dim3(kTcThreads),
+  const int64_t grid = p.work != nullptr ? (int64_t)p.work_capacity : (int64_t)nseg * p.nchunks;
+  cudaError_t e = launch_pdl(decode_attn_tc_kernel<kDtype, kG>, dim3((unsigned)grid), dim3(kTcThreads),
                              (size_t)kTcSmemBytes, st, mk, mv, p);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_attn(tc)");
@@ -330,6 +338,38 @@ static int launch_tc_g(const CUtensorMap& mk, const CUtensorMap& mv, const AttnP
     case 8: return launch_tc<kDtype, 8>(mk, mv, p, nseg, st);
     default: return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(tc): %d query heads per KV head", G);
   }
+}
+
+// Work list for ragged lengths: one item per present (segment, chunk) pair, segments in order, so that the grid of
+// the split kernel can be sized by the total number of cached tokens instead of nseg * (max_len / chunk).  An empty
+// segment still gets one item (its CTA writes the zero output).  One CTA: nseg is a few thousand at most.
+__global__ void __launch_bounds__(1024) attn_worklist_kernel(AttnParams p, int nseg, int2* work, int32_t* count) {
+  __shared__ int warp_sums[1024 / 32 + 1];
+  grid_dependency_wait();
+  grid_launch_dependents();
+  int running = 0;
+  for (int base = 0; base < nseg; base += 1024) {
+    const int i = base + threadIdx.x;
+    const int len = i < nseg ? max(min(p.seg_len[i], p.max_len), 0) : 0;
+    const int c = i < nseg ? max(1, (len + kTcChunk - 1) / kTcChunk) : 0;
+    int total;
+    const int off = running + block_exclusive_scan<1024>(c, warp_sums, &total);
+    for (int j = 0; j < c; ++j)
+      if (off + j < p.work_capacity) work[off + j] = make_int2((i << 8) | j, len);
+    running += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    if (running > p.work_capacity) report(p.status, TKV_DEV_LEN_BOUND);   // more tokens than the caller's bound
+    *count = min(running, p.work_capacity);
+  }
+}
+
+int launch_attn_worklist(const AttnParams& p, int nseg, cudaStream_t st) {
+  cudaError_t e = launch_pdl(attn_worklist_kernel, dim3(1), dim3(1024), (size_t)0, st, p, nseg,
+                             const_cast<int2*>(p.work), const_cast<int32_t*>(p.work_count));
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn_ragged(work list): %s", cudaGetErrorString(e));
+  return check_launch("tkv_decode_attn_ragged(work list)");
 }
 
 // Launches the tensor-core split kernel; `rows` = number of rows addressable behind k/v (bounds of the tensor maps).

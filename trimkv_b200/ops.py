@@ -129,12 +129,27 @@ def decode_attn_workspace_bytes(batch: int, hq: int, hkv: int, head_dim: int, ma
     return int(lib().tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len))
 
 
+def decode_attn_workspace_bytes_ragged(batch: int, hq: int, hkv: int, head_dim: int, max_len: int,
+                                       total_len_bound: int) -> int:
+    return int(lib().tkv_decode_attn_ragged_workspace_bytes(batch, hq, hkv, head_dim, max_len, total_len_bound))
+
+
 def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspace, hkv: int, scale: float,
-                max_len: int, status=None) -> None:
-    """q ``[B,Hq,D]`` (any batch/head strides), out ``[B,Hq,D]`` contiguous, workspace uint8."""
+                max_len: int, status=None, total_len_bound=None) -> None:
+    """q ``[B,Hq,D]`` (any batch/head strides), out ``[B,Hq,D]`` contiguous, workspace uint8.
+    ``total_len_bound``: host-known bound on ``seg_len.sum()`` for ragged lengths (sizes the grid by tokens instead of
+    by ``max_len``); the workspace must then have ``decode_attn_workspace_bytes_ragged`` bytes."""
     b, hq, d = q.shape
     if q.stride(2) != 1:
         q = q.contiguous()
+    if total_len_bound is not None:
+        rc = lib().tkv_decode_attn_ragged(
+            q.data_ptr(), q.stride(0), q.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
+            seg_len.data_ptr(), _ptr(seg_start), cap, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
+            b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len, int(total_len_bound), _ptr(status), _stream(q))
+        check(rc, "tkv_decode_attn_ragged")
+        _count(3)
+        return
     rc = lib().tkv_decode_attn(
         q.data_ptr(), q.stride(0), q.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
         seg_len.data_ptr(), _ptr(seg_start), cap, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
