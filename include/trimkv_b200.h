@@ -138,6 +138,10 @@ int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cach
  * Used after tkv_group_budget for the budget-sharing strategies.
  */
 enum { TKV_STRATEGY_ALPHA = 0, TKV_STRATEGY_KNORM_ALPHA = 1 };
+/* OR-ed into `strategy`: dtype the retention score log beta * (q_idx - pos) is computed in.  TrimKVCache upcasts to
+ * fp32 (src/trimkv/cache_utils.py:172); the flat budget-sharing caches multiply in the stored dtype
+ * (:386, :441, :755, :882), i.e. the age is rounded to that dtype and so is the product. */
+enum { TKV_SCORE_F32 = 0, TKV_SCORE_BF16 = 1 << 8, TKV_SCORE_F16 = 2 << 8 };
 int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
                  int32_t* seg_len, int32_t* cu_seqlens, int group,
                  int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
@@ -172,11 +176,12 @@ int tkv_evict_multi(void* k_cache, void* v_cache, float* beta_cache, int32_t* po
  * preceding head of the group).
  * Replaces the top-k + mask + per-head .item() loops of _compress_layer, _compress_all_layers,
  * _compress_layer_batched and _compress_all_layers_batched
- * (src/trimkv/cache_utils.py:371-416, 418-536, 740-834, 836-945); scores are fp32.
+ * (src/trimkv/cache_utils.py:371-416, 418-536, 740-834, 836-945); scores in fp32 or in the stored dtype.
  */
 int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const int32_t* seg_len, int64_t cap,
                      int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
                      int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
+                     int score_dtype /* 0 fp32, 1 bf16, 2 f16: as TKV_SCORE_* >> 8 */,
                      int32_t* keep_cnt, int32_t* status, tkv_stream_t stream);
 
 /*

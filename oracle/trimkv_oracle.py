@@ -27,6 +27,7 @@ import numpy as np
 
 __all__ = [
     "retention_scores",
+    "round_to_dtype",
     "canonical_topm",
     "compress_rows",
     "OracleTrimKVCache",
@@ -40,15 +41,36 @@ __all__ = [
 # --------------------------------------------------------------------------
 # eviction arithmetic
 # --------------------------------------------------------------------------
-def retention_scores(log_beta: np.ndarray, kv_positions: np.ndarray, q_idx: int) -> np.ndarray:
+def round_to_dtype(x: np.ndarray, dtype: str) -> np.ndarray:
+    """fp32 values rounded (nearest even) to ``dtype`` ("float32", "bfloat16", "float16"), returned as fp32."""
+    x = np.asarray(x, dtype=np.float32)
+    if dtype == "float32":
+        return x
+    if dtype == "float16":
+        with np.errstate(over="ignore"):
+            return x.astype(np.float16).astype(np.float32)
+    if dtype != "bfloat16":
+        raise ValueError(dtype)
+    u = x.view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000).astype(np.uint32).view(np.float32)
+    return np.where(np.isfinite(x), r, x).astype(np.float32)
+
+
+def retention_scores(log_beta: np.ndarray, kv_positions: np.ndarray, q_idx: int, score_dtype: str = "float32") -> np.ndarray:
     """fp32 score = fp32(log beta) * fp32(q_idx - pos), one rounding.
 
     src/trimkv/cache_utils.py:172-174: ``log_beta = rw.to(float32)``;
     ``q_idx = seen + 1``; ``log_alpha = log_beta * (q_idx - kv_positions)``.
     torch promotes the int64 age to fp32 and multiplies once.
+
+    ``score_dtype`` other than fp32 restates the flat classes, which skip the upcast (:386, :441, :755, :882:
+    ``(q_idx - kv_pos) * rw`` with ``rw`` in the model dtype): torch casts the int64 age to that dtype, multiplies in
+    fp32 and rounds the product to it.  ``log_beta`` must then hold values representable in that dtype.
     """
     lb = np.asarray(log_beta).astype(np.float32)
     age = (np.int64(q_idx) - np.asarray(kv_positions).astype(np.int64)).astype(np.float32)
+    if score_dtype != "float32":
+        return round_to_dtype(lb * round_to_dtype(age, score_dtype), score_dtype)
     return (lb * age).astype(np.float32)
 
 
@@ -73,13 +95,13 @@ def canonical_topm(scores: np.ndarray, m: int) -> np.ndarray:
 
 
 def compress_rows(key, value, log_beta, kv_positions, q_idx: int, m: int, sliding_window_size: int = 0,
-                  strategy: str = "alpha"):
+                  strategy: str = "alpha", score_dtype: str = "float32"):
     """One ``compress_layer`` on dense ``[..., n, D]`` / ``[..., n]`` arrays.
 
     src/trimkv/cache_utils.py:167-198, strategy "alpha"; the newest ``sliding_window_size`` rows score +inf (:186-187).
     Returns (key, value, log_beta, kv_positions, kept_idx).
     """
-    sc = retention_scores(log_beta, kv_positions, q_idx)
+    sc = retention_scores(log_beta, kv_positions, q_idx, score_dtype)
     if strategy == "knorm_alpha":
         # :176-180: scores = log_alpha + log(||k||_2); fp32 keys only here (16-bit keys round norm and log to that dtype)
         kn = np.sqrt(np.sum(np.asarray(key, np.float32) ** 2, axis=-1, dtype=np.float32))
@@ -372,21 +394,23 @@ def _group_keep_counts(scores, k_total=None, threshold=None, bucketize_attributi
 
 
 class OracleFlatBudgetCache(OracleBatchedFlatCache):
-    """``compress`` of the reference's flat caches, with fp32 scores and canonical ties.
+    """``compress`` of the reference's flat caches, with canonical ties; scores in ``score_dtype`` (the dtype the
+    reference's tensors hold log beta in: it multiplies without an upcast).
 
     ``batched=True`` restates BatchedDynamicBudgetTrimKVCache.compress (src/trimkv/cache_utils.py:697-945),
     ``batched=False`` DynamicBudgetTrimKVCache.compress (:334-536, batch size 1).  Keeping a group's top-k equals
     keeping each segment's own top-c rows for the per-segment counts c, so every variant reduces to counts.
     """
 
-    def __init__(self, batched=True):
+    def __init__(self, batched=True, score_dtype="float32"):
         super().__init__()
         self.batched = batched
+        self.score_dtype = score_dtype
 
     def _scores(self, l, seg):
         a, n = int(self.cu_seqlens_k[l][seg]), int(self.head_lens[l][seg])
         return retention_scores(self.retention_weights[l][a:a + n, 0], self.kv_positions[l][a:a + n, 0],
-                                self._seen_tokens + 1)
+                                self._seen_tokens + 1, self.score_dtype)
 
     def _apply(self, counts):
         """counts[l][seg] rows kept (canonical top-c inside the segment)."""
@@ -402,7 +426,7 @@ class OracleFlatBudgetCache(OracleBatchedFlatCache):
                     if c == 0:
                         k, v, b, p = k[:0], v[:0], b[:0], p[:0]
                     else:
-                        k, v, b, p, _ = compress_rows(k, v, b, p, q_idx, c)
+                        k, v, b, p, _ = compress_rows(k, v, b, p, q_idx, c, score_dtype=self.score_dtype)
                 ks.append(k); vs.append(v); bs.append(b[:, None]); ps.append(p[:, None]); nl.append(k.shape[0])
             self.key_cache[l] = np.concatenate(ks, 0); self.value_cache[l] = np.concatenate(vs, 0)
             self.retention_weights[l] = np.concatenate(bs, 0); self.kv_positions[l] = np.concatenate(ps, 0)
@@ -418,7 +442,8 @@ class OracleFlatBudgetCache(OracleBatchedFlatCache):
         rows = [self.key_cache[l].shape[0] for l in range(L)]
         total = sum(rows)
         thr = "threshold" in strategy
-        log_thr = np.log(np.float32(alpha_threshold)) if thr else None
+        # :462, :893 compare with a 0-dim fp32 tensor, which torch casts to the dtype of the scores
+        log_thr = round_to_dtype(np.log(np.float32(alpha_threshold)), self.score_dtype) if thr else None
         counts = {}
         if self.batched:
             if total <= B * H * (M + Bf) * L and not thr:          # :714-717

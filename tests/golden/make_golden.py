@@ -221,6 +221,41 @@ def flat_budget(cu):
     print("flat_budget: ok")
 
 
+def flat_budget_bf16(cu):
+    """The flat classes on bf16 tensors: they score in bf16 (no upcast), which makes equal scores frequent.  One
+    prefill + one compress per case; pinned are the per-group multisets of kept scores, the lengths and positions
+    (exactly comparable where no tie straddles the group's budget)."""
+    L, B, H, D, S, M, Bf = 2, 2, 3, 4, 300, 64, 16
+    cases = [("batched", "alpha", 0.0), ("batched", "layer_wise_alpha", 0.0), ("single", "alpha", 0.0),
+             ("single", "layer_wise_alpha", 0.0), ("batched", "alpha_threshold", 0.35)]
+    out = {}
+    for ci, (kind, strategy, thr) in enumerate(cases):
+        torch.manual_seed(30 + ci)
+        bsz = B if kind == "batched" else 1
+        cls = cu.BatchedDynamicBudgetTrimKVCache if kind == "batched" else cu.DynamicBudgetTrimKVCache
+        cache = cls(device="cpu")
+        logb = F.logsigmoid(torch.randn(L, bsz, H, S) * 1.5 + 3.0).to(torch.bfloat16)
+        for l in range(L):
+            k = (torch.arange(S, dtype=torch.float32)[None, None, :, None].expand(bsz, H, S, D) + 1000 * l).to(torch.bfloat16)
+            cache.update(k.contiguous(), -k.contiguous(), logb[l].contiguous(), torch.arange(S), l)
+        q_idx = cache.get_seq_length() + 1
+        cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, floor_budget_ratio=0.0, alpha_threshold=thr,
+                       num_layers=L, num_key_value_heads=H)
+        assert cache.retention_weights[0].dtype == torch.bfloat16
+        lens = torch.stack([cache.head_lens[l] for l in range(L)]).numpy()
+        # kept scores, recomputed the way the class does (bf16 product), per (layer, segment)
+        for l in range(L):
+            sc = ((q_idx - cache.kv_positions[l].squeeze(-1)) * cache.retention_weights[l].squeeze(-1)).float().numpy()
+            out[f"c{ci}_scores_l{l}"] = sc
+            out[f"c{ci}_pos_l{l}"] = cache.kv_positions[l][:, 0].numpy().astype(np.int32)
+        out[f"c{ci}_logb_bits"] = logb.view(torch.int16).numpy()
+        out[f"c{ci}_lens"] = lens
+    out["meta"] = np.asarray([L, B, H, D, S, M, Bf])
+    out["cases"] = np.asarray([f"{k}|{s}|{t}" for k, s, t in cases])
+    np.savez_compressed(os.path.join(HERE, "flat_budget_bf16.npz"), **out)
+    print("flat_budget_bf16: lens", [out[f"c{ci}_lens"].tolist() for ci in range(len(cases))])
+
+
 def eager_attention(ea):
     """Dense GQA attention from the reference's eager function (fp32), Q=1 and Q=3."""
     torch.manual_seed(3)
@@ -245,4 +280,5 @@ if __name__ == "__main__":
     sliding_window(cu_)
     knorm_alpha(cu_)
     flat_budget(cu_)
+    flat_budget_bf16(cu_)
     eager_attention(ea_)

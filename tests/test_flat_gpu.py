@@ -173,3 +173,37 @@ def test_decode_attention_over_a_budget_sharing_cache():
             lens = cache.head_lens[0].cpu().numpy()
             assert lens.max() > 4 * lens.min()          # the case is ragged
     cache.check_status()
+
+
+@pytest.mark.parametrize("ci", range(5))
+def test_flat_budget_bf16_scores(golden_dir, ci):
+    """bf16 log beta: the flat classes score in bf16 like the reference.  Same rows as the CPU restatement, and
+    against the reference's own result the same kept-score multisets (rows differ only inside tie classes)."""
+    from test_oracle import _bf16_bits_to_f32, check_flat_bf16_case
+    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, DynamicBudgetTrimKVCache
+    g = _g(golden_dir, "flat_budget_bf16.npz")
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    D = 8
+    kind, strategy, thr = str(g["cases"][ci]).split("|")
+    bsz = B if kind == "batched" else 1
+    logb = _bf16_bits_to_f32(g[f"c{ci}_logb_bits"])
+    cache = (BatchedDynamicBudgetTrimKVCache if kind == "batched" else DynamicBudgetTrimKVCache)(device=DEV)
+    want = orc.OracleFlatBudgetCache(kind == "batched", "bfloat16")
+    for l in range(L):
+        k = np.broadcast_to(np.arange(S, dtype=np.float32)[None, None, :, None], (bsz, H, S, D)) + 1000 * l
+        want.update(k, -k, logb[l], np.arange(S), l)
+        kt = torch.from_numpy(np.ascontiguousarray(k)).to(DEV)
+        cache.update(kt, -kt, torch.from_numpy(logb[l]).to(torch.bfloat16).to(DEV), torch.arange(S, device=DEV), l)
+    cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=float(thr), num_layers=L,
+                   num_key_value_heads=H)
+    want.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=float(thr))
+    cache.check_status()
+    lens = torch.stack([cache.head_lens[l] for l in range(L)]).cpu().numpy()
+    assert np.array_equal(lens, np.stack([want.head_lens[l] for l in range(L)]))
+    packed = [cache.packed(l) for l in range(L)]
+    for l in range(L):
+        assert np.array_equal(packed[l][3][:, 0].cpu().numpy(), want.kv_positions[l][:, 0])
+        assert torch.equal(packed[l][0][:, 0], packed[l][3][:, 0].float() + 1000.0 * l)
+    score_of = lambda l: orc.retention_scores(packed[l][2][:, 0].float().cpu().numpy(), packed[l][3][:, 0].cpu().numpy(),
+                                              S + 1, "bfloat16")
+    check_flat_bf16_case(g, ci, lens, lambda l: packed[l][3][:, 0].cpu().numpy().astype(np.int32), score_of)

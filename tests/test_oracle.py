@@ -191,3 +191,85 @@ def test_knorm_alpha_strategy(golden_dir):
             assert np.array_equal(cache.kv_positions[0].astype(np.int32), g["kept_positions"][ev])
             ev += 1
     assert ev == g["kept_positions"].shape[0] and ev >= 2
+
+
+def _bf16_bits_to_f32(bits):
+    return (bits.astype(np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def flat_bf16_groups(kind, strategy, L, bsz, H):
+    """Groups of (layer, segment) pairs that share one budget, in the concatenated order the reference uses."""
+    if "layer_wise" in strategy:
+        return [[(l, b * H + h) for h in range(H)] for l in range(L) for b in range(bsz)]
+    return [[(l, b * H + h) for l in range(L) for h in range(H)] for b in range(bsz)]
+
+
+def check_flat_bf16_case(g, ci, lens, pos_of, score_of):
+    """Shared by the oracle test (CPU) and the CUDA test: compares a compressed cache with what the reference kept.
+    ``lens [L, nseg]``; ``pos_of(l)`` kept positions of layer l in packed order; ``score_of(l)`` their bf16 scores."""
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, thr = str(g["cases"][ci]).split("|")
+    bsz = B if kind == "batched" else 1
+    ref_lens = g[f"c{ci}_lens"]
+    cu_ref = [np.concatenate([[0], np.cumsum(ref_lens[l])]) for l in range(L)]
+    cu_got = [np.concatenate([[0], np.cumsum(lens[l])]) for l in range(L)]
+    exact = 0
+    for grp in flat_bf16_groups(kind, strategy, L, bsz, H):
+        ref_sc = np.concatenate([g[f"c{ci}_scores_l{l}"][cu_ref[l][s]:cu_ref[l][s + 1]] for l, s in grp])
+        got_sc = np.concatenate([score_of(l)[cu_got[l][s]:cu_got[l][s + 1]] for l, s in grp])
+        # Whatever the tie order of torch.topk: the same multiset of kept scores.
+        assert np.array_equal(np.sort(ref_sc), np.sort(got_sc)), (ci, grp[0])
+        ref_pos = [g[f"c{ci}_pos_l{l}"][cu_ref[l][s]:cu_ref[l][s + 1]] for l, s in grp]
+        got_pos = [pos_of(l)[cu_got[l][s]:cu_got[l][s + 1]] for l, s in grp]
+        thr_sc = ref_sc.min()
+        same = all(np.array_equal(a, b) for a, b in zip(ref_pos, got_pos))
+        exact += same
+        if not same:
+            # Differences are confined to rows whose score equals the group's threshold score.
+            for (l, s), a, b in zip(grp, ref_pos, got_pos):
+                full = orc.retention_scores(_bf16_bits_to_f32(g[f"c{ci}_logb_bits"])[l].reshape(-1, S)[s], np.arange(S), S + 1, "bfloat16")
+                for p in np.setxor1d(a, b):
+                    assert full[p] == thr_sc, (ci, l, s, p)
+    return exact
+
+
+@pytest.mark.parametrize("ci", range(5))
+def test_flat_budget_bf16_scores_match_reference(golden_dir, ci):
+    """The flat classes score in the dtype of their tensors; on bf16 inputs the restatement keeps the same multiset
+    of scores as the reference, the same rows wherever no tie straddles a budget, and for the threshold strategy
+    (no top-k, hence no tie order) exactly the same rows."""
+    g = _load(golden_dir, "flat_budget_bf16.npz")
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, thr = str(g["cases"][ci]).split("|")
+    bsz = B if kind == "batched" else 1
+    logb = _bf16_bits_to_f32(g[f"c{ci}_logb_bits"])
+    cache = orc.OracleFlatBudgetCache(kind == "batched", "bfloat16")
+    for l in range(L):
+        k = np.broadcast_to(np.arange(S, dtype=np.float32)[None, None, :, None], (bsz, H, S, D)) + 1000 * l
+        cache.update(k, -k, logb[l], np.arange(S), l)
+    cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=float(thr))
+    lens = np.stack([cache.head_lens[l] for l in range(L)])
+    score_of = lambda l: orc.retention_scores(cache.retention_weights[l][:, 0], cache.kv_positions[l][:, 0], S + 1, "bfloat16")
+    exact = check_flat_bf16_case(g, ci, lens, lambda l: cache.kv_positions[l][:, 0].astype(np.int32), score_of)
+    if "threshold" in strategy:
+        assert np.array_equal(lens, g[f"c{ci}_lens"])
+        assert exact == len(flat_bf16_groups(kind, strategy, L, bsz, H))
+
+
+def test_flat_budget_bf16_fixture_tells_score_dtypes_apart(golden_dir):
+    """Scoring the same inputs in fp32 keeps other rows in at least one case: the fixture pins the dtype."""
+    g = _load(golden_dir, "flat_budget_bf16.npz")
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    differing = 0
+    for ci in range(len(g["cases"])):
+        kind, strategy, thr = str(g["cases"][ci]).split("|")
+        bsz = B if kind == "batched" else 1
+        logb = _bf16_bits_to_f32(g[f"c{ci}_logb_bits"])
+        caches = [orc.OracleFlatBudgetCache(kind == "batched", dt) for dt in ("bfloat16", "float32")]
+        for c in caches:
+            for l in range(L):
+                k = np.broadcast_to(np.arange(S, dtype=np.float32)[None, None, :, None], (bsz, H, S, D)) + 1000 * l
+                c.update(k, -k, logb[l], np.arange(S), l)
+            c.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=float(thr))
+        differing += any(not np.array_equal(caches[0].kv_positions[l], caches[1].kv_positions[l]) for l in range(L))
+    assert differing >= 1

@@ -492,8 +492,9 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
     ``batch_size`` / ``num_kv_heads`` (:682-687); ``compress`` implements ``alpha``, ``layer_wise_alpha``,
     ``alpha_threshold`` with ``floor_budget_ratio`` exactly as :697-945 decide which rows survive.  The rows stay
     in the capacity-strided slabs: the top-k over a request's concatenated scores becomes a keep count per segment
-    (``tkv_group_budget``) followed by the in-place per-segment eviction (``tkv_evict_ex``).  Differences: scores
-    are fp32 (the reference multiplies in the stored dtype, :755), ties go to the lower concatenated index, and
+    (``tkv_group_budget``) followed by the in-place per-segment eviction (``tkv_evict_ex``).  Scores are computed in
+    the dtype log beta arrives in, as the reference does (:755; bf16 models score in bf16).  Differences: log beta is
+    held as fp32 (exact), ties go to the lower concatenated index, and
     K/V are handed out as strided ``[B, Hkv, n_max, D]`` views (``packed(layer)`` builds the reference's
     ``[sum n, D]`` tensors on demand).
     """
@@ -505,6 +506,7 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
             raise NotImplementedError("Distributed cache data is not supported for " + type(self).__name__)
         super().__init__(max_seq_len=max_seq_len, device=device)
         self._rows: List[int] = []   # per layer: total live rows (host copy, refreshed after every eviction)
+        self._beta_dtype = torch.float32  # dtype log beta arrives in: the dtype the reference scores in
         self.batch_size: Optional[int] = None
         self.num_kv_heads: Optional[int] = None
 
@@ -519,6 +521,7 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
             else:
                 assert bsz == self.batch_size, f"Batch size changed: {self.batch_size} -> {bsz}"
                 assert h == self.num_kv_heads, f"Num KV heads changed: {self.num_kv_heads} -> {h}"
+            self._beta_dtype = retention_weights.dtype
             while len(self._rows) <= layer_idx:
                 self._rows.append(0)
             self._rows[layer_idx] += bsz * h * s
@@ -586,20 +589,26 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
                           buffer_size):
         s, nseg, nl = self._slab, self._batch * self._hkv, len(self)
         q_idx = self.get_seq_length() + 1
+        # The reference multiplies (q_idx - pos) * log beta in the dtype log beta arrived in (src/trimkv/cache_utils.py:
+        # 386, 441, 755, 882) and compares with a threshold of that dtype (:462, :893).
+        sd = {torch.bfloat16: 1, torch.float16: 2}.get(self._beta_dtype, 0)
+        if threshold is not None and sd:
+            threshold = float(torch.tensor(threshold, dtype=torch.float32).to(self._beta_dtype))
         keep = torch.empty(nl, nseg, dtype=torch.int32, device=s["k"].device)
         keep.copy_(s["len"])  # layers that do not fire keep everything
         if n_outer > 1:       # one group per request spans all layers
             ops.group_budget(s["beta"], s["pos"], s["len"], self._cap, groups_per_layer, inner, n_outer, nseg, q_idx,
-                             k_total, keep, threshold, floor_mode, floor_cnt, self._status)
+                             k_total, keep, threshold, floor_mode, floor_cnt, self._status, sd)
         else:
             for l in layers:
                 ops.group_budget(s["beta"][l], s["pos"][l], s["len"][l], self._cap, groups_per_layer, inner, 1, nseg,
-                                 q_idx, k_total, keep[l], threshold, floor_mode, floor_cnt, self._status)
+                                 q_idx, k_total, keep[l], threshold, floor_mode, floor_cnt, self._status, sd)
         kept = None
         if self.record_kept:
             kept = torch.full((nl * nseg, self._cap), -1, dtype=torch.int32, device=s["k"].device)
         ops.evict_ex(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap, q_idx,
-                     max(self._cache_len), keep, 0, kept_idx_out=kept, kept_stride=self._cap, status=self._status)
+                     max(self._cache_len), keep, 0, kept_idx_out=kept, kept_stride=self._cap, status=self._status,
+                     score_dtype=sd)
         if kept is not None:
             self.last_kept_idx = kept.view(nl, self._batch, self._hkv, self._cap)
         self._after_eviction(buffer_size)

@@ -36,6 +36,17 @@ __device__ __forceinline__ float retention_score(float log_beta, int32_t pos, in
   return __fmul_rn(log_beta, __ll2float_rn(q_idx - (int64_t)pos));
 }
 
+// The flat budget-sharing caches of the reference multiply in the dtype the gate output is stored in
+// (src/trimkv/cache_utils.py:386,441,755: `(q_idx - kv_pos) * rw` with rw in the model dtype): torch casts the
+// int64 age to that dtype, multiplies in fp32 and rounds the product to it.  score_dtype: 0 = fp32 (one rounding,
+// as TrimKVCache does after its explicit upcast), 1 = bf16, 2 = f16.  log_beta holds the stored value exactly.
+__device__ __forceinline__ float retention_score_as(float log_beta, int32_t pos, int64_t q_idx, int score_dtype) {
+  const float age = __ll2float_rn(q_idx - (int64_t)pos);
+  if (score_dtype == 1) return __bfloat162float(__float2bfloat16_rn(__fmul_rn(log_beta, __bfloat162float(__float2bfloat16_rn(age)))));
+  if (score_dtype == 2) return __half2float(__float2half_rn(__fmul_rn(log_beta, __half2float(__float2half_rn(age)))));
+  return __fmul_rn(log_beta, age);
+}
+
 __device__ __forceinline__ uint4 ld16(const void* p) { return *reinterpret_cast<const uint4*>(p); }
 __device__ __forceinline__ void st16(void* p, uint4 v) { *reinterpret_cast<uint4*>(p) = v; }
 

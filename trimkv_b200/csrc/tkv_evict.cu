@@ -162,6 +162,7 @@ struct EvictParams {
   const int32_t* keep_cnt;   // per-segment number of rows to keep (NULL: m for every segment at or above trigger_len)
   int protect_last;          // the newest `protect_last` rows always score +inf (sliding window)
   int knorm, kv_dtype;       // knorm: score += log ||k||  (strategy "knorm_alpha")
+  int score_dtype;           // dtype the retention score is computed in (retention_score_as)
   int32_t* kept_idx_out; int32_t* status;
   // Plan mode (several CTAs per segment move the rows afterwards): the kept list and {rows kept, first row that
   // moves} go to global memory and nothing is moved here.
@@ -218,14 +219,14 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
         float lg = logf(nrm);
         if (p.kv_dtype == TKV_BF16) lg = __bfloat162float(__float2bfloat16_rn(lg));
         else if (p.kv_dtype == TKV_F16) lg = __half2float(__float2half_rn(lg));
-        const float sc_ = __fadd_rn(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx), lg);
+        const float sc_ = __fadd_rn(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype), lg);
         keys[i] = i >= n - p.protect_last ? score_key(INFINITY) : score_key(sc_);
       }
     }
   } else {
     for (int i = threadIdx.x; i < n; i += kThreads)
       keys[i] = i >= n - p.protect_last ? score_key(INFINITY)
-                                        : score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+                                        : score_key(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
   }
   __syncthreads();
   uint32_t thresh; int n_eq_keep;
@@ -574,7 +575,9 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
   if (!k_cache || !v_cache || !beta_cache || !pos_cache || !seg_len)
     return fail(TKV_ERR_ARG, "tkv_evict: NULL pointer argument");
-  if (strategy != 0 && strategy != 1) return fail(TKV_ERR_ARG, "tkv_evict: unknown strategy %d", strategy);
+  const int score_dtype = (strategy >> 8) & 3;
+  strategy &= 0xff;
+  if ((strategy != 0 && strategy != 1) || score_dtype > 2) return fail(TKV_ERR_ARG, "tkv_evict: unknown strategy %d", strategy);
   if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0 || protect_last < 0)
     return fail(TKV_ERR_ARG, "tkv_evict: bad sizes nseg=%d cap=%lld head_dim=%d M=%d max_len=%d", nseg,
                 (long long)cap, head_dim, memory_size, max_len);
@@ -590,6 +593,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.nseg = nseg; p.cap = cap; p.row_vecs = (int)(row_bytes / 16); p.q_idx = q_idx;
   p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
   p.keep_cnt = keep_cnt; p.protect_last = protect_last; p.knorm = strategy; p.kv_dtype = kv_dtype;
+  p.score_dtype = score_dtype;
   p.kept_idx_out = kept_idx_out; p.status = status;
   p.plan = nullptr; p.plan_kept = nullptr; p.plan_stride = 0; p.plan_tail = nullptr; p.ctas = 1; p.tail_max = 0;
   MoveParams mp;
@@ -763,6 +767,7 @@ struct BudgetParams {
   int inner, n_outer; int64_t outer_stride;     // group g = segments {g*inner + o*outer_stride + i}
   int64_t q_idx; int64_t k_total;
   int use_threshold; float threshold;           // keep score >= threshold instead of the k_total best
+  int score_dtype;                              // see retention_score_as
   int floor_mode, floor_cnt;                    // 0: none, 1: c = min(n, s' + floor) with the reference's boundary
                                                 // attribution for s', 2: c = max(s, min(floor, n))
   int32_t* keep_cnt; int32_t* status;
@@ -814,7 +819,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
           bool valid = i < n;
           uint32_t key = 0;
           if (valid) {
-            key = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+            key = score_key(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
             valid = (key & decided) == prefix;
           }
           const int digit = valid ? (int)((key >> shift) & 255u) : 256 + lane;
@@ -846,7 +851,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
       for (int i = tid; i < n_round; i += kBudgetThreads) {
         uint32_t key = 0;
         const bool valid = i < n;
-        if (valid) key = score_key(retention_score(p.beta[row0 + i], p.pos[row0 + i], p.q_idx));
+        if (valid) key = score_key(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
         const unsigned gt = __ballot_sync(0xffffffffu, valid && key > thresh);
         const unsigned eq = __ballot_sync(0xffffffffu, valid && key == thresh);
         if (lane == 0) {
@@ -875,7 +880,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
         int first = 0;
         if (n > 0) {
           const int64_t row0 = seg_of(j) * p.cap;
-          const uint32_t key0 = score_key(retention_score(p.beta[row0], p.pos[row0], p.q_idx));
+          const uint32_t key0 = score_key(retention_score_as(p.beta[row0], p.pos[row0], p.q_idx, p.score_dtype));
           first = keep_all || key0 > thresh || (key0 == thresh && quota > 0);
         }
         s_eq[j] = first;
@@ -904,10 +909,11 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
 extern "C" int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const int32_t* seg_len, int64_t cap,
                                 int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
                                 int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
-                                int32_t* keep_cnt, int32_t* status, tkv_stream_t stream) {
+                                int score_dtype, int32_t* keep_cnt, int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   if (!beta_cache || !pos_cache || !seg_len || !keep_cnt) return fail(TKV_ERR_ARG, "tkv_group_budget: NULL pointer argument");
-  if (groups < 0 || inner <= 0 || n_outer <= 0 || cap <= 0 || floor_mode < 0 || floor_mode > 2 || floor_cnt < 0)
+  if (groups < 0 || inner <= 0 || n_outer <= 0 || cap <= 0 || floor_mode < 0 || floor_mode > 2 || floor_cnt < 0 ||
+      score_dtype < 0 || score_dtype > 2)
     return fail(TKV_ERR_ARG, "tkv_group_budget: bad sizes groups=%d inner=%d n_outer=%d", groups, inner, n_outer);
   if ((int64_t)inner * n_outer > kBudgetMaxSegs)
     return fail(TKV_ERR_UNSUPPORTED, "tkv_group_budget: %lld segments per group (limit %d)", (long long)inner * n_outer,
@@ -917,6 +923,7 @@ extern "C" int tkv_group_budget(const float* beta_cache, const int32_t* pos_cach
   p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len; p.cap = cap;
   p.inner = inner; p.n_outer = n_outer; p.outer_stride = outer_stride; p.q_idx = q_idx; p.k_total = k_total;
   p.use_threshold = use_threshold; p.threshold = threshold; p.floor_mode = floor_mode; p.floor_cnt = floor_cnt;
+  p.score_dtype = score_dtype;
   p.keep_cnt = keep_cnt; p.status = status;
   group_budget_kernel<<<groups, kBudgetThreads, 0, (cudaStream_t)stream>>>(p);
   return check_launch("tkv_group_budget");
