@@ -207,3 +207,37 @@ def test_flat_budget_bf16_scores(golden_dir, ci):
     score_of = lambda l: orc.retention_scores(packed[l][2][:, 0].float().cpu().numpy(), packed[l][3][:, 0].cpu().numpy(),
                                               S + 1, "bfloat16")
     check_flat_bf16_case(g, ci, lens, lambda l: packed[l][3][:, 0].cpu().numpy().astype(np.int32), score_of)
+
+
+def test_multi_token_query_over_ragged_cache():
+    """A second prompt (Q > 1) appended to a budget-sharing cache whose heads differ in length: bottom-right aligned
+    causal attention per segment, against the per-segment restatement."""
+    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, TrimKVCache
+    from trimkv_b200.attn import TRIMKV_ATTENTION_IMPLEMENTATIONS
+    attn = TRIMKV_ATTENTION_IMPLEMENTATIONS["db_attn_flash_batched"]
+    gen = torch.Generator().manual_seed(9)
+    B, H, G, D, S, M, Bf, Q = 2, 4, 2, 128, 400, 64, 8, 5
+    dt = torch.bfloat16
+    mean = torch.tensor([8.0, 1.0, 0.0, -1.0]).view(1, H, 1)
+    for cls in (BatchedDynamicBudgetTrimKVCache, TrimKVCache):
+        cache = cls(device=DEV)
+        k = torch.randn(B, H, S, D, generator=gen).to(dt).to(DEV)
+        logb = torch.nn.functional.logsigmoid(torch.randn(B, H, S, generator=gen) + mean).to(dt).to(DEV)
+        cache.update(k, -k, logb, torch.arange(S, device=DEV), 0)
+        cache.compress(strategy="alpha", memory_size=M, buffer_size=Bf, num_layers=1, num_key_value_heads=H)
+        k2 = torch.randn(B, H, Q, D, generator=gen).to(dt).to(DEV)
+        kk, vv, _, _, kw = cache.update(k2, -k2, logb[:, :, :Q].contiguous(), torch.arange(S, S + Q, device=DEV), 0)
+        q = torch.randn(B, H * G, Q, D, generator=gen).to(dt).to(DEV)
+        out, _, _ = attn(None, q, kk, vv, None, flash_attn_kwargs=kw)
+        lens = cache.head_lens[0].cpu().numpy()
+        if cls is BatchedDynamicBudgetTrimKVCache:
+            assert lens.max() > 2 * lens.min()
+            kp, vp, _, _ = cache.packed(0)
+        else:
+            kp = torch.cat([kk[b, h, :lens[b * H + h]] for b in range(B) for h in range(H)])
+            vp = torch.cat([vv[b, h, :lens[b * H + h]] for b in range(B) for h in range(H)])
+        want = orc.varlen_gqa_attention(q.float().cpu().numpy(), kp.float().cpu().numpy(), vp.float().cpu().numpy(),
+                                        np.concatenate([[0], np.cumsum(lens)]), B, H)
+        assert out.shape == (B, Q, H * G, D)
+        assert np.max(np.abs(out.float().cpu().numpy() - want)) <= 2e-2
+        cache.check_status()

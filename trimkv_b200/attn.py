@@ -45,6 +45,24 @@ def _dense_causal(query, key, value, scaling):
     return out.transpose(1, 2)
 
 
+def _ragged_causal(query, key, value, head_lens, scaling):
+    """Multi-token queries over strided ``[B,Hkv,n_max,D]`` views whose segments differ in length (a second prompt
+    appended to a budget-sharing cache).  Query row i of segment (b, h) sees keys ``j <= len[b,h] - Q + i``, the
+    bottom-right alignment flash-attn's ``causal=True`` gives the reference (src/trimkv/attn/flash_attn.py:135-145).
+    Not a decode-path kernel: the library attention is called with an explicit mask built from the lengths."""
+    bsz, hq, ql, _ = query.shape
+    hkv, n_max = key.shape[1], key.shape[2]
+    lens = head_lens.view(bsz, hkv, 1, 1).to(torch.int64)
+    j = torch.arange(n_max, device=query.device).view(1, 1, 1, n_max)
+    i = torch.arange(ql, device=query.device).view(1, 1, ql, 1)
+    mask = j <= lens - ql + i                                            # [B, Hkv, Q, n_max]
+    mask = mask[:, :, None].expand(bsz, hkv, hq // hkv, ql, n_max).reshape(bsz, hq, ql, n_max)
+    out = F.scaled_dot_product_attention(query, key, value, attn_mask=mask, scale=scaling, enable_gqa=True)
+    # rows of an empty segment see nothing: zeros, as the decode kernel writes
+    out = torch.where(mask.any(-1, keepdim=True), out, torch.zeros_like(out))
+    return out.transpose(1, 2)
+
+
 def tkv_attention_forward(
     module,
     query: torch.Tensor,
@@ -64,8 +82,7 @@ def tkv_attention_forward(
         if key.dim() != 4:
             raise NotImplementedError("multi-token queries over a packed flat cache")
         if head_lens is not None and not flash_attn_kwargs.get("uniform_lengths", False):
-            raise NotImplementedError("multi-token queries over a cache whose segments differ in length "
-                                      "(chunked prefill over the flat budget-sharing caches is not built)")
+            return _ragged_causal(query, key, value, head_lens, scaling), None, None
         return _dense_causal(query, key, value, scaling), None, None
 
     q3 = query[:, :, 0, :]

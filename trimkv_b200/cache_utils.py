@@ -251,7 +251,8 @@ class TrimKVCache:
         if self._slab is None or self._pending[l] is not None:
             return {}
         return {"head_lens": self._slab["len"][l], "cu_seqlens_k": self._slab["cu"][l],
-                "batch_size": self._batch, "num_kv_heads": self._hkv, "status": self._status}
+                "batch_size": self._batch, "num_kv_heads": self._hkv, "status": self._status,
+                "uniform_lengths": True}   # every segment of a layer has the same length in this class
 
     # ------------------------------------------------------------------ storage
     def _alloc(self, cap: int):
@@ -531,7 +532,7 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
     def _attn_kwargs(self, l: int) -> Dict[str, Any]:
         kw = super()._attn_kwargs(l)
         if kw:
-            kw = dict(kw, batch_size=self._batch, num_kv_heads=self._hkv)
+            kw = dict(kw, batch_size=self._batch, num_kv_heads=self._hkv, uniform_lengths=False)
             if l < len(self._rows):
                 # Head lengths differ under a shared budget; their sum is known here without a device read, which
                 # lets the attention size its grid by tokens instead of by the longest head.
