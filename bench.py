@@ -391,6 +391,9 @@ def main():
     ap.add_argument("--head-sharded", action="store_true",
                     help="N > 1: all ranks decode the same requests, each owning Hkv/N KV heads (all-gather of attention "
                          "outputs per layer) instead of the default batch partition")
+    ap.add_argument("--fused-gather", action="store_true",
+                    help="with --head-sharded: the attention merge kernel stores into every rank's gathered buffer over "
+                         "NVLink and raises a flag, instead of an NCCL all-gather per layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-batch", type=int, default=2, help="requests in the host-core baseline sample")
     ap.add_argument("--cpu-steps", type=int, default=12)
@@ -442,7 +445,8 @@ def main():
             cache = cache.head_shard(rank, world)   # the prompt pass was replicated; keep this rank's KV heads only
             torch.cuda.empty_cache()
         dec = GreedyDecoder(model, cache, use_graph=not args.no_graph, fused=not args.no_fused,
-                            head_shard_group=dist.group.WORLD if sharded else None)
+                            head_shard_group=dist.group.WORLD if sharded else None,
+                            fused_gather=sharded and args.fused_gather)
         dec.ids.copy_(first)
         for _ in range(args.warmup):  # eager warm-up steps (allocate workspaces before any capture)
             dec.step(eager=True)
@@ -571,7 +575,8 @@ def main():
             "scaling": "strong" if sharded else "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "global_batch": B * (1 if sharded else world), "batch_per_gpu": B, "prompt_len": P,
-                       "memory_size": M, "buffer_size": Bf, "parallelism": (f"kv-head-shard x{world}" if sharded else f"batch-partition x{world}"),
+                       "memory_size": M, "buffer_size": Bf, "parallelism": ((f"kv-head-shard x{world}" + (" (merge kernel pushes to peers)" if args.fused_gather else " (NCCL all-gather)"))
+                                       if sharded else f"batch-partition x{world}"),
                        "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
                        "l2": "per-step working set (all weights + every cached K/V row, many GB) exceeds the 126 MB L2; no explicit flush"},
             "roofline": roofline, "evict": evict, "cpu_baseline": cpu,

@@ -240,6 +240,45 @@ int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
                            int32_t* status, tkv_stream_t stream);
 
 /*
+ * Head-sharded decode (each rank holds hkv of the KV heads and their hq query heads; no counterpart in the
+ * single-process reference): tkv_decode_attn whose merge step stores the result straight into the gathered
+ * [batch, out_row_stride] buffer of EVERY rank, at element column out_col_offset, and then raises this rank's flag
+ * on every peer; it replaces "attention, then all-gather" by one pass.  peer_out[r] / peer_flags[r]: HOST arrays of
+ * `world` device pointers (rank r's buffer and its int32[world] flag array, mapped into this process, e.g. through
+ * CUDA IPC; entry `rank` is this rank's own memory).  Only plain stores go to peer memory; nothing is read from it.
+ * sync_state: int32[3] in this rank's memory, zero before the first exchange, private to this (stream, group).
+ * `out` is still required (scratch for single-chunk problems).  world <= 8.
+ * tkv_peer_wait: to be enqueued before the first kernel that reads the gathered buffer; returns (on the stream)
+ * once every peer's flag has reached this rank's exchange count.  The wait is bounded (about four seconds), after
+ * which the status word reports TKV_DEV_TIMEOUT and the stream continues.
+ * A buffer may be written again by the peers two exchanges later; use at least two (three if the number of
+ * exchanges per step is odd) in rotation.
+ */
+int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
+                         const void* k_cache, const void* v_cache,
+                         const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                         void* out, void* workspace, size_t workspace_bytes,
+                         int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                         float scale, int max_len,
+                         void* const* peer_out, int32_t* const* peer_flags, int world, int rank,
+                         int64_t out_row_stride, int64_t out_col_offset, int32_t* sync_state,
+                         int32_t* status, tkv_stream_t stream);
+int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank, int32_t* status,
+                  tkv_stream_t stream);
+/* Lets kernels of the current device store to memory of peer_device (cudaDeviceEnablePeerAccess; a no-op if it is
+ * already enabled or peer_device is the current device).  Needed once per peer before tkv_decode_attn_push. */
+int tkv_enable_peer_access(int peer_device);
+/* Sharing a device allocation between the rank processes of one box (CUDA IPC; host-only calls, no kernel).
+ * tkv_ipc_export: handle (TKV_IPC_HANDLE_BYTES bytes) of the allocation that contains ptr, and ptr's offset in it.
+ * tkv_ipc_import: maps an exported allocation into this process with the CURRENT device (peer access to the owning
+ * GPU is enabled by the mapping); *base_out + offset is the peer's ptr.  One import per handle and process.
+ * tkv_ipc_close: unmaps. */
+#define TKV_IPC_HANDLE_BYTES 64
+int tkv_ipc_export(const void* ptr, void* handle_out, int64_t* offset_out);
+int tkv_ipc_import(const void* handle, void** base_out);
+int tkv_ipc_close(void* base);
+
+/*
  * tkv_decode_attn for callers that cannot allocate device memory.  (No counterpart in the reference: its
  * attention always runs inside PyTorch, whose allocator provides flash-attn's temporaries.)
  * Meant for hosts that cannot hand the library a workspace: a server whose block arena already owns the whole

@@ -1,4 +1,5 @@
-"""KV-head-sharded decode on two B200s (NCCL): every rank's logits equal the unsharded step's."""
+"""KV-head-sharded decode on two B200s: every rank's logits equal the unsharded step's, with the all-gather done
+by NCCL and with the attention merge pushing its block into the peers' buffers itself."""
 import os
 import socket
 
@@ -15,6 +16,9 @@ def _free_port():
         return s.getsockname()[1]
 
 
+MODES = ("full", "sharded", "sharded_graph", "pushed", "pushed_graph")
+
+
 def _worker(rank, world, port, q):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     import torch.distributed as dist
@@ -24,38 +28,50 @@ def _worker(rank, world, port, q):
     try:
         from trimkv_b200 import TrimKVCache, TrimKVQwen3Config, TrimKVQwen3ForCausalLM
         from trimkv_b200.decoder import GreedyDecoder
-        cfg = TrimKVQwen3Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=2,
-                                num_attention_heads=8, num_key_value_heads=4, head_dim=128,
-                                retention_gate_intermediate_size=32, retention_gate_bias_init=3.0, memory_size=48,
-                                buffer_size=8, initializer_range=0.02)
-        torch.manual_seed(0)
-        model = TrimKVQwen3ForCausalLM(cfg).to(torch.bfloat16).eval().to(dev)
-        gen = torch.Generator().manual_seed(3)
-        prompt = torch.randint(0, cfg.vocab_size, (3, 70), generator=gen).to(dev)
-        forced = torch.randint(0, cfg.vocab_size, (24, 3, 1), generator=gen).to(dev)
         results = {}
-        with torch.inference_mode():
-            for mode in ("full", "sharded", "sharded_graph"):
-                cache = TrimKVCache(device=dev)
-                out = model(input_ids=prompt, past_key_values=cache, logits_to_keep=1)   # replicated prompt pass
-                if mode == "full":
-                    dec = GreedyDecoder(model, cache, use_graph=False, fused=True)
-                else:
-                    local = cache.head_shard(rank, world)
-                    dec = GreedyDecoder(model, local, use_graph=(mode == "sharded_graph"), head_shard_group=dist.group.WORLD)
-                    cache = local
-                logits = []
-                for t in range(24):
-                    dec.step(forced[t], eager=(t < 2))
-                    logits.append(dec.logits.float().clone())
-                cache.check_status()
-                n = cache.get_cache_length(0)
-                results[mode] = (torch.stack(logits).cpu().numpy(), cache.kv_positions[0][:, :, :n].cpu().numpy(), n)  # by value
+        # (memory_size, buffer_size, prompt length, layers): a cache of one chunk per segment, and one of several
+        # chunks (merge of partials) with an odd number of layers (buffer rotation across steps)
+        for tag, (M, Bf, P, L) in {"short": (48, 8, 70, 2), "long": (600, 40, 700, 3)}.items():
+            cfg = TrimKVQwen3Config(vocab_size=512, hidden_size=256, intermediate_size=512, num_hidden_layers=L,
+                                    num_attention_heads=8, num_key_value_heads=4, head_dim=128,
+                                    retention_gate_intermediate_size=32, retention_gate_bias_init=3.0, memory_size=M,
+                                    buffer_size=Bf, initializer_range=0.02)
+            torch.manual_seed(0)
+            model = TrimKVQwen3ForCausalLM(cfg).to(torch.bfloat16).eval().to(dev)
+            gen = torch.Generator().manual_seed(3)
+            prompt = torch.randint(0, cfg.vocab_size, (3, P), generator=gen).to(dev)
+            forced = torch.randint(0, cfg.vocab_size, (24, 3, 1), generator=gen).to(dev)
+            with torch.inference_mode():
+                for mode in MODES:
+                    cache = TrimKVCache(device=dev)
+                    out = model(input_ids=prompt, past_key_values=cache, logits_to_keep=1)   # replicated prompt pass
+                    if mode == "full":
+                        dec = GreedyDecoder(model, cache, use_graph=False, fused=True)
+                    else:
+                        local = cache.head_shard(rank, world)
+                        dec = GreedyDecoder(model, local, use_graph=mode.endswith("_graph"), head_shard_group=dist.group.WORLD,
+                                            fused_gather=mode.startswith("pushed"))
+                        cache = local
+                    logits = []
+                    for t in range(24):
+                        dec.step(forced[t], eager=(t < 2))
+                        logits.append(dec.logits.float().clone())
+                    cache.check_status()
+                    n = cache.get_cache_length(0)
+                    results[tag + "/" + mode] = (torch.stack(logits).cpu().numpy(),
+                                                 cache.kv_positions[0][:, :, :n].cpu().numpy(), n)  # by value
+                    torch.cuda.synchronize()
+                    dist.barrier()
         q.put((rank, results))
         q.close()
         q.join_thread()          # results are on their way before anything else can go wrong
         torch.cuda.synchronize()
         dist.barrier()
+    except Exception:            # the parent must see the failure instead of waiting for a result that never comes
+        import traceback
+        q.put((rank, {"error": traceback.format_exc()}))
+        q.close()
+        q.join_thread()
     finally:
         # Leave without NCCL / CUDA-graph teardown: destroying a communicator whose collectives were captured in a
         # still-live CUDA graph did not return here, and the test is about the numbers, which are already sent.
@@ -78,12 +94,19 @@ def test_head_sharded_decode_equals_unsharded():
             if p.is_alive():
                 p.terminate()
     for rank in range(world):
-        full_logits, full_pos, n_full = got[rank]["full"]
-        for mode in ("sharded", "sharded_graph"):
-            logits, pos, n = got[rank][mode]
-            assert n == n_full
-            assert float(np.abs(logits - full_logits).max()) <= 2e-2, (rank, mode)
-            hl = full_pos.shape[1] // world
-            assert np.array_equal(pos, full_pos[:, rank * hl:(rank + 1) * hl]), (rank, mode)  # same survivors per head
-    # both ranks hold the same logits (replicated tail of the layer)
-    assert np.array_equal(got[0]["sharded"][0], got[1]["sharded"][0])
+        assert "error" not in got[rank], got[rank]["error"]
+    for tag in ("short", "long"):
+        for rank in range(world):
+            full_logits, full_pos, n_full = got[rank][tag + "/full"]
+            for mode in MODES[1:]:
+                logits, pos, n = got[rank][tag + "/" + mode]
+                assert n == n_full
+                assert float(np.abs(logits - full_logits).max()) <= 2e-2, (tag, rank, mode)
+                hl = full_pos.shape[1] // world
+                assert np.array_equal(pos, full_pos[:, rank * hl:(rank + 1) * hl]), (tag, rank, mode)  # same survivors per head
+            # the pushed exchange moves the same bf16 values as the all-gather
+            assert np.array_equal(got[rank][tag + "/pushed"][0], got[rank][tag + "/sharded"][0]), (tag, rank)
+            assert np.array_equal(got[rank][tag + "/pushed_graph"][0], got[rank][tag + "/sharded_graph"][0]), (tag, rank)
+        # both ranks hold the same logits (replicated tail of the layer)
+        assert np.array_equal(got[0][tag + "/sharded"][0], got[1][tag + "/sharded"][0])
+        assert np.array_equal(got[0][tag + "/pushed"][0], got[1][tag + "/pushed"][0])

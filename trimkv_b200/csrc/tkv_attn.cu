@@ -186,6 +186,63 @@ decode_attn_split_kernel(AttnParams p) {
   }
 }
 
+// Merged output value of (segment, query head g, dimension d) from the chunk partials; 0 for an empty segment.
+// Called by every thread of a kD-thread block (it synchronises the block).
+template <int kD>
+__device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, int g, int d, int len) {
+  const int G = p.hq / p.hkv;
+  float r = 0.f;
+  const int nact = (len + p.chunk - 1) / p.chunk;
+  const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
+  if (nact <= kD) {
+    // One round trip for all (max, sum) pairs: thread c takes chunk c, the block reduces, the weights go to
+    // shared memory; then every thread sums its output dimension over the chunks with independent loads.
+    __shared__ float s_w[kD];
+    __shared__ float s_red[2][kD / 32];
+    const int lane = d & 31, warp = d >> 5;
+    float mc = -INFINITY, lc = 0.f;
+    if (d < nact) {
+      const float2 ml = *reinterpret_cast<const float2*>(&p.part_ml[(it0 + (int64_t)d * G) * 2]);
+      mc = ml.x; lc = ml.y;
+    }
+    float mx = mc;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    if (lane == 0) s_red[0][warp] = mx;
+    __syncthreads();
+    mx = s_red[0][0];
+#pragma unroll
+    for (int w = 1; w < kD / 32; ++w) mx = fmaxf(mx, s_red[0][w]);
+    const float wgt = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
+    if (d < nact) s_w[d] = wgt;
+    float ls = lc * wgt;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
+    if (lane == 0) s_red[1][warp] = ls;
+    __syncthreads();
+    ls = 0.f;
+#pragma unroll
+    for (int w = 0; w < kD / 32; ++w) ls += s_red[1][w];
+    float o = 0.f;
+#pragma unroll 8
+    for (int c = 0; c < nact; ++c) o = fmaf(p.part_o[(it0 + (int64_t)c * G) * kD + d], s_w[c], o);
+    r = ls > 0.f ? o / ls : 0.f;
+  } else {
+    float mx = -INFINITY;
+    for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(it0 + (int64_t)c * G) * 2]);
+    float o = 0.f, ls = 0.f;
+    for (int c = 0; c < nact; ++c) {
+      const int64_t it = it0 + (int64_t)c * G;
+      const float mc = p.part_ml[it * 2];
+      const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
+      o = fmaf(p.part_o[it * kD + d], w, o);
+      ls = fmaf(p.part_ml[it * 2 + 1], w, ls);
+    }
+    r = ls > 0.f ? o / ls : 0.f;
+  }
+  return r;
+}
+
 // Merges the chunk partials of one segment; also writes zeros for empty segments.
 template <int kDtype, int kD>
 __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
@@ -199,57 +256,77 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   float r = 0.f;
   if (len > 0) {
     if (p.nchunks == 1) return;  // written by the split kernel
-    const int nact = (len + p.chunk - 1) / p.chunk;
-    const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
-    if (nact <= kD) {
-      // One round trip for all (max, sum) pairs: thread c takes chunk c, the block reduces, the weights go to
-      // shared memory; then every thread sums its output dimension over the chunks with independent loads.
-      __shared__ float s_w[kD];
-      __shared__ float s_red[2][kD / 32];
-      const int lane = d & 31, warp = d >> 5;
-      float mc = -INFINITY, lc = 0.f;
-      if (d < nact) {
-        const float2 ml = *reinterpret_cast<const float2*>(&p.part_ml[(it0 + (int64_t)d * G) * 2]);
-        mc = ml.x; lc = ml.y;
-      }
-      float mx = mc;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
-      if (lane == 0) s_red[0][warp] = mx;
-      __syncthreads();
-      mx = s_red[0][0];
-#pragma unroll
-      for (int w = 1; w < kD / 32; ++w) mx = fmaxf(mx, s_red[0][w]);
-      const float wgt = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
-      if (d < nact) s_w[d] = wgt;
-      float ls = lc * wgt;
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
-      if (lane == 0) s_red[1][warp] = ls;
-      __syncthreads();
-      ls = 0.f;
-#pragma unroll
-      for (int w = 0; w < kD / 32; ++w) ls += s_red[1][w];
-      float o = 0.f;
-#pragma unroll 8
-      for (int c = 0; c < nact; ++c) o = fmaf(p.part_o[(it0 + (int64_t)c * G) * kD + d], s_w[c], o);
-      r = ls > 0.f ? o / ls : 0.f;
-    } else {
-      float mx = -INFINITY;
-      for (int c = 0; c < nact; ++c) mx = fmaxf(mx, p.part_ml[(it0 + (int64_t)c * G) * 2]);
-      float o = 0.f, ls = 0.f;
-      for (int c = 0; c < nact; ++c) {
-        const int64_t it = it0 + (int64_t)c * G;
-        const float mc = p.part_ml[it * 2];
-        const float w = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
-        o = fmaf(p.part_o[it * kD + d], w, o);
-        ls = fmaf(p.part_ml[it * 2 + 1], w, ls);
-      }
-      r = ls > 0.f ? o / ls : 0.f;
-    }
+    r = merge_partials<kD>(p, seg, g, d, len);
   }
   if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16_rn(r);
   else reinterpret_cast<__half*>(op)[d] = __float2half_rn(r);
+}
+
+__device__ __forceinline__ void st_release_sys(int32_t* p, int v) {
+  asm volatile("st.release.sys.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int32_t* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.b32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// The merge of a head-sharded decode step, fused with the exchange that follows it: each value goes to this
+// rank's column block of the gathered [batch, Hq_total * D] buffer of EVERY rank with a plain store (peer memory,
+// NVLink); when the whole grid has stored (fence + counter), the last CTA raises this rank's flag on every peer
+// with a system-scope release.  Nothing is read from peer memory.
+template <int kDtype, int kD>
+__global__ void __launch_bounds__(kD) decode_attn_combine_push_kernel(AttnParams p, PushParams pp) {
+  const int seg = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
+  grid_dependency_wait();
+  if (p.seg_len[seg] > p.max_len && g == 0 && d == 0) report(p.status, TKV_DEV_LEN_BOUND);
+  const int len = min(p.seg_len[seg], p.max_len);
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+  const int G = p.hq / p.hkv;
+  uint16_t bits = 0;
+  if (len > 0) {
+    if (p.nchunks == 1) {
+      bits = reinterpret_cast<const uint16_t*>(p.out + ((int64_t)b * p.hq + h * G + g) * (int64_t)kD * 2)[d];
+    } else {
+      const float r = merge_partials<kD>(p, seg, g, d, len);
+      if (kDtype == TKV_BF16) bits = __bfloat16_as_ushort(__float2bfloat16_rn(r));
+      else bits = __half_as_ushort(__float2half_rn(r));
+    }
+  }
+  const int64_t off = ((int64_t)b * pp.row_stride + pp.col_offset + (int64_t)(h * G + g) * kD + d) * 2;
+  for (int r = 0; r < pp.world; ++r) *reinterpret_cast<uint16_t*>(pp.peer_out[r] + off) = bits;
+  __threadfence_system();
+  __syncthreads();
+  if (d == 0) {
+    const int total = gridDim.x * gridDim.y;
+    if (atomicAdd(&pp.sync[0], 1) == total - 1) {
+      pp.sync[0] = 0;
+      __threadfence_system();
+      const int epoch = pp.sync[1] + 1;
+      pp.sync[1] = epoch;
+      for (int r = 0; r < pp.world; ++r)
+        if (r != pp.rank) st_release_sys(pp.peer_flags[r] + pp.rank, epoch);
+    }
+  }
+}
+
+// Waits until every peer has raised its flag for the next exchange (the counterpart of the kernel above on the
+// receiving side).  One warp, lane r watches rank r; bounded: after about four seconds the lane gives up, the
+// status word says TKV_DEV_TIMEOUT and the stream carries on, so a missing peer cannot hang the GPU.
+__global__ void __launch_bounds__(32) peer_wait_kernel(const int32_t* flags, int32_t* sync, int world, int rank,
+                                                       int32_t* status) {
+  const int lane = threadIdx.x;
+  const int expected = sync[2] + 1;
+  __syncwarp();
+  if (lane < world && lane != rank) {
+    int spins = 0;
+    while (ld_acquire_sys(flags + lane) - expected < 0) {
+      if (++spins > (1 << 24)) { report(status, TKV_DEV_TIMEOUT); break; }
+      __nanosleep(200);
+    }
+  }
+  __syncwarp();
+  if (lane == 0) sync[2] = expected;
 }
 
 template <int kDtype, int kD, int kG>
@@ -266,7 +343,7 @@ static int launch_split(const AttnParams& p, int nseg, cudaStream_t st) {
 }
 
 template <int kDtype, int kD>
-static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st) {
+static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st, const PushParams* push) {
   int rc;
   switch (G) {
     case 1: rc = launch_split<kDtype, kD, 1>(p, nseg, st); break;
@@ -280,13 +357,17 @@ static int launch_for_g(const AttnParams& p, int nseg, int G, cudaStream_t st) {
     default: return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn: %d query heads per KV head (supported: 1..8)", G);
   }
   if (rc != TKV_OK) return rc;
-  decode_attn_combine_kernel<kDtype, kD><<<dim3(nseg, G), kD, 0, st>>>(p);
+  if (push != nullptr) decode_attn_combine_push_kernel<kDtype, kD><<<dim3(nseg, G), kD, 0, st>>>(p, *push);
+  else decode_attn_combine_kernel<kDtype, kD><<<dim3(nseg, G), kD, 0, st>>>(p);
   return check_launch("tkv_decode_attn(combine)");
 }
 
-int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st) {
+int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st,
+                               const PushParams* push) {
   cudaError_t e;
-  if (head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
+  if (push != nullptr && head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_push_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p, *push);
+  else if (push != nullptr && head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_push_kernel<TKV_F16, 128>, dim3(nseg, G), dim3(128), 0, st, p, *push);
+  else if (head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
   else if (head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_kernel<TKV_F16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
   else return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(combine): head_dim=%d dtype=%d", head_dim, kv_dtype);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(combine): %s", cudaGetErrorString(e));
@@ -312,11 +393,12 @@ int attn_chunk_tokens(int nseg, int max_len) {
   return chunk;
 }
 
-int launch_decode_attn_simt(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st) {
-  if (kv_dtype == TKV_BF16 && head_dim == 128) return launch_for_g<TKV_BF16, 128>(p, nseg, G, st);
-  if (kv_dtype == TKV_F16 && head_dim == 128) return launch_for_g<TKV_F16, 128>(p, nseg, G, st);
-  if (kv_dtype == TKV_BF16 && head_dim == 64) return launch_for_g<TKV_BF16, 64>(p, nseg, G, st);
-  if (kv_dtype == TKV_F16 && head_dim == 64) return launch_for_g<TKV_F16, 64>(p, nseg, G, st);
+int launch_decode_attn_simt(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st,
+                            const PushParams* push = nullptr) {
+  if (kv_dtype == TKV_BF16 && head_dim == 128) return launch_for_g<TKV_BF16, 128>(p, nseg, G, st, push);
+  if (kv_dtype == TKV_F16 && head_dim == 128) return launch_for_g<TKV_F16, 128>(p, nseg, G, st, push);
+  if (kv_dtype == TKV_BF16 && head_dim == 64) return launch_for_g<TKV_BF16, 64>(p, nseg, G, st, push);
+  if (kv_dtype == TKV_F16 && head_dim == 64) return launch_for_g<TKV_F16, 64>(p, nseg, G, st, push);
   return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn: head_dim=%d dtype=%d (supported: bf16/f16, 64 or 128)", head_dim,
               kv_dtype);
 }
@@ -356,7 +438,8 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
                             const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
                             void* out, void* workspace, size_t workspace_bytes,
                             int batch, int hq, int hkv, int head_dim, int kv_dtype,
-                            float scale, int max_len, int64_t total_len_bound, int32_t* status, tkv_stream_t stream) {
+                            float scale, int max_len, int64_t total_len_bound, int32_t* status, tkv_stream_t stream,
+                            const tkv::PushParams* push = nullptr) {
   using namespace tkv;
   if (!q || !k_cache || !v_cache || !seg_len || !out) return fail(TKV_ERR_ARG, "%s: NULL pointer argument", who);
   if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || head_dim <= 0 || max_len <= 0)
@@ -387,7 +470,7 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.work = nullptr; p.work_count = nullptr; p.work_capacity = 0;
-  if (!tc) return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+  if (!tc) return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream, push);
   if (ragged && p.nchunks < 256) {
     const int64_t items = ragged_items(nseg, max_len, total_len_bound);
     // Only worth the extra launch when it removes a good part of the grid.
@@ -402,7 +485,7 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
   }
   int rc = launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
   if (rc != TKV_OK) return rc;
-  return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
+  return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream, push);
 }
 
 extern "C" int tkv_decode_attn(const void* q, int64_t q_sb, int64_t q_sh,
@@ -426,6 +509,43 @@ extern "C" int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
   return decode_attn_impl("tkv_decode_attn_ragged", q, q_sb, q_sh, k_cache, v_cache, seg_len, seg_start, cap, out,
                           workspace, workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, total_len_bound,
                           status, stream);
+}
+
+extern "C" int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
+                                    const void* k_cache, const void* v_cache,
+                                    const int32_t* seg_len, const int32_t* seg_start, int64_t cap,
+                                    void* out, void* workspace, size_t workspace_bytes,
+                                    int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                                    float scale, int max_len,
+                                    void* const* peer_out, int32_t* const* peer_flags, int world, int rank,
+                                    int64_t out_row_stride, int64_t out_col_offset, int32_t* sync_state,
+                                    int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!peer_out || !peer_flags || !sync_state) return fail(TKV_ERR_ARG, "tkv_decode_attn_push: NULL pointer argument");
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_push: world=%d (limit %d) rank=%d", world, kMaxPeers, rank);
+  if (out_row_stride < (int64_t)hq * head_dim || out_col_offset < 0 || out_col_offset + (int64_t)hq * head_dim > out_row_stride)
+    return fail(TKV_ERR_ARG, "tkv_decode_attn_push: column block [%lld, +%d) does not fit rows of %lld elements",
+                (long long)out_col_offset, hq * head_dim, (long long)out_row_stride);
+  PushParams pp;
+  for (int r = 0; r < kMaxPeers; ++r) { pp.peer_out[r] = nullptr; pp.peer_flags[r] = nullptr; }
+  for (int r = 0; r < world; ++r) {
+    if (!peer_out[r] || !peer_flags[r]) return fail(TKV_ERR_ARG, "tkv_decode_attn_push: NULL pointer for rank %d", r);
+    pp.peer_out[r] = (char*)peer_out[r]; pp.peer_flags[r] = peer_flags[r];
+  }
+  pp.world = world; pp.rank = rank; pp.row_stride = out_row_stride; pp.col_offset = out_col_offset; pp.sync = sync_state;
+  return decode_attn_impl("tkv_decode_attn_push", q, q_sb, q_sh, k_cache, v_cache, seg_len, seg_start, cap, out, workspace,
+                          workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, -1, status, stream, &pp);
+}
+
+extern "C" int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank, int32_t* status,
+                             tkv_stream_t stream) {
+  using namespace tkv;
+  if (!flags || !sync_state) return fail(TKV_ERR_ARG, "tkv_peer_wait: NULL pointer argument");
+  if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
+    return fail(TKV_ERR_ARG, "tkv_peer_wait: world=%d rank=%d", world, rank);
+  peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, sync_state, world, rank, status);
+  return check_launch("tkv_peer_wait");
 }
 
 // ---------------------------------------------------------------------------------------------------------

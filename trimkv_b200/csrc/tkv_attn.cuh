@@ -21,6 +21,18 @@ struct AttnParams {
   const int2* work; const int32_t* work_count; int work_capacity;
 };
 
+// Head-sharded decode: the merge kernel stores this rank's heads straight into every rank's gathered buffer (plain
+// stores to peer memory over NVLink) and the last CTA raises a flag on every peer.
+constexpr int kMaxPeers = 8;
+struct PushParams {
+  char* peer_out[kMaxPeers];        // [batch, row_stride] of K/V dtype on every rank (own rank included)
+  int32_t* peer_flags[kMaxPeers];   // [world] int32 on every rank; entry `rank` is written by this rank
+  int world, rank;
+  int64_t row_stride;               // elements between consecutive requests in peer_out
+  int64_t col_offset;               // element offset of this rank's first head in a row
+  int32_t* sync;                    // device, this rank: [0] CTA counter, [1] exchanges sent, [2] exchanges received
+};
+
 // Tokens per work item, a pure function of the problem size (the workspace size depends on it).
 int attn_chunk_tokens(int nseg, int max_len);
 
@@ -31,6 +43,7 @@ int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, in
 // Builds the compact work list of the tensor-core split kernel from the lengths (one small kernel).
 int launch_attn_worklist(const AttnParams& p, int nseg, cudaStream_t st);
 // Merge kernel shared by both split kernels.
-int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st);
+int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_dim, int kv_dtype, cudaStream_t st,
+                               const PushParams* push = nullptr);
 
 }  // namespace tkv

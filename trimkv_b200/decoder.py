@@ -118,11 +118,12 @@ class GreedyDecoder:
     previous step's argmax without leaving the device.  Returns the device tensor holding the new ids.
     """
 
-    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True, head_shard_group=None):
+    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True, head_shard_group=None,
+                 fused_gather: bool = False):
         self.model, self.cache, self.cfg = model, cache, model.config
         self.fused = None
         if head_shard_group is not None:
-            self.fused = HeadShardedDecodeStep(model, cache, head_shard_group)
+            self.fused = HeadShardedDecodeStep(model, cache, head_shard_group, fused_gather=fused_gather)
         elif fused and model.config.head_dim == 128 and model.config.retention_gate == "rg" \
                 and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
             self.fused = FusedDecodeStep(model, cache)
@@ -200,10 +201,13 @@ class HeadShardedDecodeStep(FusedDecodeStep):
     process); per head the arithmetic is that of the unsharded step.
     """
 
-    def __init__(self, model, cache: TrimKVCache, group=None):
+    def __init__(self, model, cache: TrimKVCache, group=None, fused_gather: bool = False):
         import torch.distributed as dist
         super().__init__(model, cache)
         self.group = group
+        # fused_gather: the attention merge stores into every rank's gathered buffer over NVLink and raises a flag
+        # (PeerExchange) instead of a separate all-gather; set up lazily, when the batch size is known.
+        self.fused_gather, self._xchg = fused_gather, None
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         cfg = model.config
         if cfg.num_key_value_heads % self.world:
@@ -225,6 +229,28 @@ class HeadShardedDecodeStep(FusedDecodeStep):
                 self.local.append((w[rows].contiguous(), None if bias is None else bias[rows].contiguous(),
                                    g.linear2.weight[h0:h0 + self.hkv_l].contiguous(), g.bias[h0:h0 + self.hkv_l].contiguous()))
 
+    def _attend_and_push(self, l, q_out, k, v, kw, scaling):
+        """Attention of this rank's heads, merged straight into every rank's gathered buffer; returns the local one
+        once all ranks' blocks have arrived (stream-ordered)."""
+        from .attn import _workspace
+        from .parallel import PeerExchange
+        bsz, dim = q_out.shape[0], q_out.shape[-1]
+        width = self.hq_l * self.world * dim
+        if self._xchg is None:
+            self._xchg = PeerExchange(bsz, width, q_out.dtype, q_out.device, nbuf=3, group=self.group)
+            self._local_out = torch.empty(bsz, self.hq_l, dim, dtype=q_out.dtype, device=q_out.device)
+        x = self._xchg
+        # Layer 0 has a buffer of its own and the others alternate, so that a buffer is never rewritten before
+        # every rank has read its previous content (see tkv_decode_attn_push in the header).
+        i = 2 if l == 0 else (l & 1)
+        max_len, cap = k.shape[2], k.stride(1) // dim
+        ws = _workspace(q_out.device, ops.decode_attn_workspace_bytes(bsz, self.hq_l, self.hkv_l, dim, max_len))
+        ops.decode_attn_push(q_out[:, :, 0, :], k, v, kw["head_lens"], cap, self._local_out, ws, self.hkv_l, scaling,
+                             max_len, x.out_ptrs[i], x.flag_ptrs, self.world, self.rank, width,
+                             self.rank * self.hq_l * dim, x.sync, kw.get("status"))
+        ops.peer_wait(x.flags, x.sync, self.world, self.rank, kw.get("status"))
+        return x.buffer(i)
+
     def __call__(self, ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
         import torch.nn.functional as F
@@ -245,9 +271,12 @@ class HeadShardedDecodeStep(FusedDecodeStep):
             qkvg = F.linear(h, w_l, b_l)
             k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin, g2_l, gb_l,
                                          pos, q_out, self.hq_l)
-            o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
-            dist.all_gather_into_tensor(gathered, o.view(bsz, -1), group=self.group)
-            full = gathered.permute(1, 0, 2).reshape(bsz, -1)      # rank-major head blocks = head order
+            if self.fused_gather:
+                full = self._attend_and_push(l, q_out, k, v, kw, at.scaling)
+            else:
+                o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
+                dist.all_gather_into_tensor(gathered, o.view(bsz, -1), group=self.group)
+                full = gathered.permute(1, 0, 2).reshape(bsz, -1)      # rank-major head blocks = head order
             a = F.linear(full, at.o_proj.weight, at.o_proj.bias)
             ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps)
             gu = F.linear(h, w_gu)

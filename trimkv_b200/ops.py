@@ -158,6 +158,56 @@ def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspac
     _count(2)
 
 
+def decode_attn_push(q, k_cache, v_cache, seg_len, cap: int, out, workspace, hkv: int, scale: float, max_len: int,
+                     peer_out, peer_flags, world: int, rank: int, row_stride: int, col_offset: int, sync_state,
+                     status=None) -> None:
+    """:func:`decode_attn` whose merge step stores into every rank's gathered buffer and raises this rank's flag on
+    the peers.  ``peer_out`` / ``peer_flags``: ``ctypes`` arrays of ``world`` device pointers."""
+    b, hq, d = q.shape
+    if q.stride(2) != 1:
+        q = q.contiguous()
+    rc = lib().tkv_decode_attn_push(
+        q.data_ptr(), q.stride(0), q.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
+        seg_len.data_ptr(), None, cap, out.data_ptr(), workspace.data_ptr(), workspace.numel(),
+        b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len,
+        peer_out, peer_flags, world, rank, row_stride, col_offset, sync_state.data_ptr(), _ptr(status), _stream(q))
+    check(rc, "tkv_decode_attn_push")
+    _count(2)
+
+
+def enable_peer_access(peer_device: int) -> None:
+    check(lib().tkv_enable_peer_access(int(peer_device)), "tkv_enable_peer_access")
+
+
+def ipc_export(t: torch.Tensor):
+    """``(handle bytes, offset)`` under which other rank processes of this box can map ``t``'s allocation."""
+    import ctypes
+    handle, off = ctypes.create_string_buffer(64), ctypes.c_int64(0)
+    check(lib().tkv_ipc_export(t.data_ptr(), handle, ctypes.byref(off)), "tkv_ipc_export")
+    return handle.raw, int(off.value)
+
+
+_ipc_bases = {}   # (device, handle) -> base address: an allocation is mapped once per process and device
+
+
+def ipc_import(handle: bytes) -> int:
+    """Maps an exported allocation with the current device; returns its base address in this process."""
+    import ctypes
+    key = (torch.cuda.current_device(), handle)
+    if key not in _ipc_bases:
+        base = ctypes.c_void_p(0)
+        check(lib().tkv_ipc_import(ctypes.create_string_buffer(handle, 64), ctypes.byref(base)), "tkv_ipc_import")
+        _ipc_bases[key] = int(base.value)
+    return _ipc_bases[key]
+
+
+def peer_wait(flags, sync_state, world: int, rank: int, status=None) -> None:
+    """Holds the stream until every peer has raised its flag for this rank's next exchange (bounded)."""
+    rc = lib().tkv_peer_wait(flags.data_ptr(), sync_state.data_ptr(), world, rank, _ptr(status), _stream(flags))
+    check(rc, "tkv_peer_wait")
+    _count(1)
+
+
 def decode_prep(qkvg, q_norm_w, k_norm_w, eps: float, cos, sin, gate_w2, gate_bias, pos, q_out,
                 k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, cap: int, hq: int, hkv: int,
                 status=None, in_splits: int = 0, in_bias=None) -> None:

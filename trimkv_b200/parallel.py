@@ -12,6 +12,8 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
+from . import ops
+
 
 def partition_bounds(num_requests: int, world_size: int, rank: int) -> Tuple[int, int]:
     """Contiguous slice ``[lo, hi)`` of the request list owned by ``rank``; sizes differ by at most one."""
@@ -59,3 +61,43 @@ def generate_partitioned(generate_fn: Callable[[torch.Tensor], torch.Tensor], in
     if hi == lo:
         local = input_ids.new_zeros(0, int(width.item()))
     return gather_rows(local, input_ids.shape[0], group)
+
+
+class PeerExchange:
+    """Gathered-output buffers of a head-sharded decode step, visible to every rank of one box.
+
+    Every rank allocates one block holding ``nbuf`` buffers ``[batch, width]`` and an ``int32[world]`` flag array in
+    its own memory, exports it (CUDA IPC) and maps the peers' blocks into its address space with its own device
+    current, which also enables peer access over NVLink.  The attention merge kernel then stores each rank's column
+    block into every rank's buffer and raises a flag (``ops.decode_attn_push``), and ``ops.peer_wait`` holds the
+    consumer's stream until all blocks have arrived: attention and all-gather in one pass, no library collective in
+    the step.  The mapped peer memory is only ever written, never read.
+    """
+
+    def __init__(self, batch: int, width: int, dtype: torch.dtype, device, nbuf: int = 3,
+                 group: Optional[dist.ProcessGroup] = None):
+        import ctypes
+        self.group = group
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.nbuf, self.width = nbuf, width
+        esize = torch.empty((), dtype=dtype).element_size()
+        buf_bytes = -(-batch * width * esize // 256) * 256
+        flag_off = nbuf * buf_bytes
+        self._block = torch.zeros(flag_off + 256, dtype=torch.uint8, device=device)
+        self.buffers = [self._block[i * buf_bytes: i * buf_bytes + batch * width * esize].view(dtype).view(batch, width)
+                        for i in range(nbuf)]
+        self.flags = self._block[flag_off: flag_off + 4 * self.world].view(torch.int32)
+        self.sync = torch.zeros(3, dtype=torch.int32, device=device)   # CTA counter, exchanges sent, received
+        torch.cuda.synchronize(device)
+        everyone = [None] * self.world
+        dist.all_gather_object(everyone, ops.ipc_export(self._block), group=group)
+        bases = []
+        with torch.cuda.device(device):
+            for r, (handle, offset) in enumerate(everyone):
+                bases.append(self._block.data_ptr() if r == self.rank else ops.ipc_import(handle) + offset)
+        self.out_ptrs = [(ctypes.c_void_p * self.world)(*[b + i * buf_bytes for b in bases]) for i in range(nbuf)]
+        self.flag_ptrs = (ctypes.c_void_p * self.world)(*[b + flag_off for b in bases])
+        dist.barrier(group=group)   # nobody pushes before every rank has zeroed and mapped its block
+
+    def buffer(self, i: int) -> torch.Tensor:
+        return self.buffers[i]
