@@ -137,7 +137,8 @@ int tkv_evict(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cach
  * the score (src/trimkv/cache_utils.py:176-180; norm and log rounded to K's dtype as torch does).
  * Used after tkv_group_budget for the budget-sharing strategies.
  */
-enum { TKV_STRATEGY_ALPHA = 0, TKV_STRATEGY_KNORM_ALPHA = 1 };
+enum { TKV_STRATEGY_ALPHA = 0, TKV_STRATEGY_KNORM_ALPHA = 1,
+       TKV_STRATEGY_KNORM_ALPHA_CLAMPED = 2 /* the flat classes' form: log(max(||k||, 1e-12)), :390 */ };
 /* OR-ed into `strategy`: dtype the retention score log beta * (q_idx - pos) is computed in.  TrimKVCache upcasts to
  * fp32 (src/trimkv/cache_utils.py:172); the flat budget-sharing caches multiply in the stored dtype
  * (:386, :441, :755, :882), i.e. the age is rounded to that dtype and so is the product. */
@@ -147,6 +148,7 @@ int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_c
                  int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                  int memory_size, int trigger_len, int max_len,
                  const int32_t* keep_cnt, int protect_last, int kept_stride, int strategy,
+                 const float* scores /* nullable: precomputed by tkv_flat_scores, [nseg*cap] */,
                  int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream);
 
 /*
@@ -182,7 +184,19 @@ int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const in
                      int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
                      int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
                      int score_dtype /* 0 fp32, 1 bf16, 2 f16: as TKV_SCORE_* >> 8 */,
+                     const float* scores /* nullable: precomputed by tkv_flat_scores */,
                      int32_t* keep_cnt, int32_t* status, tkv_stream_t stream);
+
+/*
+ * Scores of every live row, once, into scores_out [nseg*cap] (fp32 holding values of the score dtype), for the
+ * strategies that read the K rows: "knorm_alpha" / "knorm_alpha_threshold" of the flat caches
+ * (src/trimkv/cache_utils.py:388-390, 443-450, 757-759, 876-878: log_alpha + log(max(||k||, 1e-12)), every step
+ * rounded as torch rounds it for tensors of these dtypes).  strategy: TKV_STRATEGY_* | TKV_SCORE_*.
+ * tkv_group_budget and tkv_evict_ex then take the array through their `scores` argument.
+ */
+int tkv_flat_scores(const void* k_cache, const float* beta_cache, const int32_t* pos_cache,
+                    const int32_t* seg_len, int nseg, int64_t cap, int head_dim, int kv_dtype,
+                    int64_t q_idx, int strategy, int max_len, float* scores_out, tkv_stream_t stream);
 
 /*
  * Functional append on the reference's packed layout: out[origin_rows + heads*s_new, row] = for every head its

@@ -402,15 +402,29 @@ class OracleFlatBudgetCache(OracleBatchedFlatCache):
     keeping each segment's own top-c rows for the per-segment counts c, so every variant reduces to counts.
     """
 
-    def __init__(self, batched=True, score_dtype="float32"):
+    def __init__(self, batched=True, score_dtype="float32", key_dtype="float32"):
         super().__init__()
         self.batched = batched
         self.score_dtype = score_dtype
+        self.key_dtype = key_dtype      # dtype the reference's key tensors would have (norm and log are rounded to it)
+        self._knorm = False
 
     def _scores(self, l, seg):
         a, n = int(self.cu_seqlens_k[l][seg]), int(self.head_lens[l][seg])
-        return retention_scores(self.retention_weights[l][a:a + n, 0], self.kv_positions[l][a:a + n, 0],
-                                self._seen_tokens + 1, self.score_dtype)
+        sc = retention_scores(self.retention_weights[l][a:a + n, 0], self.kv_positions[l][a:a + n, 0],
+                              self._seen_tokens + 1, self.score_dtype)
+        if self._knorm:
+            # :388-390, :443-450, :757-759, :876-878: scores = log_alpha + log(key.norm(dim=-1).clamp_min(1e-12)); the
+            # norm (fp32 accumulation), the clamp constant and the log are rounded to the keys' dtype, the sum to the
+            # promoted dtype (16-bit only if both operands are).
+            k = np.asarray(self.key_cache[l][a:a + n], np.float32)
+            nrm = round_to_dtype(np.sqrt(np.sum(k * k, axis=-1, dtype=np.float32)), self.key_dtype)
+            nrm = np.maximum(nrm, round_to_dtype(np.float32(1e-12), self.key_dtype))
+            lg = round_to_dtype(np.log(nrm).astype(np.float32), self.key_dtype)
+            sc = (sc + lg).astype(np.float32)
+            if self.score_dtype != "float32" and self.key_dtype == self.score_dtype:
+                sc = round_to_dtype(sc, self.score_dtype)
+        return sc
 
     def _apply(self, counts):
         """counts[l][seg] rows kept (canonical top-c inside the segment)."""
@@ -426,7 +440,8 @@ class OracleFlatBudgetCache(OracleBatchedFlatCache):
                     if c == 0:
                         k, v, b, p = k[:0], v[:0], b[:0], p[:0]
                     else:
-                        k, v, b, p, _ = compress_rows(k, v, b, p, q_idx, c, score_dtype=self.score_dtype)
+                        keep = canonical_topm(self._scores(l, seg)[None], c)[0]
+                        k, v, b, p = k[keep], v[keep], b[keep], p[keep]
                 ks.append(k); vs.append(v); bs.append(b[:, None]); ps.append(p[:, None]); nl.append(k.shape[0])
             self.key_cache[l] = np.concatenate(ks, 0); self.value_cache[l] = np.concatenate(vs, 0)
             self.retention_weights[l] = np.concatenate(bs, 0); self.kv_positions[l] = np.concatenate(ps, 0)
@@ -442,6 +457,7 @@ class OracleFlatBudgetCache(OracleBatchedFlatCache):
         rows = [self.key_cache[l].shape[0] for l in range(L)]
         total = sum(rows)
         thr = "threshold" in strategy
+        self._knorm = "knorm" in strategy
         # :462, :893 compare with a 0-dim fp32 tensor, which torch casts to the dtype of the scores
         log_thr = round_to_dtype(np.log(np.float32(alpha_threshold)), self.score_dtype) if thr else None
         counts = {}

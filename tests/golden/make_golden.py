@@ -256,6 +256,48 @@ def flat_budget_bf16(cu):
     print("flat_budget_bf16: lens", [out[f"c{ci}_lens"].tolist() for ci in range(len(cases))])
 
 
+def flat_budget_knorm(cu):
+    """"knorm_alpha" strategies of the flat classes (score = log_alpha + log ||k||, in the tensors' dtype), on fp32
+    and on bf16 tensors.  One prefill + one compress per case."""
+    L, B, H, D, S, M, Bf = 2, 2, 3, 8, 128, 32, 8
+    cases = []
+    for dt in ("float32", "bfloat16"):
+        cases += [("batched", "knorm_alpha", 0.0, dt), ("batched", "layer_wise_knorm_alpha", 0.0, dt),
+                  ("single", "knorm_alpha", 0.0, dt), ("single", "layer_wise_knorm_alpha", 0.0, dt),
+                  ("single", "knorm_alpha_threshold", 0.35, dt), ("batched", "knorm_alpha_threshold", 0.35, dt)]
+    out = {}
+    for ci, (kind, strategy, thr, dt) in enumerate(cases):
+        torch.manual_seed(50 + ci)
+        tdt = getattr(torch, dt)
+        bsz = B if kind == "batched" else 1
+        cls = cu.BatchedDynamicBudgetTrimKVCache if kind == "batched" else cu.DynamicBudgetTrimKVCache
+        cache = cls(device="cpu")
+        logb = F.logsigmoid(torch.randn(L, bsz, H, S) * 1.5 + 3.0).to(tdt)
+        keys = (torch.randn(L, bsz, H, S, D) * torch.exp(torch.randn(L, bsz, H, S, 1))).to(tdt)
+        for l in range(L):
+            cache.update(keys[l].contiguous(), (keys[l] * 0.5).contiguous(), logb[l].contiguous(), torch.arange(S), l)
+        q_idx = cache.get_seq_length() + 1
+        cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, floor_budget_ratio=0.0, alpha_threshold=thr,
+                       num_layers=L, num_key_value_heads=H)
+        for l in range(L):
+            la = (q_idx - cache.kv_positions[l].squeeze(-1)) * cache.retention_weights[l].squeeze(-1)
+            sc = la + torch.log(cache.key_cache[l].norm(dim=-1).reshape(-1).clamp_min(1e-12))
+            assert sc.dtype == tdt
+            out[f"c{ci}_scores_l{l}"] = sc.float().numpy()
+            out[f"c{ci}_pos_l{l}"] = cache.kv_positions[l][:, 0].numpy().astype(np.int32)
+        if dt == "bfloat16":   # exact and half the size: the bit patterns
+            out[f"c{ci}_logb"] = logb.view(torch.int16).numpy()
+            out[f"c{ci}_keys"] = keys.view(torch.int16).numpy()
+        else:
+            out[f"c{ci}_logb"] = logb.numpy()
+            out[f"c{ci}_keys"] = keys.numpy()
+        out[f"c{ci}_lens"] = torch.stack([cache.head_lens[l] for l in range(L)]).numpy()
+    out["meta"] = np.asarray([L, B, H, D, S, M, Bf])
+    out["cases"] = np.asarray([f"{k}|{s}|{t}|{d}" for k, s, t, d in cases])
+    np.savez_compressed(os.path.join(HERE, "flat_budget_knorm.npz"), **out)
+    print("flat_budget_knorm: lens", [out[f"c{ci}_lens"].sum() for ci in range(len(cases))])
+
+
 def eager_attention(ea):
     """Dense GQA attention from the reference's eager function (fp32), Q=1 and Q=3."""
     torch.manual_seed(3)
@@ -281,4 +323,5 @@ if __name__ == "__main__":
     knorm_alpha(cu_)
     flat_budget(cu_)
     flat_budget_bf16(cu_)
+    flat_budget_knorm(cu_)
     eager_attention(ea_)

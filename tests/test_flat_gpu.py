@@ -241,3 +241,35 @@ def test_multi_token_query_over_ragged_cache():
         assert out.shape == (B, Q, H * G, D)
         assert np.max(np.abs(out.float().cpu().numpy() - want)) <= 2e-2
         cache.check_status()
+
+
+@pytest.mark.parametrize("ci", range(12))
+def test_flat_budget_knorm_strategies(golden_dir, ci):
+    """"knorm_alpha" / "knorm_alpha_threshold" (+ layer-wise) on both flat classes, fp32 and bf16 tensors, against the
+    reference's result and the CPU restatement."""
+    from test_oracle import check_knorm_case, load_knorm_case
+    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, DynamicBudgetTrimKVCache
+    g = _g(golden_dir, "flat_budget_knorm.npz")
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, thr, dt, logb, keys = load_knorm_case(g, ci)
+    tdt = getattr(torch, dt)
+    cache = (BatchedDynamicBudgetTrimKVCache if kind == "batched" else DynamicBudgetTrimKVCache)(device=DEV)
+    want = orc.OracleFlatBudgetCache(kind == "batched", dt, dt)
+    for l in range(L):
+        want.update(keys[l], keys[l] * 0.5, logb[l], np.arange(S), l)
+        kt = torch.from_numpy(keys[l]).to(tdt).to(DEV)
+        cache.update(kt, (kt.float() * 0.5).to(tdt), torch.from_numpy(logb[l]).to(tdt).to(DEV), torch.arange(S, device=DEV), l)
+    cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=thr, num_layers=L, num_key_value_heads=H)
+    want.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=thr)
+    cache.check_status()
+    lens = torch.stack([cache.head_lens[l] for l in range(L)]).cpu().numpy()
+    packed = [cache.packed(l) for l in range(L)]
+    assert np.array_equal(lens, np.stack([want.head_lens[l] for l in range(L)]))
+    for l in range(L):
+        assert np.array_equal(packed[l][3][:, 0].cpu().numpy(), want.kv_positions[l][:, 0])
+        assert np.array_equal(packed[l][0].float().cpu().numpy(), want.key_cache[l])       # payload moved with its row
+
+    def score_of(l):
+        want._knorm = True
+        return np.concatenate([want._scores(l, s) for s in range(lens.shape[1])])
+    check_knorm_case(g, ci, lens, lambda l: packed[l][3][:, 0].cpu().numpy().astype(np.int32), score_of)

@@ -273,3 +273,49 @@ def test_flat_budget_bf16_fixture_tells_score_dtypes_apart(golden_dir):
             c.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=float(thr))
         differing += any(not np.array_equal(caches[0].kv_positions[l], caches[1].kv_positions[l]) for l in range(L))
     assert differing >= 1
+
+
+def load_knorm_case(g, ci):
+    """Inputs of one case of flat_budget_knorm.npz as fp32 arrays holding the values of the case's dtype."""
+    kind, strategy, thr, dt = str(g["cases"][ci]).split("|")
+    logb, keys = g[f"c{ci}_logb"], g[f"c{ci}_keys"]
+    if dt == "bfloat16":
+        logb, keys = _bf16_bits_to_f32(logb), _bf16_bits_to_f32(keys)
+    return kind, strategy, float(thr), dt, logb.astype(np.float32), keys.astype(np.float32)
+
+
+def check_knorm_case(g, ci, lens, pos_of, score_of):
+    """fp32 cases and threshold cases: exactly the reference's rows.  bf16 top-k cases: the same multiset of kept
+    scores per budget group (equal scores are frequent in bf16 and torch.topk's tie order is unspecified)."""
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, thr, dt = str(g["cases"][ci]).split("|")
+    bsz = B if kind == "batched" else 1
+    ref_lens = g[f"c{ci}_lens"]
+    if dt == "float32" or "threshold" in strategy:
+        assert np.array_equal(lens, ref_lens), ci
+        for l in range(L):
+            assert np.array_equal(pos_of(l), g[f"c{ci}_pos_l{l}"]), (ci, l)
+        return
+    cu_ref = [np.concatenate([[0], np.cumsum(ref_lens[l])]) for l in range(L)]
+    cu_got = [np.concatenate([[0], np.cumsum(lens[l])]) for l in range(L)]
+    for grp in flat_bf16_groups(kind, strategy, L, bsz, H):
+        ref_sc = np.concatenate([g[f"c{ci}_scores_l{l}"][cu_ref[l][s]:cu_ref[l][s + 1]] for l, s in grp])
+        got_sc = np.concatenate([score_of(l)[cu_got[l][s]:cu_got[l][s + 1]] for l, s in grp])
+        assert np.array_equal(np.sort(ref_sc), np.sort(got_sc)), (ci, grp[0])
+
+
+@pytest.mark.parametrize("ci", range(12))
+def test_flat_budget_knorm_strategies_match_reference(golden_dir, ci):
+    g = _load(golden_dir, "flat_budget_knorm.npz")
+    L, B, H, D, S, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, thr, dt, logb, keys = load_knorm_case(g, ci)
+    cache = orc.OracleFlatBudgetCache(kind == "batched", dt, dt)
+    for l in range(L):
+        cache.update(keys[l], keys[l] * 0.5, logb[l], np.arange(S), l)
+    cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, alpha_threshold=thr)
+    lens = np.stack([cache.head_lens[l] for l in range(L)])
+
+    def score_of(l):   # scores of the kept rows, the way the cache computed them (q_idx = S + 1)
+        cache._knorm = True
+        return np.concatenate([cache._scores(l, s) for s in range(lens.shape[1])])
+    check_knorm_case(g, ci, lens, lambda l: cache.kv_positions[l][:, 0].astype(np.int32), score_of)

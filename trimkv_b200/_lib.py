@@ -24,10 +24,11 @@ SIGNATURES = {
     "tkv_evict_select": (I, [P, L, P, L, P, I, I, L, I, I, I, P, P, P, P]),
     "tkv_compact": (I, [P, P, P, P, L, P, P, L, L, L, P, L, P, L, P, L, P, P, P, I, I, I, I, I, I, P, P]),
     "tkv_evict": (I, [P, P, P, P, P, P, I, I, L, I, I, L, I, I, I, P, P, P]),
-    "tkv_evict_ex": (I, [P, P, P, P, P, P, I, I, L, I, I, L, I, I, I, P, I, I, I, P, P, P]),
+    "tkv_evict_ex": (I, [P, P, P, P, P, P, I, I, L, I, I, L, I, I, I, P, I, I, I, P, P, P, P]),
+    "tkv_flat_scores": (I, [P, P, P, P, I, L, I, I, L, I, I, P, P]),
     "tkv_evict_multi_workspace_bytes": (L, [I, I, I]),
     "tkv_evict_multi": (I, [P, P, P, P, P, P, I, I, L, I, I, L, I, I, I, I, I, I, P, L, P, P, P]),
-    "tkv_group_budget": (I, [P, P, P, L, I, I, I, L, L, L, I, F, I, I, I, P, P, P]),
+    "tkv_group_budget": (I, [P, P, P, L, I, I, I, L, L, L, I, F, I, I, I, P, P, P, P]),
     "tkv_flat_append_packed": (I, [P, P, P, P, I, I, L, L, P]),
     "tkv_rebuild_cu_seqlens": (I, [P, P, I, I, P]),
     "tkv_decode_attn_workspace_bytes": (c_size_t, [I, I, I, I, I]),

@@ -508,6 +508,7 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
         super().__init__(max_seq_len=max_seq_len, device=device)
         self._rows: List[int] = []   # per layer: total live rows (host copy, refreshed after every eviction)
         self._beta_dtype = torch.float32  # dtype log beta arrives in: the dtype the reference scores in
+        self._knorm = False               # set by compress() for the "knorm_*" strategies
         self.batch_size: Optional[int] = None
         self.num_kv_heads: Optional[int] = None
 
@@ -595,21 +596,29 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
         sd = {torch.bfloat16: 1, torch.float16: 2}.get(self._beta_dtype, 0)
         if threshold is not None and sd:
             threshold = float(torch.tensor(threshold, dtype=torch.float32).to(self._beta_dtype))
+        scores = None
+        if self._knorm:
+            # log_alpha + log ||k||: written once for all rows, so that the budget kernel's five passes and the
+            # eviction read 4 bytes per row instead of the K rows.
+            scores = torch.empty(nl, nseg * self._cap, dtype=torch.float32, device=s["k"].device)
+            ops.flat_scores(s["k"], s["beta"], s["pos"], s["len"], nl * nseg, self._cap, q_idx, max(self._cache_len),
+                            scores, knorm=True, score_dtype=sd)
         keep = torch.empty(nl, nseg, dtype=torch.int32, device=s["k"].device)
         keep.copy_(s["len"])  # layers that do not fire keep everything
         if n_outer > 1:       # one group per request spans all layers
             ops.group_budget(s["beta"], s["pos"], s["len"], self._cap, groups_per_layer, inner, n_outer, nseg, q_idx,
-                             k_total, keep, threshold, floor_mode, floor_cnt, self._status, sd)
+                             k_total, keep, threshold, floor_mode, floor_cnt, self._status, sd, scores)
         else:
             for l in layers:
                 ops.group_budget(s["beta"][l], s["pos"][l], s["len"][l], self._cap, groups_per_layer, inner, 1, nseg,
-                                 q_idx, k_total, keep[l], threshold, floor_mode, floor_cnt, self._status, sd)
+                                 q_idx, k_total, keep[l], threshold, floor_mode, floor_cnt, self._status, sd,
+                                 None if scores is None else scores[l])
         kept = None
         if self.record_kept:
             kept = torch.full((nl * nseg, self._cap), -1, dtype=torch.int32, device=s["k"].device)
         ops.evict_ex(s["k"], s["v"], s["beta"], s["pos"], s["len"], s["cu"], nseg, nl * nseg, self._cap, q_idx,
                      max(self._cache_len), keep, 0, kept_idx_out=kept, kept_stride=self._cap, status=self._status,
-                     score_dtype=sd)
+                     score_dtype=sd, scores=scores)
         if kept is not None:
             self.last_kept_idx = kept.view(nl, self._batch, self._hkv, self._cap)
         self._after_eviction(buffer_size)
@@ -618,10 +627,10 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
                  floor_budget_ratio: float = 0.0, alpha_threshold: float = 0.0, num_layers: Optional[int] = None,
                  num_key_value_heads: Optional[int] = None, skip_layers: int = 0):
         base = strategy.replace("layer_wise_", "")
-        if base not in ("alpha", "alpha_threshold"):
-            if base in ("knorm_alpha", "knorm_alpha_threshold"):
-                raise NotImplementedError(f"compress strategy {strategy!r} is not built on the CUDA path")
+        if base not in ("alpha", "alpha_threshold", "knorm_alpha", "knorm_alpha_threshold") or \
+                ("layer_wise" in strategy and "threshold" in base):
             raise ValueError(f"Unknown compression strategy: {strategy}")
+        self._knorm = base.startswith("knorm")
         L = len(self) if num_layers is None else num_layers
         if L == 0 or self.batch_size is None:
             return

@@ -154,6 +154,52 @@ __device__ __forceinline__ void move_range(int m, int j0, int ctas, int tail_max
   *per_out = per;
 }
 
+// log ||k||_2 of one K row as torch computes it for a tensor of K's dtype (src/trimkv/cache_utils.py:176-180, 388-390):
+// the norm accumulates in fp32 and is rounded to the dtype, and the log is rounded to it again.
+// Called by a whole warp (lanes stride over the row's 16-byte vectors); every lane returns the value.
+__device__ __forceinline__ float log_row_norm(const char* row, int row_vecs, int kv_dtype, int lane, bool clamp) {
+  float ss = 0.f;
+  for (int c = lane; c < row_vecs; c += 32) {
+    const uint4 v = ld16(row + (int64_t)c * 16);
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (kv_dtype == TKV_F32) { const float a = __uint_as_float(w[j]); ss = fmaf(a, a, ss); }
+      else if (kv_dtype == TKV_BF16) {
+        const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
+        ss = fmaf(a, a, ss); ss = fmaf(b, b, ss);
+      } else {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+        ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
+      }
+    }
+  }
+#pragma unroll
+  for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+  float nrm = sqrtf(ss);
+  if (kv_dtype == TKV_BF16) nrm = __bfloat162float(__float2bfloat16_rn(nrm));
+  else if (kv_dtype == TKV_F16) nrm = __half2float(__float2half_rn(nrm));
+  if (clamp) {  // the flat classes clamp the norm at 1e-12 (a scalar torch rounds to the tensor's dtype); TrimKVCache does not
+    float floor_ = 1e-12f;
+    if (kv_dtype == TKV_BF16) floor_ = __bfloat162float(__float2bfloat16_rn(floor_));
+    else if (kv_dtype == TKV_F16) floor_ = __half2float(__float2half_rn(floor_));
+    nrm = fmaxf(nrm, floor_);
+  }
+  float lg = logf(nrm);
+  if (kv_dtype == TKV_BF16) lg = __bfloat162float(__float2bfloat16_rn(lg));
+  else if (kv_dtype == TKV_F16) lg = __half2float(__float2half_rn(lg));
+  return lg;
+}
+
+// log_alpha + log ||k||: torch adds in fp32 and rounds to the promoted dtype, which is 16-bit only if both the
+// stored log beta (score_dtype) and K are 16-bit.
+__device__ __forceinline__ float knorm_score(float log_alpha, float log_norm, int score_dtype, int kv_dtype) {
+  const float s = __fadd_rn(log_alpha, log_norm);
+  if (score_dtype == 1 && kv_dtype == TKV_BF16) return __bfloat162float(__float2bfloat16_rn(s));
+  if (score_dtype == 2 && kv_dtype == TKV_F16) return __half2float(__float2half_rn(s));
+  return s;
+}
+
 struct EvictParams {
   char* k; char* v; float* beta; int32_t* pos;
   int32_t* seg_len;
@@ -163,6 +209,7 @@ struct EvictParams {
   int protect_last;          // the newest `protect_last` rows always score +inf (sliding window)
   int knorm, kv_dtype;       // knorm: score += log ||k||  (strategy "knorm_alpha")
   int score_dtype;           // dtype the retention score is computed in (retention_score_as)
+  const float* scores;       // precomputed scores [nseg*cap] (tkv_flat_scores), or NULL: computed here
   int32_t* kept_idx_out; int32_t* status;
   // Plan mode (several CTAs per segment move the rows afterwards): the kept list and {rows kept, first row that
   // moves} go to global memory and nothing is moved here.
@@ -187,39 +234,18 @@ __global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) 
     return;
   }
   const int64_t row0 = (int64_t)seg * p.cap;
-  if (p.knorm) {
-    // strategy "knorm_alpha" (src/trimkv/cache_utils.py:176-180): score = log_alpha + log(||k||), the norm and its
-    // log taken in the dtype of K as torch does (fp32 accumulation, one rounding each for 16-bit K).  A warp per
-    // row: lanes stride over the row's 16-byte vectors.
+  if (p.scores != nullptr) {
+    for (int i = threadIdx.x; i < n; i += kThreads)
+      keys[i] = i >= n - p.protect_last ? score_key(INFINITY) : score_key(p.scores[row0 + i]);
+  } else if (p.knorm) {
+    // strategy "knorm_alpha" (src/trimkv/cache_utils.py:176-180): score = log_alpha + log(||k||).  A warp per row.
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const char* kb = p.k + row0 * (int64_t)p.row_vecs * 16;
     for (int i = warp; i < n; i += kThreads / 32) {
-      float ss = 0.f;
-      for (int c = lane; c < p.row_vecs; c += 32) {
-        const uint4 v = ld16(kb + ((int64_t)i * p.row_vecs + c) * 16);
-        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          if (p.kv_dtype == TKV_F32) { const float a = __uint_as_float(w[j]); ss = fmaf(a, a, ss); }
-          else if (p.kv_dtype == TKV_BF16) {
-            const float a = __uint_as_float(w[j] << 16), b = __uint_as_float(w[j] & 0xffff0000u);
-            ss = fmaf(a, a, ss); ss = fmaf(b, b, ss);
-          } else {
-            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-            ss = fmaf(f.x, f.x, ss); ss = fmaf(f.y, f.y, ss);
-          }
-        }
-      }
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float lg = log_row_norm(kb + (int64_t)i * p.row_vecs * 16, p.row_vecs, p.kv_dtype, lane, p.knorm == 2);
       if (lane == 0) {
-        float nrm = sqrtf(ss);
-        if (p.kv_dtype == TKV_BF16) nrm = __bfloat162float(__float2bfloat16_rn(nrm));
-        else if (p.kv_dtype == TKV_F16) nrm = __half2float(__float2half_rn(nrm));
-        float lg = logf(nrm);
-        if (p.kv_dtype == TKV_BF16) lg = __bfloat162float(__float2bfloat16_rn(lg));
-        else if (p.kv_dtype == TKV_F16) lg = __half2float(__float2half_rn(lg));
-        const float sc_ = __fadd_rn(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype), lg);
+        const float sc_ = knorm_score(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype), lg,
+                                      p.score_dtype, p.kv_dtype);
         keys[i] = i >= n - p.protect_last ? score_key(INFINITY) : score_key(sc_);
       }
     }
@@ -569,7 +595,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
                       int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                       int memory_size, int trigger_len, int max_len, const int32_t* keep_cnt, int protect_last,
                       int strategy, int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream,
-                      int ctas = 1, void* workspace = nullptr, int64_t workspace_bytes = 0) {
+                      int ctas = 1, void* workspace = nullptr, int64_t workspace_bytes = 0, const float* scores = nullptr) {
   using namespace tkv;
   const int es = elem_size(kv_dtype);
   if (es == 0) return fail(TKV_ERR_ARG, "tkv_evict: unknown kv_dtype %d", kv_dtype);
@@ -577,7 +603,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
     return fail(TKV_ERR_ARG, "tkv_evict: NULL pointer argument");
   const int score_dtype = (strategy >> 8) & 3;
   strategy &= 0xff;
-  if ((strategy != 0 && strategy != 1) || score_dtype > 2) return fail(TKV_ERR_ARG, "tkv_evict: unknown strategy %d", strategy);
+  if (strategy < 0 || strategy > 2 || score_dtype > 2) return fail(TKV_ERR_ARG, "tkv_evict: unknown strategy %d", strategy);
   if (nseg < 0 || cap <= 0 || head_dim <= 0 || memory_size <= 0 || max_len <= 0 || protect_last < 0)
     return fail(TKV_ERR_ARG, "tkv_evict: bad sizes nseg=%d cap=%lld head_dim=%d M=%d max_len=%d", nseg,
                 (long long)cap, head_dim, memory_size, max_len);
@@ -593,7 +619,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.nseg = nseg; p.cap = cap; p.row_vecs = (int)(row_bytes / 16); p.q_idx = q_idx;
   p.m = memory_size; p.trigger_len = trigger_len; p.max_len = max_len;
   p.keep_cnt = keep_cnt; p.protect_last = protect_last; p.knorm = strategy; p.kv_dtype = kv_dtype;
-  p.score_dtype = score_dtype;
+  p.score_dtype = score_dtype; p.scores = scores;
   p.kept_idx_out = kept_idx_out; p.status = status;
   p.plan = nullptr; p.plan_kept = nullptr; p.plan_stride = 0; p.plan_tail = nullptr; p.ctas = 1; p.tail_max = 0;
   MoveParams mp;
@@ -676,11 +702,11 @@ extern "C" int tkv_evict_ex(void* k_cache, void* v_cache, float* beta_cache, int
                             int nseg, int64_t cap, int head_dim, int kv_dtype, int64_t q_idx,
                             int memory_size, int trigger_len, int max_len,
                             const int32_t* keep_cnt, int protect_last, int kept_stride, int strategy,
-                            int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
+                            const float* scores, int32_t* kept_idx_out, int32_t* status, tkv_stream_t stream) {
   // kept_stride doubles as the row stride of kept_idx_out when keep counts vary per segment.
   return evict_impl(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, head_dim, kv_dtype,
                     q_idx, keep_cnt != nullptr ? (kept_stride > 0 ? kept_stride : 1) : memory_size, trigger_len, max_len,
-                    keep_cnt, protect_last, strategy, kept_idx_out, status, stream);
+                    keep_cnt, protect_last, strategy, kept_idx_out, status, stream, 1, nullptr, 0, scores);
 }
 
 extern "C" int tkv_evict_select(const float* beta, int64_t beta_stride, const int32_t* pos, int64_t pos_stride,
@@ -768,6 +794,7 @@ struct BudgetParams {
   int64_t q_idx; int64_t k_total;
   int use_threshold; float threshold;           // keep score >= threshold instead of the k_total best
   int score_dtype;                              // see retention_score_as
+  const float* scores;                          // precomputed scores [rows] (tkv_flat_scores) or NULL
   int floor_mode, floor_cnt;                    // 0: none, 1: c = min(n, s' + floor) with the reference's boundary
                                                 // attribution for s', 2: c = max(s, min(floor, n))
   int32_t* keep_cnt; int32_t* status;
@@ -819,7 +846,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
           bool valid = i < n;
           uint32_t key = 0;
           if (valid) {
-            key = score_key(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
+            key = score_key(p.scores != nullptr ? p.scores[row0 + i] : retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
             valid = (key & decided) == prefix;
           }
           const int digit = valid ? (int)((key >> shift) & 255u) : 256 + lane;
@@ -851,7 +878,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
       for (int i = tid; i < n_round; i += kBudgetThreads) {
         uint32_t key = 0;
         const bool valid = i < n;
-        if (valid) key = score_key(retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
+        if (valid) key = score_key(p.scores != nullptr ? p.scores[row0 + i] : retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype));
         const unsigned gt = __ballot_sync(0xffffffffu, valid && key > thresh);
         const unsigned eq = __ballot_sync(0xffffffffu, valid && key == thresh);
         if (lane == 0) {
@@ -880,7 +907,7 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
         int first = 0;
         if (n > 0) {
           const int64_t row0 = seg_of(j) * p.cap;
-          const uint32_t key0 = score_key(retention_score_as(p.beta[row0], p.pos[row0], p.q_idx, p.score_dtype));
+          const uint32_t key0 = score_key(p.scores != nullptr ? p.scores[row0] : retention_score_as(p.beta[row0], p.pos[row0], p.q_idx, p.score_dtype));
           first = keep_all || key0 > thresh || (key0 == thresh && quota > 0);
         }
         s_eq[j] = first;
@@ -909,7 +936,8 @@ __global__ void __launch_bounds__(kBudgetThreads) group_budget_kernel(BudgetPara
 extern "C" int tkv_group_budget(const float* beta_cache, const int32_t* pos_cache, const int32_t* seg_len, int64_t cap,
                                 int groups, int inner, int n_outer, int64_t outer_stride, int64_t q_idx,
                                 int64_t k_total, int use_threshold, float threshold, int floor_mode, int floor_cnt,
-                                int score_dtype, int32_t* keep_cnt, int32_t* status, tkv_stream_t stream) {
+                                int score_dtype, const float* scores, int32_t* keep_cnt, int32_t* status,
+                                tkv_stream_t stream) {
   using namespace tkv;
   if (!beta_cache || !pos_cache || !seg_len || !keep_cnt) return fail(TKV_ERR_ARG, "tkv_group_budget: NULL pointer argument");
   if (groups < 0 || inner <= 0 || n_outer <= 0 || cap <= 0 || floor_mode < 0 || floor_mode > 2 || floor_cnt < 0 ||
@@ -923,8 +951,56 @@ extern "C" int tkv_group_budget(const float* beta_cache, const int32_t* pos_cach
   p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len; p.cap = cap;
   p.inner = inner; p.n_outer = n_outer; p.outer_stride = outer_stride; p.q_idx = q_idx; p.k_total = k_total;
   p.use_threshold = use_threshold; p.threshold = threshold; p.floor_mode = floor_mode; p.floor_cnt = floor_cnt;
-  p.score_dtype = score_dtype;
+  p.score_dtype = score_dtype; p.scores = scores;
   p.keep_cnt = keep_cnt; p.status = status;
   group_budget_kernel<<<groups, kBudgetThreads, 0, (cudaStream_t)stream>>>(p);
   return check_launch("tkv_group_budget");
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Scores of every live row, written once: for the strategies whose score reads the K rows ("knorm_alpha" and its
+// threshold form on the flat caches, src/trimkv/cache_utils.py:388-390, 443-450, 757-759, 876-878) the budget
+// kernel would otherwise read K five times.  One warp per row; rows beyond a segment's length are not touched.
+namespace tkv {
+struct ScoreParams {
+  const char* k; const float* beta; const int32_t* pos; const int32_t* seg_len;
+  int64_t cap; int row_vecs, kv_dtype, knorm, score_dtype; int64_t q_idx;
+  float* scores;
+};
+
+__global__ void __launch_bounds__(256) flat_scores_kernel(ScoreParams p) {
+  const int seg = blockIdx.y, lane = threadIdx.x & 31;
+  const int n = min(max(p.seg_len[seg], 0), (int)min((int64_t)INT32_MAX, p.cap));
+  const int64_t row0 = (int64_t)seg * p.cap;
+  for (int i = blockIdx.x * 8 + (threadIdx.x >> 5); i < n; i += gridDim.x * 8) {
+    float sc = retention_score_as(p.beta[row0 + i], p.pos[row0 + i], p.q_idx, p.score_dtype);
+    if (p.knorm) {
+      const float lg = log_row_norm(p.k + (row0 + i) * (int64_t)p.row_vecs * 16, p.row_vecs, p.kv_dtype, lane, p.knorm == 2);
+      sc = knorm_score(sc, lg, p.score_dtype, p.kv_dtype);
+    }
+    if (lane == 0) p.scores[row0 + i] = sc;
+  }
+}
+}  // namespace tkv
+
+extern "C" int tkv_flat_scores(const void* k_cache, const float* beta_cache, const int32_t* pos_cache,
+                               const int32_t* seg_len, int nseg, int64_t cap, int head_dim, int kv_dtype,
+                               int64_t q_idx, int strategy, int max_len, float* scores_out, tkv_stream_t stream) {
+  using namespace tkv;
+  const int es = elem_size(kv_dtype);
+  const int score_dtype = (strategy >> 8) & 3;
+  strategy &= 0xff;
+  if (!k_cache || !beta_cache || !pos_cache || !seg_len || !scores_out) return fail(TKV_ERR_ARG, "tkv_flat_scores: NULL pointer argument");
+  if (es == 0 || strategy < 0 || strategy > 2 || score_dtype > 2 || nseg < 0 || cap <= 0 || head_dim <= 0 || max_len <= 0)
+    return fail(TKV_ERR_ARG, "tkv_flat_scores: bad arguments");
+  if (((int64_t)head_dim * es) % 16 != 0 || !aligned16(k_cache)) return fail(TKV_ERR_ARG, "tkv_flat_scores: K rows must be 16-byte multiples, 16-byte aligned");
+  if (nseg == 0) return TKV_OK;
+  if (nseg > 65535) return fail(TKV_ERR_UNSUPPORTED, "tkv_flat_scores: more than 65535 segments per call");
+  ScoreParams p;
+  p.k = (const char*)k_cache; p.beta = beta_cache; p.pos = pos_cache; p.seg_len = seg_len; p.cap = cap;
+  p.row_vecs = (int)((int64_t)head_dim * es / 16); p.kv_dtype = kv_dtype; p.knorm = strategy; p.score_dtype = score_dtype;
+  p.q_idx = q_idx; p.scores = scores_out;
+  const int per_seg = (int)std::min<int64_t>(64, (max_len + 63) / 64);   // CTAs per segment, 8 rows at a time each
+  flat_scores_kernel<<<dim3((unsigned)per_seg, (unsigned)nseg), 256, 0, (cudaStream_t)stream>>>(p);
+  return check_launch("tkv_flat_scores");
 }

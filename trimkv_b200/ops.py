@@ -260,7 +260,8 @@ def skinny_gemm(x, w, partial, status=None) -> int:
 
 def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
              q_idx: int, max_len: int, keep_cnt, protect_last: int = 0, memory_size: int = 1, trigger_len: int = 0,
-             kept_idx_out=None, kept_stride: int = 0, status=None, knorm: bool = False, score_dtype: int = 0) -> None:
+             kept_idx_out=None, kept_stride: int = 0, status=None, knorm: bool = False, score_dtype: int = 0,
+             scores=None) -> None:
     """In-place eviction with a keep count per segment (``keep_cnt`` int32 ``[nseg]``) and/or a protected tail.
     ``score_dtype``: 0 fp32, 1 bf16, 2 f16 (the dtype the retention score is computed in)."""
     d = k_cache.shape[-1]
@@ -268,7 +269,7 @@ def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group
         k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(),
         seg_len.data_ptr(), _ptr(cu_seqlens), group, nseg, cap, d, dtype_code(k_cache.dtype), q_idx,
         memory_size, trigger_len, max_len, _ptr(keep_cnt), protect_last, kept_stride,
-        (1 if knorm else 0) | (score_dtype << 8), _ptr(kept_idx_out),
+        (1 if knorm else 0) | (score_dtype << 8), _ptr(scores), _ptr(kept_idx_out),
         _ptr(status), _stream(k_cache))
     check(rc, "tkv_evict_ex")
     _count(1 if cu_seqlens is None else 2)
@@ -296,14 +297,26 @@ def evict_multi(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, gr
     _count(n if cu_seqlens is None else n + 1)
 
 
+def flat_scores(k_cache, beta_cache, pos_cache, seg_len, nseg: int, cap: int, q_idx: int, max_len: int, scores_out,
+                knorm: bool = True, score_dtype: int = 0) -> None:
+    """Scores of every live row (fp32 array of ``nseg*cap``) for the strategies that read K ("knorm_alpha" on the
+    flat caches: the norm is clamped at 1e-12 as the reference does there)."""
+    rc = lib().tkv_flat_scores(k_cache.data_ptr(), beta_cache.data_ptr(), pos_cache.data_ptr(), seg_len.data_ptr(),
+                               nseg, cap, k_cache.shape[-1], dtype_code(k_cache.dtype), q_idx,
+                               (2 if knorm else 0) | (score_dtype << 8), max_len, scores_out.data_ptr(),
+                               _stream(k_cache))
+    check(rc, "tkv_flat_scores")
+    _count(1)
+
+
 def group_budget(beta_cache, pos_cache, seg_len, cap: int, groups: int, inner: int, n_outer: int, outer_stride: int,
                  q_idx: int, k_total: int, keep_cnt, threshold=None, floor_mode: int = 0, floor_cnt: int = 0,
-                 status=None, score_dtype: int = 0) -> None:
+                 status=None, score_dtype: int = 0, scores=None) -> None:
     """Per-segment keep counts when ``k_total`` rows (or all rows scoring >= ``threshold``) are kept per group."""
     rc = lib().tkv_group_budget(
         beta_cache.data_ptr(), pos_cache.data_ptr(), seg_len.data_ptr(), cap, groups, inner, n_outer, outer_stride,
         q_idx, k_total, 0 if threshold is None else 1, 0.0 if threshold is None else float(threshold),
-        floor_mode, floor_cnt, score_dtype, keep_cnt.data_ptr(), _ptr(status), _stream(beta_cache))
+        floor_mode, floor_cnt, score_dtype, _ptr(scores), keep_cnt.data_ptr(), _ptr(status), _stream(beta_cache))
     check(rc, "tkv_group_budget")
     _count(1)
 
