@@ -254,6 +254,24 @@ int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
                            int32_t* status, tkv_stream_t stream);
 
 /*
+ * Several query tokens per request against the cache that already holds them (a later prompt, speculative or
+ * multi-token decoding): what flash_attn_varlen_func(causal=True) computes for the reference when Q > 1
+ * (src/trimkv/attn/flash_attn.py:118-145).  Segment s has seg_len[s] cached tokens INCLUDING the q_tokens new ones;
+ * query token i of a request attends to the first seg_len - q_tokens + i + 1 tokens of each of its segments
+ * (bottom-right aligned causal mask).  q: [batch, q_tokens, hq, D] with element strides (q_sb, q_st, q_sh);
+ * out: [batch, q_tokens, hq, D] contiguous.  Same tensor-core kernel as tkv_decode_attn with the query rows
+ * (token, head) on the MMA's N dimension, 16 rows per CTA; each further group of 16 rows re-reads the K/V chunk, so
+ * this entry point is meant for a handful of tokens, not for whole prompts.  Requires bf16/f16, head_dim 128 and
+ * the capacity-strided layout (TKV_ERR_UNSUPPORTED otherwise).
+ */
+size_t tkv_decode_attn_multi_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len, int q_tokens);
+int tkv_decode_attn_multi(const void* q, int64_t q_sb, int64_t q_st, int64_t q_sh,
+                          const void* k_cache, const void* v_cache, const int32_t* seg_len, int64_t cap,
+                          void* out, void* workspace, size_t workspace_bytes,
+                          int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                          float scale, int max_len, int q_tokens, int32_t* status, tkv_stream_t stream);
+
+/*
  * Head-sharded decode (each rank holds hkv of the KV heads and their hq query heads; no counterpart in the
  * single-process reference): tkv_decode_attn whose merge step stores the result straight into the gathered
  * [batch, out_row_stride] buffer of EVERY rank, at element column out_col_offset, and then raises this rank's flag

@@ -343,6 +343,36 @@ def test_decode_attention_ragged_work_list(ops, bsz, hq, hkv, cap):
     assert ops.read_status(status) == 2
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 5e-3)])
+@pytest.mark.parametrize("bsz,hq,hkv,ql,cap", [(2, 16, 8, 3, 700), (1, 8, 4, 8, 300), (2, 16, 4, 7, 1100), (3, 2, 2, 5, 200),
+                                               (1, 16, 8, 20, 600)])
+def test_multi_token_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, ql, cap):
+    """Several query tokens per request against caches that already hold them: bottom-right aligned causal mask per
+    segment, query rows (token, head) on the MMA's N dimension (more than 16 rows: several row groups)."""
+    gen = torch.Generator().manual_seed(29)
+    d, nseg = 128, bsz * hkv
+    lens = [int(x) for x in torch.randint(ql, cap + 1, (nseg,), generator=gen)]
+    lens[0], lens[-1] = ql, cap                      # only the new tokens; a full segment (several chunks)
+    if nseg > 2 and cap >= 256 + ql:
+        lens[1] = 256 + ql - 1                       # the first new token sits exactly at a chunk boundary
+    q = torch.randn(bsz, ql, hq, d, generator=gen).to(dtype).to(DEV)
+    k = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.full((bsz, ql, hq, d), float("nan"), dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    ops.decode_attn_multi(q, k, v, ln, cap, out, hkv, d ** -0.5, max(lens), status=status)
+    assert ops.read_status(status) == 0
+    kf = torch.cat([k[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    vf = torch.cat([v[s, :lens[s]] for s in range(nseg)]).float().cpu().numpy()
+    want = orc.varlen_gqa_attention(q.transpose(1, 2).float().cpu().numpy(), kf, vf, np.concatenate([[0], np.cumsum(lens)]), bsz, hkv)
+    assert np.max(np.abs(out.float().cpu().numpy() - want)) <= tol
+    # one query token through this entry point is the decode kernel's result
+    out1 = torch.empty(bsz, 1, hq, d, dtype=dtype, device=DEV)
+    ops.decode_attn_multi(q[:, -1:], k, v, ln, cap, out1, hkv, d ** -0.5, max(lens), status=status)
+    assert np.max(np.abs(out1[:, 0].float().cpu().numpy() - want[:, -1])) <= tol
+
+
 # ---------------------------------------------------------------- weight-streaming GEMM and its consumers
 @pytest.mark.parametrize("m,n,k", [(32, 4224, 2048), (32, 2048, 2048), (32, 12288, 2048), (32, 2048, 6144),
                                    (5, 300, 128), (1, 128, 64), (17, 1000, 4096)])

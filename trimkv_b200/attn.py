@@ -34,6 +34,11 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
+# Query rows (new tokens x query heads per KV head) up to which multi-token queries go to the decode kernel: it re-reads
+# the K/V chunk once per 16 rows, so beyond a few passes the library attention is the better tool.
+MULTI_TOKEN_MAX_ROWS = 64
+
+
 def _dense_causal(query, key, value, scaling):
     """Causal attention with bottom-right alignment over dense ``[B,Hkv,n,D]`` keys (prompt pass)."""
     ql, n = query.shape[2], key.shape[2]
@@ -81,6 +86,16 @@ def tkv_attention_forward(
     if head_lens is None or ql != 1:
         if key.dim() != 4:
             raise NotImplementedError("multi-token queries over a packed flat cache")
+        hkv = key.shape[1]
+        if (head_lens is not None and ql * (hq // hkv) <= MULTI_TOKEN_MAX_ROWS and dim == 128
+                and query.dtype in (torch.bfloat16, torch.float16) and key.stride(3) == 1 and key.stride(2) == dim
+                and key.stride(0) == hkv * key.stride(1) and key.shape[0] * key.stride(0) // dim >= 128):
+            # A handful of new tokens against the materialised cache (a short follow-up prompt, multi-token decoding):
+            # the decode kernel with the (token, head) query rows on its N dimension.
+            out = torch.empty(bsz, ql, hq, dim, dtype=query.dtype, device=query.device)
+            ops.decode_attn_multi(query.transpose(1, 2), key, value, head_lens, key.stride(1) // dim, out, hkv, scaling,
+                                  key.shape[2], status=flash_attn_kwargs.get("status"))
+            return out, None, None
         if head_lens is not None and not flash_attn_kwargs.get("uniform_lengths", False):
             return _ragged_causal(query, key, value, head_lens, scaling), None, None
         return _dense_causal(query, key, value, scaling), None, None

@@ -190,7 +190,7 @@ decode_attn_split_kernel(AttnParams p) {
 // Called by every thread of a kD-thread block (it synchronises the block).
 template <int kD>
 __device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, int g, int d, int len) {
-  const int G = p.hq / p.hkv;
+  const int G = p.rows;   // query rows per segment (the G query heads, times the query tokens if there are several)
   float r = 0.f;
   const int nact = (len + p.chunk - 1) / p.chunk;
   const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
@@ -252,7 +252,8 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   const int len = min(p.seg_len[seg], p.max_len);
   const int b = seg / p.hkv, h = seg - b * p.hkv;
   const int G = p.hq / p.hkv;
-  char* op = p.out + ((int64_t)b * p.hq + h * G + g) * (int64_t)kD * 2;
+  // g is the query row of the segment: head g, or (several query tokens) token g / G, head g % G
+  char* op = p.out + (((int64_t)b * p.q_tokens + g / G) * p.hq + h * G + g % G) * (int64_t)kD * 2;
   float r = 0.f;
   if (len > 0) {
     if (p.nchunks == 1) return;  // written by the split kernel
@@ -367,8 +368,8 @@ int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_di
   cudaError_t e;
   if (push != nullptr && head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_push_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p, *push);
   else if (push != nullptr && head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_push_kernel<TKV_F16, 128>, dim3(nseg, G), dim3(128), 0, st, p, *push);
-  else if (head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_kernel<TKV_BF16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
-  else if (head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_kernel<TKV_F16, 128>, dim3(nseg, G), dim3(128), 0, st, p);
+  else if (head_dim == 128 && kv_dtype == TKV_BF16) e = launch_pdl(decode_attn_combine_kernel<TKV_BF16, 128>, dim3(nseg, p.rows), dim3(128), 0, st, p);
+  else if (head_dim == 128 && kv_dtype == TKV_F16) e = launch_pdl(decode_attn_combine_kernel<TKV_F16, 128>, dim3(nseg, p.rows), dim3(128), 0, st, p);
   else return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn(combine): head_dim=%d dtype=%d", head_dim, kv_dtype);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(combine): %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_attn(combine)");
@@ -439,7 +440,7 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
                             void* out, void* workspace, size_t workspace_bytes,
                             int batch, int hq, int hkv, int head_dim, int kv_dtype,
                             float scale, int max_len, int64_t total_len_bound, int32_t* status, tkv_stream_t stream,
-                            const tkv::PushParams* push = nullptr) {
+                            const tkv::PushParams* push = nullptr, int q_tokens = 1, int64_t q_st = 0) {
   using namespace tkv;
   if (!q || !k_cache || !v_cache || !seg_len || !out) return fail(TKV_ERR_ARG, "%s: NULL pointer argument", who);
   if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || head_dim <= 0 || max_len <= 0)
@@ -451,7 +452,8 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
   if ((q_sb * 2) % 16 || (q_sh * 2) % 16) return fail(TKV_ERR_ARG, "%s: q strides must be multiples of 16 bytes", who);
   if (batch == 0) return TKV_OK;
   const bool ragged = total_len_bound >= 0;
-  const size_t base = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  const size_t base = q_tokens > 1 ? tkv_decode_attn_multi_workspace_bytes(batch, hq, hkv, head_dim, max_len, q_tokens)
+                                   : tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
   const size_t need = ragged ? tkv_decode_attn_ragged_workspace_bytes(batch, hq, hkv, head_dim, max_len, total_len_bound) : base;
   if (workspace == nullptr || workspace_bytes < need || (reinterpret_cast<uintptr_t>(workspace) & 255u))
     return fail(TKV_ERR_ARG, "%s: workspace of %zu bytes (256-byte aligned) required, got %zu", who, need, workspace_bytes);
@@ -462,10 +464,13 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
   p.seg_len = seg_len; p.seg_start = seg_start; p.cap = cap;
   p.out = (char*)out;
   const bool tc = use_tensor_core_path(head_dim, kv_dtype, G, seg_start, (int64_t)nseg * cap);
+  if (q_tokens > 1 && !tc)
+    return fail(TKV_ERR_UNSUPPORTED, "%s: several query tokens need bf16/f16, head_dim 128 and the capacity-strided layout", who);
   p.chunk = tc ? attn_tc_chunk_tokens() : attn_chunk_tokens(nseg, max_len);
   p.nchunks = (max_len + p.chunk - 1) / p.chunk;
+  p.q_tokens = q_tokens; p.rows = q_tokens * G; p.q_st = q_st;
   p.part_ml = reinterpret_cast<float*>(workspace);
-  p.part_o = p.part_ml + (((int64_t)nseg * p.nchunks * G * 2 + 63) / 64) * 64;
+  p.part_o = p.part_ml + (((int64_t)nseg * p.nchunks * p.rows * 2 + 63) / 64) * 64;
   p.hq = hq; p.hkv = hkv; p.max_len = max_len;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
@@ -509,6 +514,27 @@ extern "C" int tkv_decode_attn_ragged(const void* q, int64_t q_sb, int64_t q_sh,
   return decode_attn_impl("tkv_decode_attn_ragged", q, q_sb, q_sh, k_cache, v_cache, seg_len, seg_start, cap, out,
                           workspace, workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, total_len_bound,
                           status, stream);
+}
+
+extern "C" size_t tkv_decode_attn_multi_workspace_bytes(int batch, int hq, int hkv, int head_dim, int max_len, int q_tokens) {
+  if (batch <= 0 || hq <= 0 || hkv <= 0 || head_dim <= 0 || max_len <= 0 || hq % hkv != 0 || q_tokens <= 0) return 0;
+  if (q_tokens == 1) return tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  const int64_t items = (int64_t)batch * hkv * ((max_len + tkv::attn_tc_chunk_tokens() - 1) / tkv::attn_tc_chunk_tokens());
+  return (size_t)(items * q_tokens * (hq / hkv) * (head_dim + 2) * sizeof(float) + 256);
+}
+
+extern "C" int tkv_decode_attn_multi(const void* q, int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                     const void* k_cache, const void* v_cache, const int32_t* seg_len, int64_t cap,
+                                     void* out, void* workspace, size_t workspace_bytes,
+                                     int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                                     float scale, int max_len, int q_tokens, int32_t* status, tkv_stream_t stream) {
+  if (q_tokens < 1 || (q_st * 2) % 16 != 0)
+    return tkv::fail(TKV_ERR_ARG, "tkv_decode_attn_multi: q_tokens=%d, token stride %lld", q_tokens, (long long)q_st);
+  if (hq > 0 && hkv > 0 && (int64_t)q_tokens * (hq / hkv) > 16 * 65535)
+    return tkv::fail(TKV_ERR_UNSUPPORTED, "tkv_decode_attn_multi: too many query rows per segment");
+  return decode_attn_impl("tkv_decode_attn_multi", q, q_sb, q_sh, k_cache, v_cache, seg_len, nullptr, cap, out, workspace,
+                          workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, -1, status, stream, nullptr,
+                          q_tokens, q_st);
 }
 
 extern "C" int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
@@ -618,5 +644,6 @@ extern "C" int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
   p.scale_log2 = scale * 1.4426950408889634f;
   p.status = status;
   p.work = nullptr; p.work_count = nullptr; p.work_capacity = 0;
+  p.q_tokens = 1; p.rows = G; p.q_st = 0;
   return launch_decode_attn_simt(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream);
 }

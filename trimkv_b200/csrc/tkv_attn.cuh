@@ -19,6 +19,11 @@ struct AttnParams {
   // Optional compact work list (ragged lengths): item i = {segment << 8 | chunk, clamped length of the segment};
   // *work_count items are valid.  NULL: the grid covers every (segment, chunk) pair and absent chunks exit.
   const int2* work; const int32_t* work_count; int work_capacity;
+  // Several query tokens per request (q_tokens > 1; tensor-core path only): a segment then has rows = q_tokens * G
+  // query rows, row R = token i * G + head g, and token i sees the first len - q_tokens + i + 1 cached tokens
+  // (bottom-right aligned causal mask).  q is [batch, q_tokens, hq, D] with token stride q_st (elements), out
+  // [batch, q_tokens, hq, D] contiguous, partials are [nseg, nchunks, rows, ...].  rows == G for plain decode.
+  int q_tokens, rows; int64_t q_st;
 };
 
 // Head-sharded decode: the merge kernel stores this rank's heads straight into every rank's gathered buffer (plain

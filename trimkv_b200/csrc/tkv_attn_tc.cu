@@ -38,7 +38,10 @@ struct TcSmem {                               // after the 1024-byte aligned sta
 };
 constexpr int kTcSmemBytes = 3 * kStageBytes + kQBytes + 2 * kPBytes + (int)sizeof(TcSmem) + 1024;
 
-template <int kDtype, int kG>
+// kG = query rows this CTA handles (<= 16).  kMulti = false: one query token, the rows are the G query heads of the
+// KV head.  kMulti = true: several query tokens; blockIdx.y selects a group of 16 of the segment's q_tokens * G
+// rows, row R = token * G + head, each with its own causal limit.
+template <int kDtype, int kG, bool kMulti>
 __global__ void __launch_bounds__(kTcThreads)
 decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
@@ -58,7 +61,14 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
     if (chunk == 0) {  // empty segment: its query heads get zeros
       const int b0 = seg / p.hkv, h0 = seg - b0 * p.hkv;
       for (int g = 0; g < kG; ++g) {
-        char* op = p.out + ((int64_t)b0 * p.hq + h0 * kG + g) * 256;
+        char* op;
+        if (kMulti) {
+          const int R = blockIdx.y * 16 + g, Gq = p.hq / p.hkv;
+          if (R >= p.rows) break;
+          op = p.out + (((int64_t)b0 * p.q_tokens + R / Gq) * p.hq + h0 * Gq + R % Gq) * 256;
+        } else {
+          op = p.out + ((int64_t)b0 * p.hq + h0 * kG + g) * 256;
+        }
         if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[threadIdx.x] = __float2bfloat16_rn(0.f);
         else reinterpret_cast<__half*>(op)[threadIdx.x] = __float2half_rn(0.f);
       }
@@ -105,7 +115,11 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   for (int i = tid; i < 256; i += kTcThreads) {
     const int hh = i >> 4, c = i & 15;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (hh < kG) v = ld16(p.q + ((int64_t)b * p.q_sb + (int64_t)(h * kG + hh) * p.q_sh) * 2 + c * 16);
+    if (kMulti) {
+      const int R = blockIdx.y * 16 + hh, Gq = p.hq / p.hkv;
+      if (hh < kG && R < p.rows)
+        v = ld16(p.q + ((int64_t)b * p.q_sb + (int64_t)(R / Gq) * p.q_st + (int64_t)(h * Gq + R % Gq) * p.q_sh) * 2 + c * 16);
+    } else if (hh < kG) v = ld16(p.q + ((int64_t)b * p.q_sb + (int64_t)(h * kG + hh) * p.q_sh) * 2 + c * 16);
     st16(q_s + (hh >> 3) * 2048 + c * 128 + (hh & 7) * 16, v);
   }
   fence_async_smem();
@@ -163,7 +177,14 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
       const bool valid = i < ntiles && (i * kTileTokens + tid) < n_valid;
 #pragma unroll
       for (int g = 0; g < kG; ++g) {
-        s[i][g] = valid ? v[g] * p.scale_log2 : -INFINITY;
+        bool seen = valid;
+        if (kMulti) {
+          // token of this thread = t0 + i*128 + tid; query row R (token R / G of the new ones) sees the first
+          // len - q_tokens + R / G + 1 cached tokens
+          const int R = blockIdx.y * 16 + g, Gq = p.hq / p.hkv;
+          seen = valid && R < p.rows && (t0 + i * kTileTokens + tid) < len - p.q_tokens + R / Gq + 1;
+        }
+        s[i][g] = seen ? v[g] * p.scale_log2 : -INFINITY;
         mloc[g] = fmaxf(mloc[g], s[i][g]);
       }
     }
@@ -252,14 +273,21 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
     for (int g = 0; g < kG; ++g) {
       const float ls = sm->red_sum[0][g] + sm->red_sum[1][g] + sm->red_sum[2][g] + sm->red_sum[3][g];
+      int R = g, rows = kG;
+      char* op = p.out + ((int64_t)b * p.hq + h * kG + g) * 256;
+      if (kMulti) {
+        const int Gq = p.hq / p.hkv;
+        R = blockIdx.y * 16 + g; rows = p.rows;
+        if (R >= rows) break;
+        op = p.out + (((int64_t)b * p.q_tokens + R / Gq) * p.hq + h * Gq + R % Gq) * 256;
+      }
       if (p.nchunks == 1) {
         const float r = ls > 0.f ? o[g] / ls : 0.f;
-        char* op = p.out + ((int64_t)b * p.hq + h * kG + g) * 256;
         if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[tid] = __float2bfloat16_rn(r);
         else reinterpret_cast<__half*>(op)[tid] = __float2half_rn(r);
       } else {
-        p.part_o[(item * kG + g) * 128 + tid] = o[g];
-        if (tid == 0) { p.part_ml[(item * kG + g) * 2] = mx[g]; p.part_ml[(item * kG + g) * 2 + 1] = ls; }
+        p.part_o[(item * rows + R) * 128 + tid] = o[g];
+        if (tid == 0) { p.part_ml[(item * rows + R) * 2] = mx[g]; p.part_ml[(item * rows + R) * 2 + 1] = ls; }
       }
     }
   }
@@ -309,17 +337,18 @@ int make_map_2d(CUtensorMap* map, const void* base, int64_t cols, int64_t rows, 
 
 int attn_tc_chunk_tokens() { return kTcChunk; }
 
-template <int kDtype, int kG>
+template <int kDtype, int kG, bool kMulti = false>
 static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int nseg, cudaStream_t st) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_attn_tc_kernel<kDtype, kG>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(decode_attn_tc_kernel<kDtype, kG, kMulti>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          kTcSmemBytes);
     if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
     configured = true;
   }
   const int64_t grid = p.work != nullptr ? (int64_t)p.work_capacity : (int64_t)nseg * p.nchunks;
-  cudaError_t e = launch_pdl(decode_attn_tc_kernel<kDtype, kG>, dim3((unsigned)grid), dim3(kTcThreads),
+  const unsigned groups = kMulti ? (unsigned)((p.rows + 15) / 16) : 1u;   // 16 query rows per CTA
+  cudaError_t e = launch_pdl(decode_attn_tc_kernel<kDtype, kG, kMulti>, dim3((unsigned)grid, groups), dim3(kTcThreads),
                              (size_t)kTcSmemBytes, st, mk, mv, p);
   if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_decode_attn(tc): %s", cudaGetErrorString(e));
   return check_launch("tkv_decode_attn(tc)");
@@ -327,6 +356,12 @@ static int launch_tc(const CUtensorMap& mk, const CUtensorMap& mv, const AttnPar
 
 template <int kDtype>
 static int launch_tc_g(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int nseg, int G, cudaStream_t st) {
+  if (p.q_tokens > 1) {   // several query tokens: rows = q_tokens * G, 16 per CTA
+    if (p.rows <= 2) return launch_tc<kDtype, 2, true>(mk, mv, p, nseg, st);
+    if (p.rows <= 4) return launch_tc<kDtype, 4, true>(mk, mv, p, nseg, st);
+    if (p.rows <= 8) return launch_tc<kDtype, 8, true>(mk, mv, p, nseg, st);
+    return launch_tc<kDtype, 16, true>(mk, mv, p, nseg, st);
+  }
   switch (G) {
     case 1: return launch_tc<kDtype, 1>(mk, mv, p, nseg, st);
     case 2: return launch_tc<kDtype, 2>(mk, mv, p, nseg, st);

@@ -218,7 +218,7 @@ struct EvictParams {
 };
 
 template <int kThreads>
-__global__ void __launch_bounds__(kThreads) evict_inplace_kernel(EvictParams p) {
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) evict_inplace_kernel(EvictParams p) {
   extern __shared__ __align__(16) uint32_t keys[];
   __shared__ SelectScratch sc;
   const int seg = blockIdx.x;

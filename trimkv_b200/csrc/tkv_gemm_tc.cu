@@ -100,7 +100,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   if (steps > 0 && !mbar_wait_or_abort(&sm->done, 0, abort_flag) && *abort_flag == 0) {
     *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT);
   }
-  __syncthreads();                                   // one verdict for the whole CTA
+  __syncthreads();                                   // one decision for the whole CTA
   const bool have = steps > 0 && *abort_flag == 0;
   tc_fence_after();
   const int n = n_tile * 128 + tid;

@@ -158,6 +158,24 @@ def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspac
     _count(2)
 
 
+def decode_attn_multi(q, k_cache, v_cache, seg_len, cap: int, out, hkv: int, scale: float, max_len: int,
+                      workspace=None, status=None):
+    """q ``[B,Q,Hq,D]`` (any batch/token/head strides) against caches that already hold the Q new tokens; out
+    ``[B,Q,Hq,D]`` contiguous; bottom-right aligned causal mask per segment."""
+    b, ql, hq, d = q.shape
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    if workspace is None:
+        workspace = torch.empty(lib().tkv_decode_attn_multi_workspace_bytes(b, hq, hkv, d, max_len, ql), dtype=torch.uint8,
+                                device=q.device)
+    rc = lib().tkv_decode_attn_multi(
+        q.data_ptr(), q.stride(0), q.stride(1), q.stride(2), k_cache.data_ptr(), v_cache.data_ptr(), seg_len.data_ptr(), cap,
+        out.data_ptr(), workspace.data_ptr(), workspace.numel(), b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale),
+        max_len, ql, _ptr(status), _stream(q))
+    check(rc, "tkv_decode_attn_multi")
+    _count(2)
+
+
 def decode_attn_push(q, k_cache, v_cache, seg_len, cap: int, out, workspace, hkv: int, scale: float, max_len: int,
                      peer_out, peer_flags, world: int, rank: int, row_stride: int, col_offset: int, sync_state,
                      status=None) -> None:
