@@ -171,6 +171,7 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
   using T = T16<kDtype>;
   __shared__ float red[8];
   grid_dependency_wait();
+  grid_launch_dependents();  // a following weight-streaming GEMM may start fetching weights; it waits before reading `out`
   const int64_t off = (int64_t)blockIdx.x * cols * 2;
   const int nvec = cols / 8;  // 16-byte vectors per row
   float ss = 0.f;
@@ -227,6 +228,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const char* gu, char* out
   const int nvec = inter / 8;
   const int64_t total = (int64_t)rows * nvec;
   grid_dependency_wait();
+  grid_launch_dependents();  // as in add_rmsnorm_kernel
   for (int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x; i < total; i += (int64_t)gridDim.x * 256) {
     const int64_t r = i / nvec, c = i - r * nvec;
     auto f = [](float gg, float uu) {

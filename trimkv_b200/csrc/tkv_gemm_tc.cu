@@ -62,13 +62,26 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  grid_dependency_wait();  // x is produced by the preceding kernel of the stream (weights are not)
+  // The weights do not depend on the preceding kernel of the stream, the activations do: the first ring of weight
+  // tiles is requested before the dependency wait, so that under programmatic dependent launch the pipeline fills
+  // while the predecessor is still running.
+  const int pre = min(steps, kGemmStages);
+  if (tid == 0) {
+    for (int i = 0; i < pre; ++i) {
+      mbar_expect_tx(&sm->full[i], kGemmStageBytes);
+      tma_load_2d(base + i * kGemmStageBytes, &map_w, &sm->full[i], (ks0 + i) * kGemmBK, n_tile * 128);
+    }
+  }
+  grid_dependency_wait();  // x is produced by the preceding kernel of the stream
+  grid_launch_dependents();  // the consumer of the partial sums may be scheduled; it waits for this grid before reading
 
   if (tid == 0) {
     // ---- producer: keeps up to kGemmStages tiles of W and x in flight
-    for (int i = 0; i < steps; ++i) {
+    for (int i = 0; i < pre; ++i)
+      tma_load_2d(base + i * kGemmStageBytes + kGemmWBytes, &map_x, &sm->full[i], (ks0 + i) * kGemmBK, 0);
+    for (int i = pre; i < steps; ++i) {
       const int s = i % kGemmStages;
-      if (i >= kGemmStages && !mbar_wait_or_abort(&sm->empty[s], ((i / kGemmStages) - 1) & 1, abort_flag)) {
+      if (!mbar_wait_or_abort(&sm->empty[s], ((i / kGemmStages) - 1) & 1, abort_flag)) {
         if (*abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
         break;
       }
