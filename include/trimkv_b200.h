@@ -295,8 +295,9 @@ int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
                          void* const* peer_out, int32_t* const* peer_flags, int world, int rank,
                          int64_t out_row_stride, int64_t out_col_offset, int32_t* sync_state,
                          int32_t* status, tkv_stream_t stream);
-int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank, int32_t* status,
-                  tkv_stream_t stream);
+int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank,
+                  int max_polls /* polls of about 0.2 us each before giving up; <= 0: 2^24, about four seconds */,
+                  int32_t* status, tkv_stream_t stream);
 /* Lets kernels of the current device store to memory of peer_device (cudaDeviceEnablePeerAccess; a no-op if it is
  * already enabled or peer_device is the current device).  Needed once per peer before tkv_decode_attn_push. */
 int tkv_enable_peer_access(int peer_device);

@@ -480,3 +480,20 @@ def test_decode_attention_vs_flash_attn_varlen(ops):
         pytest.skip(f"flash_attn cannot run here: {type(e).__name__}: {e}")
     want = ref.view(bsz, hkv, g, d).reshape(bsz, hq, d)
     assert float((out.float() - want.float()).abs().max()) <= 2e-2
+
+
+def test_peer_wait_gives_up_when_no_peer_answers(ops):
+    """The receiving side of the head-sharded exchange never waits without a bound: with flags nobody raises, the wait
+    kernel runs out of polls, reports TKV_DEV_TIMEOUT through the status word and the stream stays usable."""
+    flags = torch.zeros(4, dtype=torch.int32, device=DEV)
+    sync = torch.zeros(3, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    ops.peer_wait(flags, sync, 4, 1, status, max_polls=2000)          # about a millisecond
+    assert ops.read_status(status) == 4
+    assert sync.tolist() == [0, 0, 1]                                  # the exchange is counted all the same
+    # flags already at the expected count: returns at once with a clean status
+    flags.fill_(2)
+    ops.peer_wait(flags, sync, 4, 1, status, max_polls=2000)
+    assert ops.read_status(status) == 0 and sync.tolist() == [0, 0, 2]
+    x = torch.arange(8, device=DEV).sum().item()                       # the context is fine
+    assert x == 28

@@ -36,7 +36,7 @@ SIGNATURES = {
     "tkv_decode_attn_ragged_workspace_bytes": (c_size_t, [I, I, I, I, I, L]),
     "tkv_decode_attn_ragged": (I, [P, L, L, P, P, P, P, L, P, P, c_size_t, I, I, I, I, I, F, I, L, P, P]),
     "tkv_decode_attn_push": (I, [P, L, L, P, P, P, P, L, P, P, c_size_t, I, I, I, I, I, F, I, P, P, I, I, L, L, P, P, P]),
-    "tkv_peer_wait": (I, [P, P, I, I, P, P]),
+    "tkv_peer_wait": (I, [P, P, I, I, I, P, P]),
     "tkv_enable_peer_access": (I, [I]),
     "tkv_ipc_export": (I, [P, P, P]),
     "tkv_ipc_import": (I, [P, P]),

@@ -315,14 +315,14 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_push_kernel(AttnParams
 // receiving side).  One warp, lane r watches rank r; bounded: after about four seconds the lane gives up, the
 // status word says TKV_DEV_TIMEOUT and the stream carries on, so a missing peer cannot hang the GPU.
 __global__ void __launch_bounds__(32) peer_wait_kernel(const int32_t* flags, int32_t* sync, int world, int rank,
-                                                       int32_t* status) {
+                                                       int max_polls, int32_t* status) {
   const int lane = threadIdx.x;
   const int expected = sync[2] + 1;
   __syncwarp();
   if (lane < world && lane != rank) {
     int spins = 0;
     while (ld_acquire_sys(flags + lane) - expected < 0) {
-      if (++spins > (1 << 24)) { report(status, TKV_DEV_TIMEOUT); break; }
+      if (++spins > max_polls) { report(status, TKV_DEV_TIMEOUT); break; }
       __nanosleep(200);
     }
   }
@@ -564,13 +564,13 @@ extern "C" int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
                           workspace_bytes, batch, hq, hkv, head_dim, kv_dtype, scale, max_len, -1, status, stream, &pp);
 }
 
-extern "C" int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank, int32_t* status,
-                             tkv_stream_t stream) {
+extern "C" int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank, int max_polls,
+                             int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   if (!flags || !sync_state) return fail(TKV_ERR_ARG, "tkv_peer_wait: NULL pointer argument");
   if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world)
     return fail(TKV_ERR_ARG, "tkv_peer_wait: world=%d rank=%d", world, rank);
-  peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, sync_state, world, rank, status);
+  peer_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(flags, sync_state, world, rank, max_polls > 0 ? max_polls : (1 << 24), status);
   return check_launch("tkv_peer_wait");
 }
 

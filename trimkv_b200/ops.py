@@ -219,9 +219,10 @@ def ipc_import(handle: bytes) -> int:
     return _ipc_bases[key]
 
 
-def peer_wait(flags, sync_state, world: int, rank: int, status=None) -> None:
-    """Holds the stream until every peer has raised its flag for this rank's next exchange (bounded)."""
-    rc = lib().tkv_peer_wait(flags.data_ptr(), sync_state.data_ptr(), world, rank, _ptr(status), _stream(flags))
+def peer_wait(flags, sync_state, world: int, rank: int, status=None, max_polls: int = 0) -> None:
+    """Holds the stream until every peer has raised its flag for this rank's next exchange.  Bounded: after
+    ``max_polls`` polls (default about four seconds) the status word reports a timeout and the stream carries on."""
+    rc = lib().tkv_peer_wait(flags.data_ptr(), sync_state.data_ptr(), world, rank, max_polls, _ptr(status), _stream(flags))
     check(rc, "tkv_peer_wait")
     _count(1)
 
