@@ -195,11 +195,16 @@ __device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, in
   const int nact = (len + p.chunk - 1) / p.chunk;
   const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
   if (nact <= kD) {
-    // One round trip for all (max, sum) pairs: thread c takes chunk c, the block reduces, the weights go to
-    // shared memory; then every thread sums its output dimension over the chunks with independent loads.
+    // One round trip for everything: the first kEarly partial outputs of this thread's dimension are requested
+    // before anything else, then thread c takes chunk c's (max, sum) pair, the block reduces them and the weights
+    // go to shared memory; by then the outputs have arrived and only need the weighted sum.
+    constexpr int kEarly = 32;
     __shared__ float s_w[kD];
     __shared__ float s_red[2][kD / 32];
     const int lane = d & 31, warp = d >> 5;
+    float early[kEarly];
+#pragma unroll
+    for (int c = 0; c < kEarly; ++c) early[c] = c < nact ? p.part_o[(it0 + (int64_t)c * G) * kD + d] : 0.f;
     float mc = -INFINITY, lc = 0.f;
     if (d < nact) {
       const float2 ml = *reinterpret_cast<const float2*>(&p.part_ml[(it0 + (int64_t)d * G) * 2]);
@@ -214,7 +219,7 @@ __device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, in
 #pragma unroll
     for (int w = 1; w < kD / 32; ++w) mx = fmaxf(mx, s_red[0][w]);
     const float wgt = (mc == -INFINITY) ? 0.f : exp2f(mc - mx);
-    if (d < nact) s_w[d] = wgt;
+    s_w[d] = d < nact ? wgt : 0.f;
     float ls = lc * wgt;
 #pragma unroll
     for (int o = 16; o >= 1; o >>= 1) ls += __shfl_xor_sync(0xffffffffu, ls, o);
@@ -224,8 +229,10 @@ __device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, in
 #pragma unroll
     for (int w = 0; w < kD / 32; ++w) ls += s_red[1][w];
     float o = 0.f;
+#pragma unroll
+    for (int c = 0; c < kEarly; ++c) o = fmaf(early[c], s_w[c], o);   // same order of additions as a plain loop
 #pragma unroll 8
-    for (int c = 0; c < nact; ++c) o = fmaf(p.part_o[(it0 + (int64_t)c * G) * kD + d], s_w[c], o);
+    for (int c = kEarly; c < nact; ++c) o = fmaf(p.part_o[(it0 + (int64_t)c * G) * kD + d], s_w[c], o);
     r = ls > 0.f ? o / ls : 0.f;
   } else {
     float mx = -INFINITY;
