@@ -534,9 +534,11 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
         kw = super()._attn_kwargs(l)
         if kw:
             kw = dict(kw, batch_size=self._batch, num_kv_heads=self._hkv, uniform_lengths=False)
-            if l < len(self._rows):
+            if l < len(self._rows) and not self.static_views:
                 # Head lengths differ under a shared budget; their sum is known here without a device read, which
-                # lets the attention size its grid by tokens instead of by the longest head.
+                # lets the attention size its grid by tokens instead of by the longest head.  (Not for views of the
+                # whole capacity: a captured step is replayed with growing lengths, which a captured total would
+                # under-state.)
                 kw["total_len_bound"] = self._rows[l]
         return kw
 
