@@ -110,6 +110,27 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   const int col = (is_q ? head : p.hq + kvh) * 128 + lane * 4;
   float x[4];
   gemm_out4<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + col, col, x);
+  // A KV-head warp requests everything else it will need right away (the segment's length, its V row, its share of
+  // the gate's hidden layer and second-layer weights), so that the memory round trips overlap instead of adding up.
+  constexpr int kGatePre = 4;                              // hidden values per lane held in registers (gate_inter <= 128)
+  const int seg = b * p.hkv + kvh;
+  const int gcol = (p.hq + 2 * p.hkv) * 128;
+  int len = 0;
+  float vv[4] = {0.f, 0.f, 0.f, 0.f}, gate_h[kGatePre], gate_w[kGatePre];
+  if (!is_q) {
+    len = p.seg_len[seg];
+    const int vcol = (p.hq + p.hkv + kvh) * 128 + lane * 4;
+    gemm_out4<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + vcol, vcol, vv);
+#pragma unroll
+    for (int j = 0; j < kGatePre; ++j) {
+      const int i = lane + 32 * j;
+      gate_h[j] = 0.f; gate_w[j] = 0.f;
+      if (i < p.gate_inter) {
+        gate_h[j] = gemm_out<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + gcol + i, gcol + i);
+        gate_w[j] = T::ld(p.gate_w2, (int64_t)kvh * p.gate_inter + i);
+      }
+    }
+  }
   // RMSNorm over the head: fp32 statistics, normalised value rounded, then multiplied by the weight.
   const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
   const float rstd = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
@@ -131,13 +152,17 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
     return;
   }
   // KV head: append K (normalised + rotated), V (as is), log beta and the position.
-  const int seg = b * p.hkv + kvh;
-  const int len = p.seg_len[seg];
   __syncwarp();
   // Retention gate tail: log beta = logsigmoid(linear2(SiLU(hidden)) + bias), rounded after every op.
-  const int gcol = (p.hq + 2 * p.hkv) * 128;
   float acc = 0.f;
-  for (int i = lane; i < p.gate_inter; i += 32) {
+#pragma unroll
+  for (int j = 0; j < kGatePre; ++j) {
+    if (lane + 32 * j < p.gate_inter) {
+      const float act = T::round(gate_h[j] / (1.0f + expf(-gate_h[j])));
+      acc = fmaf(act, gate_w[j], acc);
+    }
+  }
+  for (int i = lane + 32 * kGatePre; i < p.gate_inter; i += 32) {
     const float g = gemm_out<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + gcol + i, gcol + i);
     const float act = T::round(g / (1.0f + expf(-g)));
     acc = fmaf(act, T::ld(p.gate_w2, (int64_t)kvh * p.gate_inter + i), acc);
@@ -151,9 +176,6 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
   }
   const int64_t dst = (int64_t)seg * p.cap + len;
   *reinterpret_cast<uint2*>(p.k_cache + dst * 256 + lane * 8) = packed;
-  float vv[4];
-  const int vcol = (p.hq + p.hkv + kvh) * 128 + lane * 4;
-  gemm_out4<T>(p.qkvg, p.in_splits, p.split_stride, p.in_bias, row + vcol, vcol, vv);
   *reinterpret_cast<uint2*>(p.v_cache + dst * 256 + lane * 8) = make_uint2(T::pack(vv[0], vv[1]), T::pack(vv[2], vv[3]));
   if (lane == 0) {
     p.beta_cache[dst] = log_beta;
