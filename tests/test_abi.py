@@ -61,6 +61,31 @@ def test_argument_errors_are_reported_without_a_gpu(built):
     assert rc == -1
     assert lib.tkv_decode_attn_workspace_bytes(0, 16, 8, 128, 100) == 0
     assert lib.tkv_decode_attn_workspace_bytes(2, 16, 8, 128, 4224) > 0
+    # entry points added around the core path: same contract
+    dummy = ctypes.create_string_buffer(4096)
+    ptr = ctypes.cast(dummy, ctypes.c_void_p)
+    rc = lib.tkv_evict_multi(ptr, ptr, ptr, ptr, ptr, None, 1, 1, 4224, 128, 0, 1, 4096, 4224, 4224, 0, 0, 64, ptr, 1 << 20,
+                             None, None, None)
+    assert rc == -2 and b"ctas_per_segment" in lib.tkv_last_error()          # more CTAs per segment than supported
+    rc = lib.tkv_evict_multi(ptr, ptr, ptr, ptr, ptr, None, 1, 1, 4224, 128, 0, 1, 4096, 4224, 4224, 0, 0, 4, None, 0,
+                             None, None, None)
+    assert rc == -1 and b"workspace" in lib.tkv_last_error()
+    assert lib.tkv_evict_multi_workspace_bytes(8, 4096, 16) == (2 * 8 * 16 + 2 * 8 + 8 * 4096) * 4
+    # the ragged entry point's workspace holds the dense workspace plus one 8-byte item per possible chunk
+    dense = lib.tkv_decode_attn_workspace_bytes(64, 32, 8, 128, 8192)
+    ragged = lib.tkv_decode_attn_ragged_workspace_bytes(64, 32, 8, 128, 8192, 1_000_000)
+    assert ragged >= dense + (1_000_000 // 256 + 512) * 8
+    assert lib.tkv_decode_attn_multi_workspace_bytes(2, 16, 8, 128, 700, 1) == lib.tkv_decode_attn_workspace_bytes(2, 16, 8, 128, 700)
+    assert lib.tkv_decode_attn_multi_workspace_bytes(2, 16, 8, 128, 700, 5) > lib.tkv_decode_attn_multi_workspace_bytes(2, 16, 8, 128, 700, 2)
+    rc = lib.tkv_decode_attn_push(ptr, 0, 0, ptr, ptr, ptr, None, 4224, ptr, ptr, 1 << 20, 1, 2, 1, 128, 0, 0.1, 4224,
+                                  None, None, 2, 0, 512, 0, None, None, None)
+    assert rc == -1 and b"NULL" in lib.tkv_last_error()
+    rc = lib.tkv_peer_wait(ptr, ptr, 9, 0, 0, None, None)
+    assert rc == -1 and b"world" in lib.tkv_last_error()
+    rc = lib.tkv_flat_scores(ptr, ptr, ptr, ptr, 4, 100, 128, 7, 1, 0, 100, ptr, None)
+    assert rc == -1                                                            # unknown K/V dtype
+    rc = lib.tkv_group_budget(ptr, ptr, ptr, 100, 1, 4000, 1, 0, 1, 10, 0, 0.0, 0, 0, 0, None, ptr, None, None)
+    assert rc == -2 and b"segments per group" in lib.tkv_last_error()
 
 
 def test_cpu_tensors_are_refused():
