@@ -265,14 +265,25 @@ class TrimKVQwen3ForCausalLM(nn.Module):
         return out
 
     @torch.inference_mode()
-    def generate(self, input_ids, max_new_tokens=16, past_key_values=None, eos_token_id=None, **_unused):
-        """Greedy decoding; returns ``[B, prompt + new]`` token ids like HF ``generate``."""
+    def generate(self, input_ids, max_new_tokens=16, past_key_values=None, eos_token_id=None,
+                 prefill_chunk_size=None, **_unused):
+        """Greedy decoding; returns ``[B, prompt + new]`` token ids like HF ``generate``.
+
+        ``prefill_chunk_size``: feed the prompt in pieces of that many tokens, evicting after each piece (the model
+        calls ``compress`` at the end of every forward), so that a prompt much longer than ``memory_size`` never has
+        its whole K/V resident.  The eviction schedule, and with it the result, differs from the one-piece prompt pass
+        exactly as it would in the reference if it were fed the same pieces."""
         if past_key_values is None:
             hints = dict(memory_size=self.config.memory_size, buffer_size=self.config.buffer_size,
                          num_layers=self.config.num_hidden_layers) \
                 if (self.config.compress_memory and self.config.compress_strategy == "alpha") else {}
             past_key_values = TrimKVCache(max_seq_len=self.config.max_seq_len, device=input_ids.device, **hints)
-        out = self(input_ids=input_ids, past_key_values=past_key_values, logits_to_keep=1)
+        if prefill_chunk_size:
+            for lo in range(0, input_ids.shape[1], prefill_chunk_size):
+                out = self(input_ids=input_ids[:, lo:lo + prefill_chunk_size], past_key_values=past_key_values,
+                           logits_to_keep=1)
+        else:
+            out = self(input_ids=input_ids, past_key_values=past_key_values, logits_to_keep=1)
         tokens = [input_ids]
         nxt = out.logits[:, -1].argmax(-1, keepdim=True)
         done = torch.zeros_like(nxt, dtype=torch.bool)
