@@ -345,10 +345,11 @@ def test_decode_attention_ragged_work_list(ops, bsz, hq, hkv, cap):
 
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 5e-3)])
 @pytest.mark.parametrize("bsz,hq,hkv,ql,cap", [(2, 16, 8, 3, 700), (1, 8, 4, 8, 300), (2, 16, 4, 7, 1100), (3, 2, 2, 5, 200),
-                                               (1, 16, 8, 20, 600)])
+                                               (1, 16, 8, 20, 600), (1, 8, 2, 48, 900), (2, 4, 4, 70, 400), (1, 16, 8, 32, 130)])
 def test_multi_token_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, ql, cap):
     """Several query tokens per request against caches that already hold them: bottom-right aligned causal mask per
-    segment, query rows (token, head) on the MMA's N dimension (more than 16 rows: several row groups)."""
+    segment, query rows (token, head) on the MMA's N dimension: up to 16 rows on the decode kernel, more on the
+    kernel with 64 rows per CTA (several row groups beyond that)."""
     gen = torch.Generator().manual_seed(29)
     d, nseg = 128, bsz * hkv
     lens = [int(x) for x in torch.randint(ql, cap + 1, (nseg,), generator=gen)]

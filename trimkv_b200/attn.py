@@ -34,9 +34,15 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-# Query rows (new tokens x query heads per KV head) up to which multi-token queries go to the decode kernel: it re-reads
-# the K/V chunk once per 16 rows, so beyond a few passes the library attention is the better tool.
-MULTI_TOKEN_MAX_ROWS = 64
+# Query rows per segment (new tokens x query heads per KV head) up to which multi-token queries go to the hand-written
+# kernels, from timings on B200 (batch 32, 16/8 heads, about 4100 cached tokens per head, ms per layer):
+#   rows  16: decode kernel 0.26 | library causal attention 0.35 | library attention with a length mask 0.47
+#   rows  64: 64-rows-per-CTA kernel 0.81 | 0.36 | 0.77
+#   rows 256: 3.2 | 0.63 | 2.3
+# so caches whose segments share one length leave the kernel beyond 16 rows (the causal library path needs no mask),
+# and caches with differing head lengths beyond 64 rows.
+MULTI_TOKEN_MAX_ROWS_UNIFORM = 16
+MULTI_TOKEN_MAX_ROWS_RAGGED = 64
 
 
 def _dense_causal(query, key, value, scaling):
@@ -87,11 +93,13 @@ def tkv_attention_forward(
         if key.dim() != 4:
             raise NotImplementedError("multi-token queries over a packed flat cache")
         hkv = key.shape[1]
-        if (head_lens is not None and ql * (hq // hkv) <= MULTI_TOKEN_MAX_ROWS and dim == 128
+        uniform = head_lens is not None and flash_attn_kwargs.get("uniform_lengths", False)
+        limit = MULTI_TOKEN_MAX_ROWS_UNIFORM if uniform else MULTI_TOKEN_MAX_ROWS_RAGGED
+        if (head_lens is not None and ql * (hq // hkv) <= limit and dim == 128
                 and query.dtype in (torch.bfloat16, torch.float16) and key.stride(3) == 1 and key.stride(2) == dim
                 and key.stride(0) == hkv * key.stride(1) and key.shape[0] * key.stride(0) // dim >= 128):
-            # A handful of new tokens against the materialised cache (a short follow-up prompt, multi-token decoding):
-            # the decode kernel with the (token, head) query rows on its N dimension.
+            # New tokens against the materialised cache (a piece of a chunked prefill, a follow-up prompt, multi-token
+            # decoding): the tensor-core kernels with the (token, head) query rows on the N dimension.
             out = torch.empty(bsz, ql, hq, dim, dtype=query.dtype, device=query.device)
             ops.decode_attn_multi(query.transpose(1, 2), key, value, head_lens, key.stride(1) // dim, out, hkv, scaling,
                                   key.shape[2], status=flash_attn_kwargs.get("status"))

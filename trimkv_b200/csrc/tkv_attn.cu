@@ -495,7 +495,8 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
       if (rc != TKV_OK) return rc;
     }
   }
-  int rc = launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
+  int rc = (q_tokens > 1 && p.rows > 16) ? launch_multi_attn_tc(p, nseg, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream)
+                                         : launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
   if (rc != TKV_OK) return rc;
   return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream, push);
 }
