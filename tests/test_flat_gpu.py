@@ -209,12 +209,12 @@ def test_flat_budget_bf16_scores(golden_dir, ci):
     check_flat_bf16_case(g, ci, lens, lambda l: packed[l][3][:, 0].cpu().numpy().astype(np.int32), score_of)
 
 
-@pytest.mark.parametrize("Q", [5, 24, 40])
+@pytest.mark.parametrize("Q", [5, 24, 150])
 def test_multi_token_query_over_ragged_cache(Q):
     """A second prompt (Q > 1) appended to a budget-sharing cache whose heads differ in length: bottom-right aligned
     causal attention per segment, against the per-segment restatement.  Q = 5 (10 query rows per segment) runs on
-    the decode kernel, Q = 24 (48 rows) on the 64-rows-per-CTA kernel for the ragged cache and through the library's
-    causal attention for the uniform one, Q = 40 through the library attention (with a mask built from the lengths
+    the decode kernel, Q = 24 (48 rows) on the 32-rows-per-CTA kernel for the ragged cache and through the library's
+    causal attention for the uniform one, Q = 150 through the library attention (with a mask built from the lengths
     where they differ)."""
     from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, TrimKVCache
     from trimkv_b200.attn import TRIMKV_ATTENTION_IMPLEMENTATIONS

@@ -45,7 +45,7 @@ int attn_chunk_tokens(int nseg, int max_len);
 // Tensor-core (tcgen05 + TMA) split kernel: fixed chunk, needs the capacity-strided layout and head_dim 128.
 int attn_tc_chunk_tokens();
 int launch_decode_attn_tc(const AttnParams& p, int nseg, int G, int kv_dtype, int64_t rows, cudaStream_t st);
-// Several query tokens with more than 16 query rows per segment: 64 rows per CTA (tkv_attn_multi.cu).
+// Several query tokens with more than 16 query rows per segment: 32 rows per CTA (tkv_attn_multi.cu).
 int launch_multi_attn_tc(const AttnParams& p, int nseg, int kv_dtype, int64_t rows, cudaStream_t st);
 // Builds the compact work list of the tensor-core split kernel from the lengths (one small kernel).
 int launch_attn_worklist(const AttnParams& p, int nseg, cudaStream_t st);

@@ -1,16 +1,18 @@
-// Several query tokens per request on the tensor cores, 64 query rows per CTA.
+// Several query tokens per request on the tensor cores, 32 query rows per CTA.
 //
 // Same arithmetic as the multi-token form of decode_attn_tc_kernel (tkv_attn_tc.cu), which keeps 16 query rows per CTA
 // and therefore reads a K/V chunk once per 16 rows.  For the pieces of a chunked prefill (tens of tokens times G
 // query heads per KV head; the reference hands them to flash_attn_varlen_func with causal=True,
-// src/trimkv/attn/flash_attn.py:118-145) this kernel puts 64 rows (token, head) on the MMA's N dimension, so a chunk
-// of 256 cached tokens is read once per 64 rows:
-//   S[128 tokens x 64] = K_tile . Q^T        8 x tcgen05.mma (M=128, N=64, K=16) per tile, D in TMEM columns [0,128)
+// src/trimkv/attn/flash_attn.py:118-145) this kernel puts 32 rows (token, head) on the MMA's N dimension, so a chunk
+// of 256 cached tokens is read once per 32 rows:
+//   S[128 tokens x 32] = K_tile . Q^T        8 x tcgen05.mma (M=128, N=32, K=16) per tile, D in TMEM columns [0,64)
 //   softmax per column over the chunk        one thread per token row; column maxima / sums by warp shuffles
-//   O^T[128 dims x 64] += V_tile^T . P       TMEM columns [128,192)
+//   O^T[128 dims x 32] += V_tile^T . P       TMEM columns [64,96)
+// P (the B operand of the second product) is written over the second K tile, which the tensor core has consumed by
+// then, so that two CTAs fit on an SM (107 KB of shared memory each) and overlap each other's phases.
 // Row R of a segment = token R / G of the new ones, head R % G; it sees the first len - q_tokens + R / G + 1 cached
 // tokens (bottom-right aligned causal mask).  Partials go to the same [segment, chunk, row] workspace that
-// decode_attn_combine_kernel merges.  One CTA per SM (147 KB of shared memory); every wait is bounded.
+// decode_attn_combine_kernel merges.  Every wait is bounded.
 #include <cuda.h>
 #include "tkv_common.cuh"
 #include "tkv_attn.cuh"
@@ -21,12 +23,13 @@ namespace tkv {
 constexpr int kMtThreads = 128;
 constexpr int kMtTile = 128;                  // tokens per tile
 constexpr int kMtChunk = 256;                 // tokens per CTA (must equal the decode kernel's chunk: shared workspace)
-constexpr int kMtRows = 64;                   // query rows per CTA
+constexpr int kMtRows = 32;                   // query rows per CTA
 constexpr int kMtStageBytes = 32768;
 constexpr int kMtHalfBytes = 16384;
-constexpr int kMtQBytes = kMtRows * 256;      // 64 rows x 128 dims
-constexpr int kMtPBytes = kMtRows * 256;      // 64 rows x 128 tokens, per tile
-constexpr int kMtTmemCols = 256;              // S tile 0: [0,64)  S tile 1: [64,128)  O: [128,192)
+constexpr int kMtQBytes = kMtRows * 256;      // rows x 128 dims
+constexpr int kMtPBytes = kMtRows * 256;      // rows x 128 tokens, per tile
+constexpr int kMtTmemCols = 128;              // S tile 0: [0,32)  S tile 1: [32,64)  O: [64,96)
+static_assert(2 * kMtPBytes <= kMtStageBytes, "both P tiles live in the second K tile's buffer");
 
 struct MtSmem {
   uint64_t bar_k[2], bar_v[2], bar_s, bar_o;
@@ -36,7 +39,7 @@ struct MtSmem {
   float red_max[4][kMtRows];
   float red_sum[4][kMtRows];
 };
-constexpr int kMtSmemBytes = 3 * kMtStageBytes + kMtQBytes + 2 * kMtPBytes + (int)sizeof(MtSmem) + 1024;
+constexpr int kMtSmemBytes = 3 * kMtStageBytes + kMtQBytes + (int)sizeof(MtSmem) + 1024;
 
 template <int kDtype>
 __global__ void __launch_bounds__(kMtThreads)
@@ -70,8 +73,8 @@ multi_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   uint8_t* stage = base;
   uint8_t* q_s = base + 3 * kMtStageBytes;
-  uint8_t* p_s = q_s + kMtQBytes;
-  MtSmem* sm = reinterpret_cast<MtSmem*>(p_s + 2 * kMtPBytes);
+  uint8_t* p_s = stage + kMtStageBytes;        // over K tile 1, written only after the S MMAs have completed
+  MtSmem* sm = reinterpret_cast<MtSmem*>(q_s + kMtQBytes);
   const int64_t row0 = (int64_t)seg * p.cap + t0;
 
   if (tid == 0) {
@@ -301,7 +304,7 @@ static int launch_multi(const CUtensorMap& mk, const CUtensorMap& mv, const Attn
   return check_launch("tkv_decode_attn_multi");
 }
 
-// 64 query rows per CTA; `rows` = rows addressable behind k/v (bounds of the tensor maps).
+// kMtRows query rows per CTA; `rows` = rows addressable behind k/v (bounds of the tensor maps).
 int launch_multi_attn_tc(const AttnParams& p, int nseg, int kv_dtype, int64_t rows, cudaStream_t st) {
   static_assert(kMtChunk == 256, "the partial workspace is laid out for 256-token chunks");
   CUtensorMap mk, mv;
