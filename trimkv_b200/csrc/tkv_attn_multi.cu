@@ -154,64 +154,52 @@ multi_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
   __syncthreads();
   const bool aborted = *abort_flag != 0;
 
-  // ---- pass 1: column maxima over the chunk (this thread = token `tid` of each tile)
-  for (int cg = 0; cg < kMtRows / 16; ++cg) {
-    float mloc[16];
+  // ---- softmax over the chunk, this thread = token `tid` of each tile.  Shared memory allows two CTAs per SM, so a
+  // thread may use up to 256 registers: the masked scores of both tiles stay in registers between the maximum and
+  // the exponentials (one TMEM read each).
+  float s[2][kMtRows];
 #pragma unroll
-    for (int g = 0; g < 16; ++g) mloc[g] = -INFINITY;
-    if (!aborted) {
-      for (int i = 0; i < ntiles; ++i) {
-        float v[16];
-        tmem_ld16(tmem + lane_base + kMtRows * i + 16 * cg, v);
-        const int tok = t0 + i * kMtTile + tid;
+  for (int i = 0; i < 2; ++i) {
+    const int tok = t0 + i * kMtTile + tid;
 #pragma unroll
-        for (int g = 0; g < 16; ++g)
-          if (tok < sm->vis[cg * 16 + g]) mloc[g] = fmaxf(mloc[g], v[g] * p.scale_log2);
+    for (int cg = 0; cg < kMtRows / 16; ++cg) {
+      float v[16];
+      if (!aborted && i < ntiles) tmem_ld16(tmem + lane_base + kMtRows * i + 16 * cg, v);
+#pragma unroll
+      for (int g = 0; g < 16; ++g) {
+        const int c = cg * 16 + g;
+        s[i][c] = (!aborted && i < ntiles && tok < sm->vis[c]) ? v[g] * p.scale_log2 : -INFINITY;
       }
-    }
-#pragma unroll
-    for (int g = 0; g < 16; ++g) {
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) mloc[g] = fmaxf(mloc[g], __shfl_xor_sync(0xffffffffu, mloc[g], o));
-      if (lane == 0) sm->red_max[warp][cg * 16 + g] = mloc[g];
     }
   }
+#pragma unroll
+  for (int c = 0; c < kMtRows; ++c) {
+    float m = fmaxf(s[0][c], s[1][c]);
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if (lane == 0) sm->red_max[warp][c] = m;
+  }
   __syncthreads();
-  // ---- pass 2: P = exp2(s - max) rounded to the K/V dtype into shared memory (B operand of the second product),
-  // column sums of the rounded weights
-  for (int cg = 0; cg < kMtRows / 16; ++cg) {
-    float mx[16], lsum[16];
+  // P = exp2(s - max) rounded to the K/V dtype into shared memory (B operand of the second product); the column sums
+  // use the rounded weights so that numerator and denominator see the same values.
 #pragma unroll
-    for (int g = 0; g < 16; ++g) {
-      const int c = cg * 16 + g;
-      mx[g] = fmaxf(fmaxf(sm->red_max[0][c], sm->red_max[1][c]), fmaxf(sm->red_max[2][c], sm->red_max[3][c]));
-      lsum[g] = 0.f;
-    }
-    if (!aborted) {
-      for (int i = 0; i < ntiles; ++i) {
-        float v[16];
-        tmem_ld16(tmem + lane_base + kMtRows * i + 16 * cg, v);
-        const int tok = t0 + i * kMtTile + tid;
-        uint8_t* pt = p_s + i * kMtPBytes + (tid >> 3) * 128 + (tid & 7) * 2;
+  for (int c = 0; c < kMtRows; ++c) {
+    const float mx = fmaxf(fmaxf(sm->red_max[0][c], sm->red_max[1][c]), fmaxf(sm->red_max[2][c], sm->red_max[3][c]));
+    float lsum = 0.f;
 #pragma unroll
-        for (int g = 0; g < 16; ++g) {
-          const int c = cg * 16 + g;
-          const float pw = tok < sm->vis[c] ? exp2f(v[g] * p.scale_log2 - mx[g]) : 0.f;
-          unsigned short bits;
-          float back;
-          if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
-          else { __half x = __float2half_rn(pw); bits = __half_as_ushort(x); back = __half2float(x); }
-          lsum[g] += back;
-          *reinterpret_cast<unsigned short*>(pt + (c >> 3) * 2048 + (c & 7) * 16) = bits;
-        }
-      }
+    for (int i = 0; i < 2; ++i) {
+      const float pw = s[i][c] == -INFINITY ? 0.f : exp2f(s[i][c] - mx);
+      unsigned short bits;
+      float back;
+      if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
+      else { __half x = __float2half_rn(pw); bits = __half_as_ushort(x); back = __half2float(x); }
+      lsum += back;
+      if (i < ntiles)
+        *reinterpret_cast<unsigned short*>(p_s + i * kMtPBytes + (tid >> 3) * 128 + (tid & 7) * 2 + (c >> 3) * 2048 + (c & 7) * 16) = bits;
     }
 #pragma unroll
-    for (int g = 0; g < 16; ++g) {
-#pragma unroll
-      for (int o = 16; o >= 1; o >>= 1) lsum[g] += __shfl_xor_sync(0xffffffffu, lsum[g], o);
-      if (lane == 0) sm->red_sum[warp][cg * 16 + g] = lsum[g];
-    }
+    for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
+    if (lane == 0) sm->red_sum[warp][c] = lsum;
   }
   // Rows of a V tile beyond the segment's length may hold anything: their weight is zero, but 0 x NaN would poison
   // the product, so they are cleared in shared memory.

@@ -167,8 +167,16 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
   const bool aborted = *abort_flag != 0;
 
   float s[2][kG], mloc[kG];
+  int vis[kG];   // several query tokens: cached tokens each query row may see (bottom-right aligned causal mask)
 #pragma unroll
-  for (int g = 0; g < kG; ++g) mloc[g] = -INFINITY;
+  for (int g = 0; g < kG; ++g) {
+    mloc[g] = -INFINITY;
+    vis[g] = 0;
+    if (kMulti) {
+      const int R = blockIdx.y * 16 + g, Gq = p.hq / p.hkv;
+      vis[g] = R < p.rows ? len - p.q_tokens + R / Gq + 1 : 0;
+    }
+  }
   if (!aborted) {
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
@@ -178,12 +186,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
 #pragma unroll
       for (int g = 0; g < kG; ++g) {
         bool seen = valid;
-        if (kMulti) {
-          // token of this thread = t0 + i*128 + tid; query row R (token R / G of the new ones) sees the first
-          // len - q_tokens + R / G + 1 cached tokens
-          const int R = blockIdx.y * 16 + g, Gq = p.hq / p.hkv;
-          seen = valid && R < p.rows && (t0 + i * kTileTokens + tid) < len - p.q_tokens + R / Gq + 1;
-        }
+        if (kMulti) seen = valid && (t0 + i * kTileTokens + tid) < vis[g];   // this thread's token = t0 + i*128 + tid
         s[i][g] = seen ? v[g] * p.scale_log2 : -INFINITY;
         mloc[g] = fmaxf(mloc[g], s[i][g]);
       }
