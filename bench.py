@@ -190,6 +190,9 @@ def run_micro(args):
     evict : nseg segments, live lengths uniform in [M, M+B], keep top-M on every segment (forced), bf16, D=128.
     attn  : one layer of decode attention, batch x 8 KV heads, lengths lognormal(median 2048, sigma 1) in [64, 8192].
     append: one token per segment.
+    steady: append every step, evict only the segments that reached M+B.
+    multi : --q-tokens new tokens per request against M cached ones (a piece of a chunked prefill, multi-token
+            decoding): the multi-token kernels beside the library attention, causal and with a length mask.
     Each timed launch works on data that was not touched by the previous one (buffers rotate; each is > L2).
     """
     from trimkv_b200 import ops
@@ -202,6 +205,36 @@ def run_micro(args):
     times = []
     ws = ops.evict_multi_workspace(nseg, M, args.ctas, dev) if args.ctas > 1 else None
     res["ctas_per_segment"] = args.ctas
+    if args.micro == "multi":
+        from trimkv_b200.attn import _dense_causal, _ragged_causal
+        batch, hq, hkv, Q = nseg // 8, 16, 8, args.q_tokens
+        n, cap = M + Q, M + 256
+        k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        lens = torch.full((nseg,), n, device=dev, dtype=torch.int32)
+        q = torch.randn(batch, Q, hq, D, generator=g, device=dev, dtype=torch.bfloat16)
+        out = torch.empty_like(q)
+        wsm = torch.empty(ops._lib.lib().tkv_decode_attn_multi_workspace_bytes(batch, hq, hkv, D, n, Q), dtype=torch.uint8, device=dev)
+        k4, v4, qh = k.view(batch, hkv, cap, D)[:, :, :n], v.view(batch, hkv, cap, D)[:, :, :n], q.transpose(1, 2)
+
+        def avg_ms(fn):
+            for _ in range(args.warmup):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / args.steps
+        ours = avg_ms(lambda: ops.decode_attn_multi(q, k, v, lens, cap, out, hkv, D ** -0.5, n, workspace=wsm))
+        res.update({"config": {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16", "q_tokens": Q,
+                               "query_rows_per_segment": Q * hq // hkv, "cached_tokens": n},
+                    "kv_bytes": nseg * n * 4 * D, "avg_ms": ours,
+                    "library_causal_ms": avg_ms(lambda: _dense_causal(qh, k4, v4, D ** -0.5)),
+                    "library_masked_ms": avg_ms(lambda: _ragged_causal(qh, k4, v4, lens, D ** -0.5)),
+                    "max_abs_diff_vs_library": float((_dense_causal(qh, k4, v4, D ** -0.5).float() - out.float()).abs().max())})
+        print(json.dumps(res))
+        return
     if args.micro == "steady":
         # Triggered steady state: every step appends one token to every segment, then evicts only the segments that
         # reached M+B (lengths start uniform in [M, M+B), so about 1/B of them fire per step).  Amortised per step.
@@ -373,11 +406,12 @@ def run_micro(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady"],
+    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--nseg", type=int, default=2048)
+    ap.add_argument("--q-tokens", type=int, default=16, help="multi microbenchmark: new tokens per request")
     ap.add_argument("--token-bound", action="store_true",
                     help="attention microbenchmark: size the grid by the total token count (ragged lengths)")
     ap.add_argument("--ctas", type=int, default=1, help="CTAs sharing one segment in the eviction microbenchmarks")
