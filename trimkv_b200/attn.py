@@ -37,9 +37,9 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 # Query rows per segment (new tokens x query heads per KV head) up to which multi-token queries go to the hand-written
 # kernels, from timings on B200 (batch 32, 16/8 heads, about 4100 cached tokens per head, ms per layer):
 #   rows  16: decode kernel 0.19        | library causal attention 0.35 | library attention with a length mask 0.47
-#   rows  64: 32-rows-per-CTA kernel 0.56 | 0.36 | 0.77
-#   rows 256: 2.1 | 0.64 | 2.3          rows 512: 4.5 | 0.50 | 3.8
-# (the kernel reads the K/V chunk once per 32 rows, about 0.28 ms a pass).  Caches whose segments share one length
+#   rows  32: 32-rows-per-CTA kernel 0.24 | 0.36 | 0.55
+#   rows  64: 0.46 | 0.36 | 0.77        rows 256: 1.8 | 0.64 | 2.3
+# (the kernel reads the K/V chunk once per 32 rows, about 0.23 ms a pass).  Caches whose segments share one length
 # leave the kernels beyond one pass (the causal library path needs no mask), caches with differing head lengths
 # beyond 256 rows.
 MULTI_TOKEN_MAX_ROWS_UNIFORM = 32

@@ -41,6 +41,24 @@ struct MtSmem {
 };
 constexpr int kMtSmemBytes = 3 * kMtStageBytes + kMtQBytes + (int)sizeof(MtSmem) + 1024;
 
+// Column-wise reduction over the 32 lanes of a warp of 32 values per lane: returns, on lane l, the reduction of
+// column l.  Each step halves the columns a lane still carries (it keeps the half selected by one bit of its lane
+// index and hands the other half to its partner), so 16+8+4+2+1 = 31 shuffles do the work of 32 x 5.
+template <typename Op>
+__device__ __forceinline__ float warp_reduce_columns(float (&v)[32], int lane, Op op) {
+#pragma unroll
+  for (int w = 16; w >= 1; w >>= 1) {
+    const bool upper = (lane & w) != 0;
+#pragma unroll
+    for (int j = 0; j < w; ++j) {
+      const float send = upper ? v[j] : v[j + w];
+      const float keep = upper ? v[j + w] : v[j];
+      v[j] = op(keep, __shfl_xor_sync(0xffffffffu, send, w));
+    }
+  }
+  return v[0];
+}
+
 template <int kDtype>
 __global__ void __launch_bounds__(kMtThreads)
 multi_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p) {
@@ -172,34 +190,35 @@ multi_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_con
       }
     }
   }
+  static_assert(kMtRows == 32, "warp_reduce_columns leaves column l on lane l");
+  {
+    float m[kMtRows];
 #pragma unroll
-  for (int c = 0; c < kMtRows; ++c) {
-    float m = fmaxf(s[0][c], s[1][c]);
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if (lane == 0) sm->red_max[warp][c] = m;
+    for (int c = 0; c < kMtRows; ++c) m[c] = fmaxf(s[0][c], s[1][c]);
+    sm->red_max[warp][lane] = warp_reduce_columns(m, lane, [](float a, float b) { return fmaxf(a, b); });
   }
   __syncthreads();
   // P = exp2(s - max) rounded to the K/V dtype into shared memory (B operand of the second product); the column sums
   // use the rounded weights so that numerator and denominator see the same values.
+  {
+    float l[kMtRows];
 #pragma unroll
-  for (int c = 0; c < kMtRows; ++c) {
-    const float mx = fmaxf(fmaxf(sm->red_max[0][c], sm->red_max[1][c]), fmaxf(sm->red_max[2][c], sm->red_max[3][c]));
-    float lsum = 0.f;
+    for (int c = 0; c < kMtRows; ++c) {
+      const float mx = fmaxf(fmaxf(sm->red_max[0][c], sm->red_max[1][c]), fmaxf(sm->red_max[2][c], sm->red_max[3][c]));
+      l[c] = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float pw = s[i][c] == -INFINITY ? 0.f : exp2f(s[i][c] - mx);
-      unsigned short bits;
-      float back;
-      if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
-      else { __half x = __float2half_rn(pw); bits = __half_as_ushort(x); back = __half2float(x); }
-      lsum += back;
-      if (i < ntiles)
-        *reinterpret_cast<unsigned short*>(p_s + i * kMtPBytes + (tid >> 3) * 128 + (tid & 7) * 2 + (c >> 3) * 2048 + (c & 7) * 16) = bits;
+      for (int i = 0; i < 2; ++i) {
+        const float pw = s[i][c] == -INFINITY ? 0.f : exp2_weight(s[i][c] - mx);
+        unsigned short bits;
+        float back;
+        if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
+        else { __half x = __float2half_rn(pw); bits = __half_as_ushort(x); back = __half2float(x); }
+        l[c] += back;
+        if (i < ntiles)
+          *reinterpret_cast<unsigned short*>(p_s + i * kMtPBytes + (tid >> 3) * 128 + (tid & 7) * 2 + (c >> 3) * 2048 + (c & 7) * 16) = bits;
+      }
     }
-#pragma unroll
-    for (int o = 16; o >= 1; o >>= 1) lsum += __shfl_xor_sync(0xffffffffu, lsum, o);
-    if (lane == 0) sm->red_sum[warp][c] = lsum;
+    sm->red_sum[warp][lane] = warp_reduce_columns(l, lane, [](float a, float b) { return a + b; });
   }
   // Rows of a V tile beyond the segment's length may hold anything: their weight is zero, but 0 x NaN would poison
   // the product, so they are cleared in shared memory.

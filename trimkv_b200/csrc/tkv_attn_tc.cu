@@ -214,7 +214,7 @@ decode_attn_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_co
         uint8_t* pt = p_s + i * kPBytes + (tid >> 3) * 128 + (tid & 7) * 2;
 #pragma unroll
         for (int g = 0; g < kG; ++g) {
-          const float pw = (s[i][g] == -INFINITY) ? 0.f : exp2f(s[i][g] - mx[g]);
+          const float pw = (s[i][g] == -INFINITY) ? 0.f : exp2_weight(s[i][g] - mx[g]);
           unsigned short bits;
           float back;
           if (kDtype == TKV_BF16) { __nv_bfloat16 x = __float2bfloat16_rn(pw); bits = __bfloat16_as_ushort(x); back = __bfloat162float(x); }
