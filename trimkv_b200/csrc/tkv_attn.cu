@@ -188,23 +188,36 @@ decode_attn_split_kernel(AttnParams p) {
 
 // Merged output value of (segment, query head g, dimension d) from the chunk partials; 0 for an empty segment.
 // Called by every thread of a kD-thread block (it synchronises the block).
+constexpr int kMergeEarly = 32;   // partial outputs per thread requested before anything else is known
+
+// Requests this thread's dimension of the first kMergeEarly chunk partials of (segment, row g).  Nothing here depends
+// on the segment's length, so the loads go out together with the length load; chunks beyond the live ones are
+// read too (the workspace covers nchunks per segment) and discarded by merge_partials.
 template <int kD>
-__device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, int g, int d, int len) {
+__device__ __forceinline__ void load_partials_early(const AttnParams& p, int seg, int g, int d, float (&early)[kMergeEarly]) {
+  const int64_t it0 = ((int64_t)seg * p.nchunks) * p.rows + g;
+#pragma unroll
+  for (int c = 0; c < kMergeEarly; ++c)
+    early[c] = (p.nchunks > 1 && c < p.nchunks) ? p.part_o[(it0 + (int64_t)c * p.rows) * kD + d] : 0.f;
+}
+
+template <int kD>
+__device__ __forceinline__ float merge_partials(const AttnParams& p, int seg, int g, int d, int len,
+                                                float (&early)[kMergeEarly]) {
   const int G = p.rows;   // query rows per segment (the G query heads, times the query tokens if there are several)
   float r = 0.f;
   const int nact = (len + p.chunk - 1) / p.chunk;
   const int64_t it0 = ((int64_t)seg * p.nchunks) * G + g;  // partial of chunk c: it0 + c*G
   if (nact <= kD) {
-    // One round trip for everything: the first kEarly partial outputs of this thread's dimension are requested
-    // before anything else, then thread c takes chunk c's (max, sum) pair, the block reduces them and the weights
-    // go to shared memory; by then the outputs have arrived and only need the weighted sum.
-    constexpr int kEarly = 32;
+    // One round trip for everything: the first partial outputs of this thread's dimension were requested by the
+    // caller before the length was known; thread c takes chunk c's (max, sum) pair, the block reduces them and the
+    // weights go to shared memory; by then the outputs have arrived and only need the weighted sum.
+    constexpr int kEarly = kMergeEarly;
     __shared__ float s_w[kD];
     __shared__ float s_red[2][kD / 32];
     const int lane = d & 31, warp = d >> 5;
-    float early[kEarly];
 #pragma unroll
-    for (int c = 0; c < kEarly; ++c) early[c] = c < nact ? p.part_o[(it0 + (int64_t)c * G) * kD + d] : 0.f;
+    for (int c = 0; c < kEarly; ++c) early[c] = c < nact ? early[c] : 0.f;   // chunks without tokens hold stale bytes
     float mc = -INFINITY, lc = 0.f;
     if (d < nact) {
       const float2 ml = *reinterpret_cast<const float2*>(&p.part_ml[(it0 + (int64_t)d * G) * 2]);
@@ -255,6 +268,8 @@ template <int kDtype, int kD>
 __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   const int seg = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
   grid_dependency_wait();  // launched with programmatic serialization behind the split kernel
+  float early[kMergeEarly];
+  load_partials_early<kD>(p, seg, g, d, early);
   if (p.seg_len[seg] > p.max_len && g == 0 && d == 0) report(p.status, TKV_DEV_LEN_BOUND);
   const int len = min(p.seg_len[seg], p.max_len);
   const int b = seg / p.hkv, h = seg - b * p.hkv;
@@ -264,7 +279,7 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_kernel(AttnParams p) {
   float r = 0.f;
   if (len > 0) {
     if (p.nchunks == 1) return;  // written by the split kernel
-    r = merge_partials<kD>(p, seg, g, d, len);
+    r = merge_partials<kD>(p, seg, g, d, len, early);
   }
   if (kDtype == TKV_BF16) reinterpret_cast<__nv_bfloat16*>(op)[d] = __float2bfloat16_rn(r);
   else reinterpret_cast<__half*>(op)[d] = __float2half_rn(r);
@@ -287,6 +302,8 @@ template <int kDtype, int kD>
 __global__ void __launch_bounds__(kD) decode_attn_combine_push_kernel(AttnParams p, PushParams pp) {
   const int seg = blockIdx.x, g = blockIdx.y, d = threadIdx.x;
   grid_dependency_wait();
+  float early[kMergeEarly];
+  load_partials_early<kD>(p, seg, g, d, early);
   if (p.seg_len[seg] > p.max_len && g == 0 && d == 0) report(p.status, TKV_DEV_LEN_BOUND);
   const int len = min(p.seg_len[seg], p.max_len);
   const int b = seg / p.hkv, h = seg - b * p.hkv;
@@ -296,7 +313,7 @@ __global__ void __launch_bounds__(kD) decode_attn_combine_push_kernel(AttnParams
     if (p.nchunks == 1) {
       bits = reinterpret_cast<const uint16_t*>(p.out + ((int64_t)b * p.hq + h * G + g) * (int64_t)kD * 2)[d];
     } else {
-      const float r = merge_partials<kD>(p, seg, g, d, len);
+      const float r = merge_partials<kD>(p, seg, g, d, len, early);
       if (kDtype == TKV_BF16) bits = __bfloat16_as_ushort(__float2bfloat16_rn(r));
       else bits = __half_as_ushort(__float2half_rn(r));
     }
