@@ -283,8 +283,11 @@ int tkv_decode_attn_multi(const void* q, int64_t q_sb, int64_t q_st, int64_t q_s
  * tkv_peer_wait: to be enqueued before the first kernel that reads the gathered buffer; returns (on the stream)
  * once every peer's flag has reached this rank's exchange count.  The wait is bounded (about four seconds), after
  * which the status word reports TKV_DEV_TIMEOUT and the stream continues.
- * A buffer may be written again by the peers two exchanges later; use at least two (three if the number of
- * exchanges per step is odd) in rotation.
+ * A buffer may be written again by the peers as soon as this rank has completed its NEXT exchange (raising its flag
+ * for exchange e+1 is what tells the peers that it has consumed the buffer of exchange e), so consecutive exchanges
+ * must use different buffers and a buffer's next use must lie at least two exchanges later: two buffers in
+ * alternation for an even number of exchanges per step, three (one of them for the first exchange of a step) in
+ * general; a single exchange per step is not supported.
  */
 int tkv_decode_attn_push(const void* q, int64_t q_sb, int64_t q_sh,
                          const void* k_cache, const void* v_cache,

@@ -208,6 +208,10 @@ class HeadShardedDecodeStep(FusedDecodeStep):
         # fused_gather: the attention merge stores into every rank's gathered buffer over NVLink and raises a flag
         # (PeerExchange) instead of a separate all-gather; set up lazily, when the batch size is known.
         self.fused_gather, self._xchg = fused_gather, None
+        if fused_gather and model.config.num_hidden_layers < 2:
+            # The buffer rotation relies on a second exchange between two uses of a buffer (it is what proves that the
+            # peers have read it); a one-layer model has none.
+            raise ValueError("fused_gather needs a model of at least two layers")
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
         cfg = model.config
         if cfg.num_key_value_heads % self.world:
