@@ -583,7 +583,8 @@ def main():
         # 561.2 MB against 545.5 MB algorithmic; scaled by the bytes.
         traffic = tot_b / len(ach) * (561.19 / 545.52) if args.workload == "qwen3-1.7b-decode" else None
         roofline = {"bound": "hbm", "kernel": "decode_attn_tc_kernel+decode_attn_combine_kernel", "achieved": gbs,
-                    "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src, "traffic": traffic,
+                    "peak": peak, "unit": "GB/s", "frac": gbs / peak, "peak_source": peak_src,
+                    "frac_of_nominal_8tbs": gbs / 8000.0, "traffic": traffic,
                     "launches_timed": len(ach), "avg_launch_us": tot_t / len(ach) * 1e6,
                     "bytes_per_launch": tot_b / len(ach)}
     evict = None
@@ -592,7 +593,8 @@ def main():
         eb = sum(nseg * (8 * n + (4 * D + 8) * 1 * M + 4 * D * M) for _, _, n in evict_events)  # 8n + 1032 M
         et = sum(a.elapsed_time(b) for a, b, _ in evict_events) * 1e-3
         evict = {"kernel": "evict_inplace_kernel", "segments": nseg, "achieved": eb / et / 1e9, "peak": peak,
-                 "unit": "GB/s", "frac": eb / et / 1e9 / peak, "launches_timed": len(evict_events),
+                 "unit": "GB/s", "frac": eb / et / 1e9 / peak, "frac_of_nominal_8tbs": eb / et / 1e9 / 8000.0,
+                 "launches_timed": len(evict_events),
                  "avg_launch_ms": et / len(evict_events) * 1e3}
 
     cpu = None
