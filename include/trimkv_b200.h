@@ -341,7 +341,10 @@ int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
  * Fused producer of one decode step (one new token per request), head_dim 128, bf16/f16.
  * Replaces, per layer, q_norm / k_norm, the retention-gate tail, RoPE, the transposes and
  * cache.update of TrimKVQwen3Attention.forward
- * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:328-353, gate tail :174-178).
+ * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:328-353, gate tail :174-178); with q_norm_w and
+ * k_norm_w both NULL the per-head RMSNorm is skipped, which is the producer of the Llama and Phi-3 attention
+ * (src/trimkv/models/llama/modeling_trimkv_llama.py:303-332, src/trimkv/models/phi3/modeling_trimkv_phi3.py:353-384;
+ * Phi-3's fused qkv_proj already has the q | k | v row layout).
  * qkvg : [batch, row_stride] rows holding  q (hq*128) | k (hkv*128) | v (hkv*128) | gate hidden (gate_inter),
  *        i.e. the output of one GEMM over the concatenated q/k/v/linear1 weights (linear1 bias included).
  * cos/sin : [128] of the model dtype for this token's position; pos: int64[1], that position.

@@ -11,6 +11,12 @@ files import a class that was removed), so an empty ``trimkv`` package whose
 ``trimkv.cache_utils`` / ``trimkv.attn.eager_attn`` are imported.  The flat cache
 classes call a CUDA-only Triton append; on CPU it is rebound to a per-head
 concatenation with the same semantics (src/trimkv/triton/db_cache_utils.py:97-117).
+
+The model files (``models/{qwen3,llama,phi3}/modeling_trimkv_*.py``) import under the installed
+transformers after two additions to transformers' own namespaces, made by ``import_reference_models``:
+an empty ``transformers.cache_utils.SlidingWindowCache`` (imported, never used on this path) and the
+plain ``ROPE_INIT_FUNCTIONS["default"]`` (inverse frequencies ``theta^(-2i/d)``, scale 1) that older
+transformers registered.  Nothing of the reference is edited.
 """
 import os
 import sys
@@ -313,8 +319,108 @@ def eager_attention(ea):
     print("eager_attention: ok")
 
 
+def import_reference_models():
+    """The reference's three model families (call after ``import_reference``)."""
+    import importlib
+    import transformers.cache_utils as tcu
+    from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
+    if not hasattr(tcu, "SlidingWindowCache"):
+        tcu.SlidingWindowCache = type("SlidingWindowCache", (), {})
+    if "default" not in ROPE_INIT_FUNCTIONS:
+        def default_rope(config, device=None, seq_len=None, **kw):
+            d = getattr(config, "head_dim", None) or config.hidden_size // config.num_attention_heads
+            rp = getattr(config, "rope_parameters", None) or {}
+            theta = rp.get("rope_theta", getattr(config, "rope_theta", 10000.0))
+            d = int(d * rp.get("partial_rotary_factor", getattr(config, "partial_rotary_factor", 1.0)))
+            return 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.int64).to(device=device, dtype=torch.float) / d)), 1.0
+        ROPE_INIT_FUNCTIONS["default"] = default_rope
+    for name in ("trimkv.models", "trimkv.models.qwen3", "trimkv.models.llama", "trimkv.models.phi3"):
+        pkg = types.ModuleType(name)
+        pkg.__path__ = [os.path.join(sys.modules["trimkv"].__path__[0], *name.split(".")[1:])]
+        sys.modules[name] = pkg
+    # the reference's own attention package (its __init__ holds the registry the models call)
+    del sys.modules["trimkv.attn"]
+    importlib.import_module("trimkv.attn")
+    out = {}
+    for fam, cfg_name, cls_name in (("qwen3", "TrimKVQwen3Config", "TrimKVQwen3ForCausalLM"),
+                                    ("llama", "TrimKVLlamaConfig", "TrimKVLlamaForCausalLM"),
+                                    ("phi3", "TrimKVPhi3Config", "TrimKVPhi3ForCausalLM")):
+        mod = importlib.import_module(f"trimkv.models.{fam}.modeling_trimkv_{fam}")
+        out[fam] = (getattr(mod, cfg_name), getattr(mod, cls_name))
+    return out
+
+
+def model_goldens(cu, models):
+    """Prompt + teacher-forced greedy decode through the reference's own model classes and ``TrimKVCache`` on CPU.
+
+    Per case (tiny_models.CASES: the three families with the ``rg`` gate, Qwen3 with ``rg2`` and ``rg3``): fp32 and
+    bf16 runs on the same token ids (the fp32 run's own greedy choices); after every forward the logits of the last
+    position, every layer's cache length and kept positions; plus the ids HF ``generate`` returns for the fp32 model
+    with a fresh reference cache.  Weights and prompt come from tiny_models.py."""
+    import tiny_models as tm
+    import warnings
+    warnings.filterwarnings("ignore")
+    for case, (fam, extra, T) in tm.CASES.items():
+        Cfg, Cls = models[fam]
+        cfg = Cfg(**dict(tm.FAMILIES[fam], **extra), attn_implementation="sdpa", pad_token_id=0,
+                  eos_token_id=None, bos_token_id=None)  # no end-of-sequence id: no row ever "finishes" under generate
+        model = Cls(cfg).eval()
+        shapes = {k: tuple(v.shape) for k, v in model.state_dict().items()}
+        sd = {k: torch.from_numpy(v) for k, v in tm.fill_state_dict(shapes).items()}
+        prompt = torch.from_numpy(tm.prompt_ids(fam, cfg.vocab_size))
+        L, Hkv, cap = cfg.num_hidden_layers, cfg.num_key_value_heads, cfg.memory_size + cfg.buffer_size
+        out = {"param_names": np.array(sorted(shapes)), "param_shapes": np.array([str(shapes[k]) for k in sorted(shapes)])}
+
+        def fresh(dt):
+            model.to(torch.float32).load_state_dict(sd, strict=True)       # .to() converts in place
+            m = model.to(dt)
+            # .to(bf16) also rounds the rotary inverse frequencies (a non-persistent buffer); a checkpoint loaded with
+            # from_pretrained(torch_dtype=bfloat16) keeps them in fp32, so put the fp32 values back.
+            m.model.rotary_emb.inv_freq = m.model.rotary_emb.original_inv_freq.clone().float()
+            return m
+
+        forced = None
+        for tag, dt in (("fp32", torch.float32), ("bf16", torch.bfloat16)):
+            m = fresh(dt)
+            cache = cu.TrimKVCache(device="cpu")
+            logits = np.zeros((T + 1, tm.BATCH, cfg.vocab_size), np.float32)
+            lens = np.zeros((T + 1, L), np.int32)
+            pos = np.full((T + 1, L, tm.BATCH, Hkv, cap), -1, np.int16)
+            ids, chosen = prompt, []
+            with torch.no_grad():
+                for t in range(T + 1):
+                    o = m(input_ids=ids, past_key_values=cache, logits_to_keep=1)
+                    logits[t] = o.logits[:, -1].float().numpy()
+                    for l in range(L):
+                        n = cache.get_cache_length(l)
+                        lens[t, l] = n
+                        pos[t, l, :, :, :n] = cache.kv_positions[l].numpy()
+                    nxt = o.logits[:, -1].argmax(-1, keepdim=True) if forced is None else forced[:, t:t + 1]
+                    chosen.append(nxt)
+                    ids = nxt
+            if forced is None:
+                forced = torch.cat(chosen, 1)          # [B, T+1]; the last one is never fed
+            out[f"logits_{tag}"], out[f"lens_{tag}"], out[f"pos_{tag}"] = logits, lens, pos
+        out["ids"] = torch.cat([prompt, forced[:, :T]], 1).numpy()
+        m = fresh(torch.float32)
+        with torch.no_grad():
+            gen = m.generate(prompt, attention_mask=torch.ones_like(prompt), max_new_tokens=24, do_sample=False,
+                             past_key_values=cu.TrimKVCache(device="cpu"))
+        out["generate_ids"] = gen.numpy()
+        assert np.array_equal(out["generate_ids"][:, tm.PROMPT_LEN:], forced[:, :24].numpy()), "generate != forward loop"
+        np.savez_compressed(os.path.join(HERE, f"model_{case}.npz"), **out)
+        d = np.abs(out["logits_fp32"] - out["logits_bf16"]).max()
+        print(f"model_{case}: lens {out['lens_fp32'][0].tolist()} -> {out['lens_fp32'][-1].tolist()}, |logits| max "
+              f"{np.abs(out['logits_fp32']).max():.2f}, fp32-bf16 max diff {d:.4f}, bf16 positions equal fp32: "
+              f"{np.array_equal(out['pos_fp32'], out['pos_bf16'])}")
+
+
 if __name__ == "__main__":
+    sys.path.insert(0, HERE)
     cu_, ea_ = import_reference(sys.argv[1])
+    if len(sys.argv) > 2 and sys.argv[2] == "models":      # only the model-level vectors
+        model_goldens(cu_, import_reference_models())
+        sys.exit(0)
     config1(cu_)
     ties_bf16(cu_)
     ties_single_shot(cu_)
@@ -325,3 +431,4 @@ if __name__ == "__main__":
     flat_budget_bf16(cu_)
     flat_budget_knorm(cu_)
     eager_attention(ea_)
+    model_goldens(cu_, import_reference_models())

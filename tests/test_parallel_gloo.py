@@ -93,7 +93,7 @@ def _shard_worker(rank, world, port, q):
         step = HeadShardedDecodeStep(model, types.SimpleNamespace(_hkv=hkv_l), group=None)
         h = torch.randn(3, cfg.hidden_size)
         ok = True
-        for l, (layer, w, bias, _) in enumerate(step.layers):
+        for l, (layer, w, bias, _, _) in enumerate(step.layers):
             w_l, b_l, g2_l, gb_l = step.local[l]
             full = F.linear(h, w, bias)
             mine = F.linear(h, w_l, b_l)

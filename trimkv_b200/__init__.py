@@ -7,9 +7,13 @@ from .cache_utils import BatchedDynamicBudgetTrimKVCache, DynamicBudgetTrimKVCac
 from .ops import update_flatten_view, update_flatten_view_triton
 from .attn import TRIMKV_ATTENTION_IMPLEMENTATIONS, get_attention_interface
 from .modeling_qwen3 import TrimKVQwen3Config, TrimKVQwen3ForCausalLM, TrimKVQwen3Model
+from .modeling_llama import TrimKVLlamaConfig, TrimKVLlamaForCausalLM, TrimKVLlamaModel
+from .modeling_phi3 import TrimKVPhi3Config, TrimKVPhi3ForCausalLM, TrimKVPhi3Model
 
 __all__ = [
     "TrimKVCache", "DynamicBudgetTrimKVCache", "BatchedDynamicBudgetTrimKVCache", "update_flatten_view",
     "update_flatten_view_triton", "TRIMKV_ATTENTION_IMPLEMENTATIONS", "get_attention_interface",
     "TrimKVQwen3Config", "TrimKVQwen3ForCausalLM", "TrimKVQwen3Model",
+    "TrimKVLlamaConfig", "TrimKVLlamaForCausalLM", "TrimKVLlamaModel",
+    "TrimKVPhi3Config", "TrimKVPhi3ForCausalLM", "TrimKVPhi3Model",
 ]

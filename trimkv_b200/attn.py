@@ -151,6 +151,19 @@ TRIMKV_ATTENTION_IMPLEMENTATIONS: Dict[str, Callable] = {
 }
 
 
+def register_with_transformers() -> None:
+    """Makes the registry's names known to transformers' own table of attention functions, so that a config whose
+    ``_attn_implementation`` is one of them passes ``PreTrainedModel``'s check at construction.  The models here
+    resolve the name through ``get_attention_interface``; transformers never calls these entries itself."""
+    try:
+        from transformers.modeling_utils import ALL_ATTENTION_FUNCTIONS
+    except ImportError:
+        return
+    for name, fn in TRIMKV_ATTENTION_IMPLEMENTATIONS.items():
+        if name not in ALL_ATTENTION_FUNCTIONS:
+            ALL_ATTENTION_FUNCTIONS.register(name, lambda *a, _fn=fn, **k: _fn(*a, **k)[:2])
+
+
 def get_attention_interface(attn_impl: str, compile: bool = False) -> Callable:
     if compile:
         raise NotImplementedError("torch.compile is not used on this path")

@@ -3,7 +3,7 @@
 // The reference runs the producer of the cache path as ~50 small PyTorch kernels per layer
 // (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:328-353: q_norm/k_norm, retention gate tail, RoPE,
 // transposes, then cache.update).  Here:
-//   decode_prep_kernel : q/k RMSNorm + RoPE, retention-gate tail (SiLU -> linear2 -> +bias -> logsigmoid),
+//   decode_prep_kernel : q/k RMSNorm (where the family has one) + RoPE, retention-gate tail (SiLU -> linear2 -> +bias -> logsigmoid),
 //                        and the append of K, V, log beta, position into the flat cache, one launch;
 //   add_rmsnorm_kernel : residual += delta, out = RMSNorm(residual) * weight;
 //   silu_mul_kernel    : SiLU(gate) * up of the MLP.
@@ -131,13 +131,19 @@ __global__ void __launch_bounds__(kPrepWarps * 32) decode_prep_kernel(PrepParams
       }
     }
   }
-  // RMSNorm over the head: fp32 statistics, normalised value rounded, then multiplied by the weight.
-  const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
-  const float rstd = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
+  // RMSNorm over the head: fp32 statistics, normalised value rounded, then multiplied by the weight.  Families
+  // without a per-head norm (Llama, Phi-3) pass no weights and the projection goes to RoPE as it is.
   const void* nw = is_q ? p.q_norm_w : p.k_norm_w;
   float y[4], rot[4], o[4];
+  if (nw != nullptr) {
+    const float ss = warp_sum(x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3]);
+    const float rstd = rsqrtf(ss * (1.0f / 128.0f) + p.eps);
 #pragma unroll
-  for (int i = 0; i < 4; ++i) y[i] = T::round(T::ld(nw, lane * 4 + i) * T::round(x[i] * rstd));
+    for (int i = 0; i < 4; ++i) y[i] = T::round(T::ld(nw, lane * 4 + i) * T::round(x[i] * rstd));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) y[i] = x[i];
+  }
   // RoPE: out = round(round(y * cos) + round(rotate_half(y) * sin)).
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -293,7 +299,9 @@ extern "C" int tkv_decode_prep(const void* qkvg, int64_t row_stride,
                                int in_splits, const void* in_bias,
                                int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
-  if (!qkvg || !q_norm_w || !k_norm_w || !cos || !sin || !gate_w2 || !gate_bias || !pos || !q_out || !k_cache ||
+  if ((q_norm_w == nullptr) != (k_norm_w == nullptr))
+    return fail(TKV_ERR_ARG, "tkv_decode_prep: q_norm_w and k_norm_w must both be given or both be NULL");
+  if (!qkvg || !cos || !sin || !gate_w2 || !gate_bias || !pos || !q_out || !k_cache ||
       !v_cache || !beta_cache || !pos_cache || !seg_len)
     return fail(TKV_ERR_ARG, "tkv_decode_prep: NULL pointer argument");
   if (head_dim != 128) return fail(TKV_ERR_UNSUPPORTED, "tkv_decode_prep: head_dim=%d (only 128)", head_dim);

@@ -25,32 +25,49 @@ class FusedDecodeStep:
     weights replace the originals' storage (the module parameters become views of them).
     """
 
+    @staticmethod
+    def supports(model) -> bool:
+        """Shapes the fused kernels cover: head_dim 128 rotated in full, the ``rg`` gate with at most 1024 hidden
+        units, SiLU activations (and, when it runs, 16-bit weights).  Anything else decodes through the module path."""
+        from .modeling_trimkv import head_dim_of, rotary_dim_of
+        cfg = model.config
+        return (head_dim_of(cfg) == 128 and rotary_dim_of(cfg) == 128 and cfg.retention_gate == "rg"
+                and getattr(cfg, "hidden_act", "silu") == "silu")
+
     def __init__(self, model, cache: TrimKVCache):
         cfg = model.config
-        if cfg.head_dim != 128 or cfg.retention_gate != "rg":
-            raise NotImplementedError("fused decode step needs head_dim 128 and retention_gate 'rg'")
+        if not self.supports(model):
+            raise NotImplementedError("fused decode step needs head_dim 128 (fully rotated), retention_gate 'rg' and SiLU")
         self.model, self.cache, self.cfg = model, cache, cfg
         self.layers = []
+
+        def fuse(parts):
+            """One weight (and bias) for several Linear modules that read the same input; the modules' parameters
+            become views of the fused storage."""
+            if len(parts) == 1:
+                return parts[0].weight, parts[0].bias
+            w = torch.cat([m.weight for m in parts], 0).contiguous()
+            bias = None
+            if any(m.bias is not None for m in parts):
+                bias = torch.cat([m.bias if m.bias is not None else m.weight.new_zeros(m.weight.shape[0])
+                                  for m in parts]).contiguous()
+            off = 0
+            for m in parts:
+                n = m.weight.shape[0]
+                m.weight.data = w[off:off + n]
+                if m.bias is not None:
+                    m.bias.data = bias[off:off + n]
+                off += n
+            return w, bias
+
         with torch.no_grad():
             for layer in model.model.layers[: cfg.num_hidden_layers]:
                 at, mlp = layer.self_attn, layer.mlp
-                parts = [at.q_proj, at.k_proj, at.v_proj, at.retention_gate.linear1]
-                w = torch.cat([m.weight for m in parts], 0).contiguous()
-                bias = None
-                if any(m.bias is not None for m in parts):
-                    bias = torch.cat([m.bias if m.bias is not None else m.weight.new_zeros(m.weight.shape[0])
-                                      for m in parts]).contiguous()
-                off = 0
-                for m in parts:  # re-point the module parameters at the fused storage
-                    n = m.weight.shape[0]
-                    m.weight.data = w[off:off + n]
-                    if m.bias is not None:
-                        m.bias.data = bias[off:off + n]
-                    off += n
-                gu = torch.cat([mlp.gate_proj.weight, mlp.up_proj.weight], 0).contiguous()
-                inter = mlp.gate_proj.weight.shape[0]
-                mlp.gate_proj.weight.data, mlp.up_proj.weight.data = gu[:inter], gu[inter:]
-                self.layers.append((layer, w, bias, gu))
+                # Phi-3 ships q|k|v and gate|up already fused (modeling_trimkv_phi3.py:98,338); Qwen3 and Llama do not.
+                qkv = [at.qkv_proj] if hasattr(at, "qkv_proj") else [at.q_proj, at.k_proj, at.v_proj]
+                w, bias = fuse(qkv + [at.retention_gate.linear1])
+                gu, gu_bias = fuse([mlp.gate_up_proj] if hasattr(mlp, "gate_up_proj") else [mlp.gate_proj, mlp.up_proj])
+                self.layers.append((layer, w, bias, gu, gu_bias))
         self.hq, self.hkv, self.eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps
         # tkv_skinny_gemm for the four per-layer projections.  Off by default: at 32 rows these GEMMs are bound by
         # launch and pipeline-fill latency, and the tensor-core kernel only matches cuBLAS (5-12 us per call either
@@ -85,13 +102,16 @@ class FusedDecodeStep:
         h = torch.empty_like(x)
         q_out = torch.empty(bsz, self.hq, 1, 128, dtype=x.dtype, device=x.device)
         delta, d_splits = None, 0
-        for l, (layer, w_qkvg, b_qkvg, w_gu) in enumerate(self.layers):
+        d_bias = None
+        for l, (layer, w_qkvg, b_qkvg, w_gu, b_gu) in enumerate(self.layers):
             at = layer.self_attn
-            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps, d_splits)
+            ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps, d_splits, d_bias if d_splits else None)
             qkvg, s1 = self._gemm(h, w_qkvg, "qkvg")
             if s1 == 0:
                 qkvg = F.linear(h, w_qkvg, b_qkvg)
-            k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin,
+            qn, kn = getattr(at, "q_norm", None), getattr(at, "k_norm", None)
+            k, v, kw = cache.decode_prep(l, qkvg, qn.weight if qn is not None else None,
+                                         kn.weight if kn is not None else None, self.eps, cos, sin,
                                          at.retention_gate.linear2.weight, at.retention_gate.bias, pos, q_out, self.hq,
                                          s1, b_qkvg if s1 else None)
             o, _, _ = tkv_attention_forward(at, q_out, k, v, None, scaling=at.scaling, flash_attn_kwargs=kw)
@@ -101,13 +121,14 @@ class FusedDecodeStep:
             ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps, s2, at.o_proj.bias if s2 else None)
             gu, s3 = self._gemm(h, w_gu, "gu")
             if s3 == 0:
-                gu = F.linear(h, w_gu)
+                gu = F.linear(h, w_gu, b_gu)
             act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
-            ops.silu_mul(gu, act, s3)
+            ops.silu_mul(gu, act, s3, b_gu if s3 else None)
+            d_bias = layer.mlp.down_proj.bias
             delta, d_splits = self._gemm(act, layer.mlp.down_proj.weight, "down")
             if d_splits == 0:
-                delta = F.linear(act, layer.mlp.down_proj.weight)
-        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps, d_splits)
+                delta = F.linear(act, layer.mlp.down_proj.weight, d_bias)
+        ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps, d_splits, d_bias if d_splits else None)
         return F.linear(h, self.model.lm_head.weight)
 
 
@@ -124,8 +145,7 @@ class GreedyDecoder:
         self.fused = None
         if head_shard_group is not None:
             self.fused = HeadShardedDecodeStep(model, cache, head_shard_group, fused_gather=fused_gather)
-        elif fused and model.config.head_dim == 128 and model.config.retention_gate == "rg" \
-                and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
+        elif fused and FusedDecodeStep.supports(model) and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
             self.fused = FusedDecodeStep(model, cache)
         dev = model.device
         self.batch = cache._batch
@@ -224,7 +244,7 @@ class HeadShardedDecodeStep(FusedDecodeStep):
         q0, k0 = self.rank * self.hq_l * d, self.rank * self.hkv_l * d
         self.local = []
         with torch.no_grad():
-            for layer, w, bias, _ in self.layers:
+            for layer, w, bias, _, _ in self.layers:
                 rows = torch.cat([torch.arange(q0, q0 + self.hq_l * d), hq * d + torch.arange(k0, k0 + self.hkv_l * d),
                                   (hq + hkv) * d + torch.arange(k0, k0 + self.hkv_l * d),
                                   torch.arange((hq + 2 * hkv) * d, w.shape[0])]).to(w.device)
@@ -268,12 +288,14 @@ class HeadShardedDecodeStep(FusedDecodeStep):
         q_out = torch.empty(bsz, self.hq_l, 1, 128, dtype=x.dtype, device=x.device)
         gathered = torch.empty(self.world, bsz, self.hq_l * 128, dtype=x.dtype, device=x.device)
         delta = None
-        for l, (layer, _, _, w_gu) in enumerate(self.layers):
+        for l, (layer, _, _, w_gu, b_gu) in enumerate(self.layers):
             at = layer.self_attn
             w_l, b_l, g2_l, gb_l = self.local[l]
             ops.add_rmsnorm(x, delta, layer.input_layernorm.weight, h, self.eps)
             qkvg = F.linear(h, w_l, b_l)
-            k, v, kw = cache.decode_prep(l, qkvg, at.q_norm.weight, at.k_norm.weight, self.eps, cos, sin, g2_l, gb_l,
+            qn, kn = getattr(at, "q_norm", None), getattr(at, "k_norm", None)
+            k, v, kw = cache.decode_prep(l, qkvg, qn.weight if qn is not None else None,
+                                         kn.weight if kn is not None else None, self.eps, cos, sin, g2_l, gb_l,
                                          pos, q_out, self.hq_l)
             if self.fused_gather:
                 full = self._attend_and_push(l, q_out, k, v, kw, at.scaling)
@@ -283,9 +305,9 @@ class HeadShardedDecodeStep(FusedDecodeStep):
                 full = gathered.permute(1, 0, 2).reshape(bsz, -1)      # rank-major head blocks = head order
             a = F.linear(full, at.o_proj.weight, at.o_proj.bias)
             ops.add_rmsnorm(x, a, layer.post_attention_layernorm.weight, h, self.eps)
-            gu = F.linear(h, w_gu)
+            gu = F.linear(h, w_gu, b_gu)
             act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
             ops.silu_mul(gu, act)
-            delta = F.linear(act, layer.mlp.down_proj.weight)
+            delta = F.linear(act, layer.mlp.down_proj.weight, layer.mlp.down_proj.bias)
         ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps)
         return F.linear(h, self.model.lm_head.weight)

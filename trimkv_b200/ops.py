@@ -231,10 +231,11 @@ def decode_prep(qkvg, q_norm_w, k_norm_w, eps: float, cos, sin, gate_w2, gate_bi
                 k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, cap: int, hq: int, hkv: int,
                 status=None, in_splits: int = 0, in_bias=None) -> None:
     """Fused q/k-norm + RoPE + retention-gate tail + append for one new token per request (head_dim 128).
+    ``q_norm_w`` / ``k_norm_w`` are both None for families without a per-head norm (Llama, Phi-3).
     ``qkvg`` is ``[B, cols]`` in the model dtype, or (``in_splits`` > 0) the fp32 ``[splits, B, cols]`` of skinny_gemm."""
     b, cols = qkvg.shape[-2], qkvg.shape[-1]
     rc = lib().tkv_decode_prep(
-        qkvg.data_ptr(), cols if in_splits else qkvg.stride(0), q_norm_w.data_ptr(), k_norm_w.data_ptr(), float(eps),
+        qkvg.data_ptr(), cols if in_splits else qkvg.stride(0), _ptr(q_norm_w), _ptr(k_norm_w), float(eps),
         cos.data_ptr(), sin.data_ptr(), gate_w2.data_ptr(), gate_bias.data_ptr(), gate_w2.shape[1],
         pos.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), beta_cache.data_ptr(),
         pos_cache.data_ptr(), seg_len.data_ptr(), _ptr(cu_seqlens), cap, b, hq, hkv, 128,
