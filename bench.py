@@ -61,14 +61,14 @@ class ClockSampler:
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index: int, period_ms: int = 20):
+        self.index, self.rows, self.proc, self.period_ms = index, [], None, period_ms
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -77,7 +77,7 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.time(), [x.strip() for x in line.split(",")]))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -88,10 +88,11 @@ class ClockSampler:
                 self.proc.kill()
             self.thread.join(timeout=2)
 
-    def summary(self):
+    def summary(self, t0=None, t1=None):
+        """Median SM clock and the throttle reasons seen between wall-clock times t0 and t1 (all samples if None)."""
         sm, mx, reasons = [], 0, set()
-        for r in self.rows:
-            if len(r) < 6 or not r[0].isdigit():
+        for t, r in list(self.rows):
+            if len(r) < 6 or not r[0].isdigit() or (t0 is not None and not (t0 <= t <= t1)):
                 continue
             sm.append(int(r[0])); mx = max(mx, int(r[1]))
             for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
@@ -161,27 +162,161 @@ def cpu_reference_run(cfg_kw, steps, warmup, sample_batch, seed=0):
     return sample_batch * steps / dt_s, dt_s / steps * 1e3
 
 
+def shutdown_process_group(decoder=None, limit_s: float = 60.0):
+    """Tears the NCCL communicator down.  A captured decode graph that holds collectives of the communicator must be
+    destroyed first: NCCL's communicator destruction waits until every CUDA graph that captured its work is gone.  A
+    watchdog bounds the wait and turns a teardown that does not return into exit code 3 instead of a silent stall."""
+    import torch.distributed as dist
+    if decoder is not None:
+        decoder.release_graph()
+    torch.cuda.synchronize()
+    dist.barrier()
+    torch.cuda.synchronize()
+
+    def give_up():
+        sys.stderr.write(f"bench.py: communicator teardown did not return within {limit_s:.0f} s\n")
+        sys.stderr.flush()
+        os._exit(3)
+    t = threading.Timer(limit_s, give_up)
+    t.daemon = True
+    t.start()
+    dist.destroy_process_group()
+    t.cancel()
+
+
+def host_threads():
+    """All host cores for the CPU arms: torch.distributed.run exports OMP_NUM_THREADS=1 to its workers, which would
+    otherwise leave the eager baseline on one core."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
+def reference_batch(wl, requested):
+    """Requests the host-core arm decodes per step: the workload's full batch when the host has the memory for the
+    eager path's cache plus the transient copies torch.cat makes of it, else the largest power-of-two fraction."""
+    if requested:
+        return min(requested, wl["batch"])
+    per_request = wl["num_hidden_layers"] * wl["num_key_value_heads"] * (wl["memory_size"] + wl["buffer_size"]) * wl["head_dim"] * 2 * 2
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:
+        avail = 32 << 30
+    weights = 4 << 30 if wl["hidden_size"] <= 2048 else 32 << 30
+    b = wl["batch"]
+    while b > 1 and weights + 3 * b * per_request > 0.6 * avail:
+        b //= 2
+    return b
+
+
 def run_reference(args, wl_name, wl):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = torch.get_num_threads()
-    sample_batch = args.cpu_batch
+    cores = host_threads()
+    sample_batch = reference_batch(wl, args.cpu_batch)
     tok_s, ms = cpu_reference_run(wl, args.steps, args.warmup, sample_batch)
-    sample = (f"{sample_batch} of {wl['batch']} requests, all {wl['num_hidden_layers']} layers, cache pre-filled with "
-              f"M={wl['memory_size']} random rows per head (prompt pass skipped), {args.steps} decode steps in bf16; "
-              "tok/s is that of the sample, not scaled to the full batch")
+    full = sample_batch == wl["batch"]
+    sample = (f"{'all ' if full else ''}{sample_batch} of {wl['batch']} requests per step, all {wl['num_hidden_layers']} layers, "
+              f"cache pre-filled with M={wl['memory_size']} random rows per head (the prompt pass is not part of a decode "
+              f"step), {args.steps} decode steps in bf16 on {cores} host threads"
+              + ("" if full else "; tok/s is that of the sample (per-step work is linear in the requests)"))
     line = {
         "impl": "reference", "metric": "decode_tok_per_s", "value": tok_s, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": wl_name, "global_batch": wl["batch"], "prompt_len": wl["prompt"],
-                   "memory_size": wl["memory_size"], "buffer_size": wl["buffer_size"]},
+        "config": {"workload": wl_name, "global_batch": wl["batch"], "batch_per_gpu": wl["batch"], "prompt_len": wl["prompt"],
+                   "memory_size": wl["memory_size"], "buffer_size": wl["buffer_size"],
+                   "cpu_sample_batch": sample_batch, "ran_on": "host cores of rank 0 (eager PyTorch path of the reference, restated)"},
         "cpu_baseline": {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": tok_s, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line))
+
+
+def micro_cache_phase(kind, M, nseg, steps, warmup, ctas=1, cpu_baseline=True, dev=None, Bf=128, D=128):
+    """The forced-eviction ("evict") or append ("append") phase of the kernel-level workload of the benchmark
+    specification (its configs[2]): nseg segments of bf16 K/V with live lengths uniform in [M, M+B], log beta =
+    logsigmoid(N(3, 1.5)) rounded to bf16, creation steps drawn without replacement from [0, 4M).  Every timed launch
+    works on a buffer the previous launch did not touch (buffers rotate; each exceeds L2).  Returns a dict with GB/s
+    from the algorithmic bytes (evict: 8 n + 1032 M per segment; append: 2 * 520 per segment) and CUDA-event times."""
+    from trimkv_b200 import ops
+    dev = dev or torch.device("cuda", torch.cuda.current_device())
+    peak, peak_src = measured_peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+    cap = M + Bf
+    ws = ops.evict_multi_workspace(nseg, M, ctas, dev) if ctas > 1 else None
+    nbuf = max(2, min(4, int(2e9 // (nseg * cap * 512)) or 2)) if kind == "evict" else 1
+    bufs = []
+    for _ in range(nbuf):
+        k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
+        beta = torch.nn.functional.logsigmoid(torch.randn(nseg * cap, generator=g, device=dev) * 1.5 + 3).bfloat16().float()
+        pos = torch.sort(torch.rand(nseg, 4 * M, generator=g, device=dev).argsort(-1)[:, :cap], -1)[0].to(torch.int32).view(-1)
+        bufs.append((k, v, beta, pos))
+    len0 = torch.randint(M + 1 if kind == "evict" else M, cap + (1 if kind == "evict" else 0),
+                         (nseg,), generator=g, device=dev, dtype=torch.int32)
+    ln, cu = len0.clone(), torch.zeros(nseg + 1, dtype=torch.int32, device=dev)
+    status = ops.new_status(dev)
+    kn = torch.randn(nseg // 8, 8, 1, D, generator=g, device=dev, dtype=torch.bfloat16)
+    bn = torch.zeros(nseg // 8, 8, 1, device=dev, dtype=torch.bfloat16)
+    pn = torch.tensor([4 * M], device=dev)
+    times = []
+    for i in range(warmup + steps):
+        k, v, beta, pos = bufs[i % nbuf]
+        ln.copy_(len0)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if kind == "evict":
+            if ctas > 1:
+                ops.evict_multi(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, ctas, ws, status=status)
+            else:
+                ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, None, status)
+        else:
+            ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
+        e1.record()
+        if i >= warmup:
+            times.append((e0, e1))
+    torch.cuda.synchronize()
+    assert ops.read_status(status) == 0
+    n_sum = int(len0.long().sum())
+    alg = (8 * n_sum + nseg * 1032 * M) if kind == "evict" else nseg * 2 * 520
+    res = {"kernel": "evict_inplace_kernel" if kind == "evict" else "append_warp_per_segment",
+           "config": {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16", "buffers": nbuf},
+           "ctas_per_segment": ctas, "peak": peak, "peak_source": peak_src, "unit": "GB/s"}
+    del bufs
+    if cpu_baseline:
+        # The reference's eager ops for the same phase on the host cores, on a sample of the segments
+        # (src/trimkv/cache_utils.py:104-108 for append, :172-198 for eviction), same algorithmic-byte formula.
+        ns, n = min(64, nseg), M + Bf
+        gc = torch.Generator().manual_seed(0)
+        kc = torch.randn(1, ns, n, D, generator=gc).bfloat16(); vc = torch.randn(1, ns, n, D, generator=gc).bfloat16()
+        bc = torch.nn.functional.logsigmoid(torch.randn(1, ns, n, generator=gc) * 1.5 + 3).bfloat16()
+        pc = torch.sort(torch.rand(1, ns, 4 * M, generator=gc).argsort(-1)[..., :n], -1)[0]
+        reps, t0 = 0, time.perf_counter()
+        while reps < 3 or time.perf_counter() - t0 < 3.0:
+            if kind == "evict":
+                sc = bc.to(torch.float32) * (4 * M + 1 - pc)
+                idx, _ = torch.sort(torch.topk(sc, M, dim=-1).indices, dim=-1)
+                _ = (kc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)), vc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)),
+                     bc.gather(-1, idx), pc.gather(-1, idx))
+            else:
+                _ = (torch.cat([kc, kc[:, :, :1]], dim=-2), torch.cat([vc, vc[:, :, :1]], dim=-2),
+                     torch.cat([bc, bc[:, :, :1]], dim=-1), torch.cat([pc, pc[:, :, :1]], dim=-1))
+            reps += 1
+        sec = (time.perf_counter() - t0) / reps
+        cpu_alg = ns * (8 * n + 1032 * M) if kind == "evict" else ns * 2 * 520
+        res["cpu_baseline"] = {"value": cpu_alg / sec / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
+                               "sample": f"{ns} of {nseg} segments with n = M+B = {n}, eager torch ops of the reference "
+                                         f"({'score/topk/sort/4 gathers' if kind == 'evict' else '4 torch.cat'}), {reps} repetitions"}
+    ms = sorted(a.elapsed_time(b) for a, b in times)
+    avg = sum(ms) / len(ms)
+    res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
+                "achieved": alg / (avg * 1e-3) / 1e9, "frac": alg / (avg * 1e-3) / 1e9 / peak,
+                "frac_of_nominal_8tbs": alg / (avg * 1e-3) / 1e9 / 8000.0})
+    return res
 
 
 def run_micro(args):
@@ -278,44 +413,12 @@ def run_micro(args):
         print(json.dumps(res))
         return
     if args.micro in ("evict", "append"):
-        cap = M + Bf
-        nbuf = max(2, min(4, int(2e9 // (nseg * cap * 512)) or 2)) if args.micro == "evict" else 1
-        bufs = []
-        for _ in range(nbuf):
-            k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
-            v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
-            beta = torch.nn.functional.logsigmoid(torch.randn(nseg * cap, generator=g, device=dev) * 1.5 + 3).bfloat16().float()
-            pos = torch.sort(torch.rand(nseg, 4 * M, generator=g, device=dev).argsort(-1)[:, :cap], -1)[0].to(torch.int32).view(-1)
-            bufs.append((k, v, beta, pos))
-        len0 = torch.randint(M + 1 if args.micro == "evict" else M, cap + (1 if args.micro == "evict" else 0),
-                             (nseg,), generator=g, device=dev, dtype=torch.int32)
-        ln, cu = len0.clone(), torch.zeros(nseg + 1, dtype=torch.int32, device=dev)
-        status = ops.new_status(dev)
-        kn = torch.randn(nseg // 8, 8, 1, D, generator=g, device=dev, dtype=torch.bfloat16)
-        bn = torch.zeros(nseg // 8, 8, 1, device=dev, dtype=torch.bfloat16)
-        pn = torch.tensor([4 * M], device=dev)
-        for i in range(args.warmup + args.steps):
-            k, v, beta, pos = bufs[i % nbuf]
-            ln.copy_(len0)
-            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            e0.record()
-            if args.micro == "evict":
-                if args.ctas > 1:
-                    ops.evict_multi(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, args.ctas, ws,
-                                    status=status)
-                else:
-                    ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, 4 * M + 1, M, M + 1, cap, None, status)
-            else:
-                ops.append(k, v, beta, pos, ln, cu, kn, kn, bn, pn, cap, status)
-            e1.record()
-            if i >= args.warmup:
-                times.append((e0, e1))
-        torch.cuda.synchronize()
-        assert ops.read_status(status) == 0
-        n_sum = int(len0.long().sum())
-        alg = (8 * n_sum + nseg * 1032 * M) if args.micro == "evict" else nseg * 2 * 520
-        res["config"] = {"nseg": nseg, "M": M, "B": Bf, "head_dim": D, "dtype": "bf16", "buffers": nbuf}
-    else:
+        out = micro_cache_phase(args.micro, M, nseg, args.steps, args.warmup, args.ctas, not args.no_cpu_baseline, dev)
+        out.update({"micro": args.micro, "steps": args.steps, "warmup": args.warmup, "achieved_gbs": out["achieved"],
+                    "frac_of_peak": out["frac"]})
+        print(json.dumps(out))
+        return
+    if True:
         if args.attn_shape == "config4":   # Qwen3-8B heads, ragged lengths
             batch, hq, hkv = args.nseg // 8, 32, 8
             lens = torch.exp(torch.randn(nseg, generator=g, device=dev) + 7.6246).clamp(64, 8192).round().to(torch.int32)
@@ -373,30 +476,6 @@ def run_micro(args):
             res["flash_attn_varlen"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
                          "mean_len": float(lens.float().mean()), "buffers": nbuf, "shape": args.attn_shape}
-    if args.micro in ("evict", "append") and not args.no_cpu_baseline:
-        # The reference's eager ops for the same phase on the host cores, on a sample of the segments
-        # (src/trimkv/cache_utils.py:104-108 for append, :172-198 for eviction), same algorithmic-byte formula.
-        ns, n = min(64, nseg), M + Bf
-        gc = torch.Generator().manual_seed(0)
-        kc = torch.randn(1, ns, n, D, generator=gc).bfloat16(); vc = torch.randn(1, ns, n, D, generator=gc).bfloat16()
-        bc = torch.nn.functional.logsigmoid(torch.randn(1, ns, n, generator=gc) * 1.5 + 3).bfloat16()
-        pc = torch.sort(torch.rand(1, ns, 4 * M, generator=gc).argsort(-1)[..., :n], -1)[0]
-        reps, t0 = 0, time.perf_counter()
-        while reps < 3 or time.perf_counter() - t0 < 3.0:
-            if args.micro == "evict":
-                sc = bc.to(torch.float32) * (4 * M + 1 - pc)
-                idx, _ = torch.sort(torch.topk(sc, M, dim=-1).indices, dim=-1)
-                _ = (kc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)), vc.gather(-2, idx.unsqueeze(-1).expand(-1, -1, -1, D)),
-                     bc.gather(-1, idx), pc.gather(-1, idx))
-            else:
-                _ = (torch.cat([kc, kc[:, :, :1]], dim=-2), torch.cat([vc, vc[:, :, :1]], dim=-2),
-                     torch.cat([bc, bc[:, :, :1]], dim=-1), torch.cat([pc, pc[:, :, :1]], dim=-1))
-            reps += 1
-        sec = (time.perf_counter() - t0) / reps
-        cpu_alg = ns * (8 * n + 1032 * M) if args.micro == "evict" else ns * 2 * 520
-        res["cpu_baseline"] = {"value": cpu_alg / sec / 1e9, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                               "sample": f"{ns} of {nseg} segments with n = M+B = {n}, eager torch ops of the reference "
-                                         f"({'score/topk/sort/4 gathers' if args.micro == 'evict' else '4 torch.cat'}), {reps} repetitions"}
     ms = sorted(a.elapsed_time(b) for a, b in times)
     avg = sum(ms) / len(ms)
     res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
@@ -429,19 +508,23 @@ def main():
                     help="with --head-sharded: the attention merge kernel stores into every rank's gathered buffer over "
                          "NVLink and raises a flag, instead of an NCCL all-gather per layer")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--cpu-batch", type=int, default=2, help="requests in the host-core baseline sample")
+    ap.add_argument("--cpu-batch", type=int, default=0,
+                    help="requests per step of the host-core arm (--impl reference; 0 = the full batch if host memory allows)")
+    ap.add_argument("--cpu-sample-batch", type=int, default=2, help="requests in the cpu_baseline sample of the native arm")
     ap.add_argument("--cpu-steps", type=int, default=12)
+    ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.warmup < 3:
         args.warmup = 3
     if args.micro:
         return run_micro(args)
-    if args.workload == "qwen3-14b-decode" and args.cpu_batch > 1:
-        args.cpu_batch = 1
+    if args.workload == "qwen3-14b-decode":
+        args.cpu_sample_batch = 1
+        args.cpu_batch = args.cpu_batch or 1
     if args.impl == "reference":
-        if args.steps > 64:
-            args.steps = 64  # bounded sample: the host-core run must end within minutes
+        if args.steps > 32:
+            args.steps = 32  # bounded: the host-core run must end within minutes
         return run_reference(args, args.workload, wl)
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -482,6 +565,8 @@ def main():
                             head_shard_group=dist.group.WORLD if sharded else None,
                             fused_gather=sharded and args.fused_gather)
         dec.ids.copy_(first)
+        clocks = ClockSampler(local)
+        clocks.__enter__()             # sampled from before the warm-up; the line reports the timed spans
         for _ in range(args.warmup):  # eager warm-up steps (allocate workspaces before any capture)
             dec.step(eager=True)
         if dec.use_graph:
@@ -508,58 +593,74 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return float(t.item())
 
-        # ---- timed region 1: device-resident decode (ids never leave the GPU)
-        sample_every = max(1, args.steps // 8)
-        attn_events, evict_events, lens_at_sample = [], [], []
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = ops.launch_count
-        barrier()
-        with ClockSampler(local) as clocks:
+        def advance_to(steps_before_trigger):
+            """Untimed steps until the cache is `steps_before_trigger` tokens short of M+B, so that a timed window
+            of any length holds an all-layer eviction (it fires once per B steps; a short window would miss it)."""
+            n = 0
+            while (M + Bf - cache.get_cache_length(0)) % Bf != steps_before_trigger % Bf and n < Bf:
+                dec.step(); n += 1
+            return n
+
+        def timed_steps(step_fn):
+            """K steps between events; a step on which the eviction fires is split so that the eviction launch is
+            bracketed by events of its own (graph replay, then compress: the same launches in the same order)."""
+            evs = []
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            w0 = time.time()
             e0.record()
             for i in range(args.steps):
-                sampled = (i % sample_every) == sample_every // 2
-                fires = cache.get_cache_length(0) + 1 >= M + Bf
-                if fires:
-                    # time the eviction kernel (all layers, one launch) on the launching stream
+                if cache.get_cache_length(0) + 1 >= M + Bf:
                     n_before = cache.get_cache_length(0) + 1
-                if sampled:
-                    tkv_attn.event_log = []
-                    lens_at_sample.append(cache.get_cache_length(0) + 1)
-                if fires:
-                    # split the step so the eviction launch can be bracketed by events
                     comp, cfg.compress_memory = cfg.compress_memory, False
-                    dec.step(eager=sampled)
+                    step_fn()
                     cfg.compress_memory = comp
                     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                     ev0.record()
                     cache.compress(memory_size=M, buffer_size=Bf)
                     ev1.record()
-                    evict_events.append((ev0, ev1, n_before))
+                    evs.append((ev0, ev1, n_before))
                 else:
-                    dec.step(eager=sampled)
-                if sampled:
-                    attn_events.append(tkv_attn.event_log)
-                    tkv_attn.event_log = None
+                    step_fn()
             e1.record()
             barrier()
-        ms_total = max_over_ranks(e0.elapsed_time(e1))
+            return max_over_ranks(e0.elapsed_time(e1)), evs, (w0, time.time())
+
+        # ---- timed region 1: device-resident decode (ids never leave the GPU); CUDA-graph replays only
+        pre1 = advance_to(max(1, args.steps // 2))
+        launches0 = ops.launch_count
+        ms_total, evict_events, span1 = timed_steps(lambda: dec.step())
         launches = ops.launch_count - launches0
-        clk = clocks.summary()
 
         # ---- timed region 2: end to end, ids cross PCIe both ways every step
         host_ids = torch.zeros(B, 1, dtype=torch.int64).pin_memory()
         host_ids.copy_(dec.next_ids)
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        barrier()
-        f0.record()
-        for i in range(args.steps):
+
+        def e2e_step():
             nxt = dec.step(host_ids)                      # H2D of this step's input ids (pinned)
             host_ids.copy_(nxt, non_blocking=True)        # D2H of the step's result
             torch.cuda.current_stream().synchronize()
-        f1.record()
-        barrier()
-        ms_e2e = max_over_ranks(f0.elapsed_time(f1))
+        pre2 = advance_to(max(1, args.steps // 2))
+        ms_e2e, evict_events2, span2 = timed_steps(e2e_step)
         cache.check_status()
+
+        # ---- untimed: the dominant kernel (decode attention) bracketed by events on the launching stream, on a few
+        # eagerly dispatched steps (the graph replays above cannot be bracketed per kernel)
+        attn_events, lens_at_sample = [], []
+        for _ in range(4):
+            tkv_attn.event_log = []
+            lens_at_sample.append(cache.get_cache_length(0) + 1)
+            dec.step(eager=True)
+            attn_events.append(tkv_attn.event_log)
+            tkv_attn.event_log = None
+        torch.cuda.synchronize()
+        clocks.__exit__(None, None, None)
+        clk = clocks.summary(span1[0], span2[1])
+        clk["samples_all"] = clocks.summary()["samples"]
+        clk["window"] = "both timed regions"
+        if clk["samples"] == 0:
+            clk = dict(clocks.summary(), window="whole run (no sample fell inside the timed regions)")
+        evict_events = evict_events + evict_events2
 
     tokens = B * args.steps * (1 if sharded else world)
     value = tokens / (ms_total * 1e-3)
@@ -597,12 +698,26 @@ def main():
                  "launches_timed": len(evict_events),
                  "avg_launch_ms": et / len(evict_events) * 1e3}
 
+    # ---- the second half of the metric, "cache update+evict GB/s": besides the in-window eviction above, the forced
+    # eviction and the append phase of the kernel-level workload (2048 segments, M = 4096, B = 128) on rank 0.
+    want_cpu = rank == 0 and world == 1 and not args.no_cpu_baseline
+    evict_micro = append_micro = None
+    if rank == 0 and not args.no_micro:
+        if want_cpu:
+            host_threads()
+        with torch.inference_mode():
+            evict_micro = micro_cache_phase("evict", 4096, 2048, 20, 5, 1, want_cpu, dev)
+            append_micro = micro_cache_phase("append", 4096, 2048, 50, 10, 1, want_cpu, dev)
+        append_micro["note"] = "2 MB per launch: bound by launch latency, not by bandwidth"
+
     cpu = None
-    if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        tok_s, ms = cpu_reference_run(wl, args.cpu_steps, 2, args.cpu_batch)
-        cpu = {"value": tok_s, "unit": "tok/s", "cores": torch.get_num_threads(), "kind": "port",
-               "sample": f"{args.cpu_batch} of {B} requests, all {L} layers, cache pre-filled with M={M} random rows per head, "
-                         f"{args.cpu_steps} decode steps in bf16 ({ms:.0f} ms/step); not scaled to the full batch"}
+    if want_cpu:
+        cores = host_threads()
+        tok_s, ms = cpu_reference_run(wl, args.cpu_steps, 2, args.cpu_sample_batch)
+        cpu = {"value": tok_s, "unit": "tok/s", "cores": cores, "kind": "port",
+               "sample": f"{args.cpu_sample_batch} of {B} requests, all {L} layers, cache pre-filled with M={M} random rows per head, "
+                         f"{args.cpu_steps} decode steps in bf16 ({ms:.0f} ms/step); tok/s of the sample (per-step work is "
+                         "linear in the requests)"}
 
     if rank == 0:
         line = {
@@ -614,22 +729,18 @@ def main():
                        "memory_size": M, "buffer_size": Bf, "parallelism": ((f"kv-head-shard x{world}" + (" (merge kernel pushes to peers)" if args.fused_gather else " (NCCL all-gather)"))
                                        if sharded else f"batch-partition x{world}"),
                        "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
+                       "untimed_steps_before_windows": [pre1, pre2],
+                       "evictions_in_windows": len(evict_events),
                        "l2": "per-step working set (all weights + every cached K/V row, many GB) exceeds the 126 MB L2; no explicit flush"},
-            "roofline": roofline, "evict": evict, "cpu_baseline": cpu,
+            "roofline": roofline, "evict": evict, "evict_micro": evict_micro, "append": append_micro, "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * 8 * world, "d2h_bytes_per_step": B * 8 * world},
             "gpu_launches": launches * world, "clocks": clk,
         }
         print(json.dumps(line))
     if world > 1:
-        if sharded:
-            # NCCL collectives live inside the captured decode graph; communicator teardown with such a graph alive
-            # did not return on this stack, so the sharded mode synchronises and leaves without it.
-            sys.stdout.flush()
-            torch.cuda.synchronize()
-            dist.barrier()
-            os._exit(0)
-        dist.destroy_process_group()
+        sys.stdout.flush()
+        shutdown_process_group(dec)
 
 
 if __name__ == "__main__":

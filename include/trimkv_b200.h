@@ -219,7 +219,10 @@ int tkv_rebuild_cu_seqlens(const int32_t* seg_len, int32_t* cu_seqlens, int nseg
  * for segment s = b*hkv + h the G = hq/hkv query heads h*G..h*G+G-1 of request b attend to
  * rows [start(s), start(s)+seg_len[s]) of k_cache/v_cache, softmax in f32, scale applied to
  * q.k before the softmax.  start(s) = seg_start[s] if seg_start != NULL (packed layout,
- * cu_seqlens_k of the reference) else s*cap.
+ * cu_seqlens_k of the reference) else s*cap.  With seg_start, cap states the number of rows of the packed
+ * k_cache / v_cache (sum of the lengths, at least seg_start[s] + seg_len[s] for every s): the tensor-core
+ * kernel bounds its tile loads by it; cap = 0 (rows not stated) selects the CUDA-core kernel, which reads
+ * row by row.
  * q   : [batch, hq, D] with element strides (q_sb, q_sh); same dtype as K/V (bf16 or f16).
  * out : [batch, hq, D] contiguous (the reference's [B, Q=1, Hq, D], flash_attn.py:147-149).
  * workspace: tkv_decode_attn_workspace_bytes(...) bytes of scratch, 256-byte aligned.
@@ -322,10 +325,14 @@ int tkv_ipc_close(void* base);
  * synchronisation of cudaMalloc/cudaFree.  Same arguments and results as tkv_decode_attn without
  * `workspace`; the per-chunk partial results live in an array of TKV_STATIC_SCRATCH_BYTES that is part of
  * the library image, so every GPU that loads the library holds that much memory until the process exits.
- *  - Limit: problems whose tkv_decode_attn_workspace_bytes(...) exceeds TKV_STATIC_SCRATCH_BYTES are
- *    refused with TKV_ERR_UNSUPPORTED (nothing is launched); use tkv_decode_attn for those.
+ *  - Limit: problems whose per-chunk partials exceed TKV_STATIC_SCRATCH_BYTES (never more than
+ *    tkv_decode_attn_workspace_bytes(...) of the same problem) are refused with TKV_ERR_UNSUPPORTED (nothing is
+ *    launched); use tkv_decode_attn for those.
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with that
  *    device current); make that first call outside any stream capture.  No call allocates or frees memory.
+ *    The address is kept per device for the life of the process, so do not call this after cudaDeviceReset.
+ *  - It runs the CUDA-core split kernel for every shape (head_dim 64 or 128, bf16 or f16, either layout; with
+ *    seg_start, cap is not used).
  *  - All calls on a device share the one array, and it keeps whatever the previous call left there (no call
  *    relies on its initial content).  Two calls that can overlap on the GPU (different streams, or a second
  *    process thread) race on it: serialise them on one stream or order them with events.

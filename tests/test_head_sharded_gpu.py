@@ -60,22 +60,30 @@ def _worker(rank, world, port, q):
                     n = cache.get_cache_length(0)
                     results[tag + "/" + mode] = (torch.stack(logits).cpu().numpy(),
                                                  cache.kv_positions[0][:, :, :n].cpu().numpy(), n)  # by value
+                    # The captured step holds the communicator's collectives; the communicator can only be
+                    # destroyed once no such graph is left.
+                    dec.release_graph()
+                    del dec
                     torch.cuda.synchronize()
                     dist.barrier()
         q.put((rank, results))
         q.close()
         q.join_thread()          # results are on their way before anything else can go wrong
-        torch.cuda.synchronize()
-        dist.barrier()
     except Exception:            # the parent must see the failure instead of waiting for a result that never comes
         import traceback
         q.put((rank, {"error": traceback.format_exc()}))
         q.close()
         q.join_thread()
-    finally:
-        # Leave without NCCL / CUDA-graph teardown: destroying a communicator whose collectives were captured in a
-        # still-live CUDA graph did not return here, and the test is about the numbers, which are already sent.
-        os._exit(0)
+        os._exit(1)
+    # Orderly teardown, bounded: a destroy that does not return ends the process with code 3, which the parent checks.
+    import threading
+    torch.cuda.synchronize()
+    dist.barrier()
+    watchdog = threading.Timer(60.0, lambda: os._exit(3))
+    watchdog.daemon = True
+    watchdog.start()
+    dist.destroy_process_group()
+    watchdog.cancel()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
@@ -90,11 +98,12 @@ def test_head_sharded_decode_equals_unsharded():
         got = dict(q.get(timeout=240) for _ in range(world))
     finally:
         for p in procs:
-            p.join(timeout=30)
+            p.join(timeout=90)
             if p.is_alive():
                 p.terminate()
     for rank in range(world):
         assert "error" not in got[rank], got[rank]["error"]
+    assert [p.exitcode for p in procs] == [0] * world, "communicator teardown did not complete"
     for tag in ("short", "long"):
         for rank in range(world):
             full_logits, full_pos, n_full = got[rank][tag + "/full"]

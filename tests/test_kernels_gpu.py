@@ -229,7 +229,8 @@ def test_select_then_compact_from_dense_prompt(ops):
 
 
 def test_full_size_eviction_properties(ops):
-    """Benchmark-spec configs[2] sizes (2048 segments, M=4096, B=128): properties that need no oracle."""
+    """Benchmark-spec configs[2] sizes (2048 segments, M=4096, B=128): properties that hold for all segments, and the
+    oracle's selection on a sample of them."""
     gen = torch.Generator(device=DEV).manual_seed(0)
     nseg, m, bsz, d = 2048, 4096, 128, 128
     cap = m + bsz
@@ -262,6 +263,20 @@ def test_full_size_eviction_properties(ops):
     rows = (torch.arange(nseg, device=DEV)[:, None] * cap + idx).view(-1)
     assert torch.equal(k.view(nseg, cap, d)[:, :m].reshape(-1, d), k0[rows])
     assert torch.equal(v.view(nseg, cap, d)[:, :m].reshape(-1, d), v0[rows])
+    # the oracle's canonical selection (ties to the lower index) on a sample of 96 segments: kept positions,
+    # log beta and the K/V payload bit for bit
+    rng = np.random.default_rng(1)
+    sample = np.unique(np.concatenate([rng.choice(nseg, 94, replace=False), [0, nseg - 1]]))
+    l0_h, b0_h, p0_h = l0.cpu().numpy(), b0.cpu().numpy(), p0.cpu().numpy()
+    for sgm in sample:
+        n = int(l0_h[sgm])
+        if n <= m:
+            continue
+        idx = orc.canonical_topm(orc.retention_scores(b0_h[sgm, :n], p0_h[sgm, :n], step + 1), m)
+        assert np.array_equal(pos[sgm, :m].cpu().numpy(), p0_h[sgm, idx]), sgm
+        assert np.array_equal(beta[sgm, :m].cpu().numpy(), b0_h[sgm, idx]), sgm
+        src = torch.from_numpy(idx).to(DEV) + sgm * cap
+        assert torch.equal(k.view(nseg, cap, d)[sgm, :m], k0[src]) and torch.equal(v.view(nseg, cap, d)[sgm, :m], v0[src]), sgm
 
 
 # ---------------------------------------------------------------- decode attention
@@ -415,13 +430,29 @@ def test_consumers_accept_gemm_partials(ops):
     assert torch.equal(a1, a2)
 
 
+def _oracle_attention_sample(q, k_seg, v_seg, lens, hkv, sample):
+    """fp32 oracle outputs [len(sample), G, D] for the sampled segments; k_seg(s) / v_seg(s) return that segment's rows."""
+    bsz, hq, d = q.shape
+    g = hq // hkv
+    want = np.zeros((len(sample), g, d), np.float32)
+    for i, s in enumerate(sample):
+        b, h = divmod(int(s), hkv)
+        n = int(lens[s])
+        qs = q[b, h * g:(h + 1) * g].float().cpu().numpy()[None, :, None, :]   # [1, G, 1, D]: one request, one KV head
+        ks, vs = k_seg(s)[:n].float().cpu().numpy(), v_seg(s)[:n].float().cpu().numpy()
+        want[i] = orc.varlen_gqa_attention(qs, ks, vs, np.asarray([0, n], np.int32), 1, 1)[0, 0]
+    return want
+
+
 def test_full_size_attention_cross_check(ops):
     """benchmark-spec configs[3] sizes (batch 64, 32/8 heads, lognormal lengths in [64, 8192]): the tensor-core kernel on the
-    capacity-strided layout against the CUDA-core kernel on the packed copy of the same cache, plus two properties that
-    need no second implementation (constant V gives that constant; the output is a convex combination of V rows)."""
+    capacity-strided layout and on the packed copy of the same cache (the reference's own layout), and the CUDA-core
+    kernel on the packed copy, each against the fp32 oracle on a sample of 96 segments (the shortest, the longest and
+    random ones) and against one another on all 512; plus two properties that need no second implementation
+    (constant V gives that constant; the output is a convex combination of V rows)."""
     gen = torch.Generator(device=DEV).manual_seed(0)
     bsz, hq, hkv, d, cap = 64, 32, 8, 128, 8192
-    nseg = bsz * hkv
+    nseg, g = bsz * hkv, hq // hkv
     lens = torch.exp(torch.randn(nseg, generator=gen, device=DEV) + 7.6246).clamp(64, 8192).round().to(torch.int32)
     q = torch.randn(bsz, hq, d, generator=gen, device=DEV, dtype=torch.bfloat16)
     k = torch.randn(nseg * cap, d, generator=gen, device=DEV, dtype=torch.bfloat16)
@@ -434,10 +465,22 @@ def test_full_size_attention_cross_check(ops):
     kp, vp = k[mask].contiguous(), v[mask].contiguous()
     cu = torch.zeros(nseg + 1, dtype=torch.int32, device=DEV)
     cu[1:] = lens.cumsum(0)
-    out2 = torch.empty_like(out)
-    ops.decode_attn(q, kp, vp, lens, cu[:-1].contiguous(), 0, out2, ws, hkv, d ** -0.5, cap, status)
+    starts = cu[:-1].contiguous()
+    out_packed_tc, out_packed_cc = torch.empty_like(out), torch.empty_like(out)
+    ops.decode_attn(q, kp, vp, lens, starts, 0, out_packed_tc, ws, hkv, d ** -0.5, cap, status)                  # tensor cores
+    ops.decode_attn(q, kp, vp, lens, starts, 0, out_packed_cc, ws, hkv, d ** -0.5, cap, status, packed_rows=0)   # CUDA cores
     assert ops.read_status(status) == 0
-    assert float((out.float() - out2.float()).abs().max()) <= 2e-2
+    assert float((out.float() - out_packed_cc.float()).abs().max()) <= 2e-2
+    assert torch.equal(out, out_packed_tc)      # same tiles, same arithmetic: the layout changes addresses only
+    lens_h = lens.cpu().numpy()
+    order = np.argsort(lens_h)
+    rng = np.random.default_rng(0)
+    sample = np.unique(np.concatenate([order[:8], order[-8:], rng.choice(nseg, 80, replace=False)]))
+    k3, v3 = k.view(nseg, cap, d), v.view(nseg, cap, d)
+    want = _oracle_attention_sample(q, lambda s: k3[s], lambda s: v3[s], lens_h, hkv, sample)
+    for name, o in (("strided/tc", out), ("packed/tc", out_packed_tc), ("packed/cuda-core", out_packed_cc)):
+        got = o.float().view(bsz, hkv, g, d).cpu().numpy().reshape(nseg, g, d)[sample]
+        assert np.max(np.abs(got - want)) <= 2e-2, name
     vmax = v.view(nseg, cap, d).float().masked_fill(~mask.view(nseg, cap, 1), -1e30).amax(1)   # per segment, per dim
     vmin = v.view(nseg, cap, d).float().masked_fill(~mask.view(nseg, cap, 1), 1e30).amin(1)
     o = out.float().view(bsz, hkv, hq // hkv, d)
@@ -498,3 +541,48 @@ def test_peer_wait_gives_up_when_no_peer_answers(ops):
     assert ops.read_status(status) == 0 and sync.tolist() == [0, 0, 2]
     x = torch.arange(8, device=DEV).sum().item()                       # the context is fine
     assert x == 28
+
+
+def test_push_exchange_two_ranks_emulated_on_one_gpu(ops):
+    """The head-sharded exchange with both "ranks" on one GPU, one after the other on one stream: each rank's gathered
+    buffer and flag array live in this GPU's memory, rank 0's merge kernel stores its column block into both buffers
+    and raises its flag in rank 1's array, then rank 1's does the same; only then do the wait kernels run, so
+    they find their flags raised and never spin.  Both buffers must hold what the oracle computes for all heads.
+    Two exchanges in a row (the counters advance): one chunk per segment (the split kernel writes the output itself)
+    and several chunks (merged partials)."""
+    import ctypes
+    gen = torch.Generator().manual_seed(31)
+    bsz, hq, hkv, d, world = 3, 8, 4, 128, 2          # per rank: 8 query / 4 KV heads; 16 / 8 in total
+    width = world * hq * d
+    flags = [torch.zeros(world, dtype=torch.int32, device=DEV) for _ in range(world)]
+    sync = [torch.zeros(3, dtype=torch.int32, device=DEV) for _ in range(world)]
+    status = ops.new_status(DEV)
+    flag_ptrs = (ctypes.c_void_p * world)(*[f.data_ptr() for f in flags])
+    for call, cap in enumerate((200, 1300)):
+        nseg = bsz * hkv
+        gathered = [torch.full((bsz, width), 7.0, dtype=torch.bfloat16, device=DEV) for _ in range(world)]
+        out_ptrs = (ctypes.c_void_p * world)(*[g.data_ptr() for g in gathered])
+        want = np.zeros((bsz, width), np.float32)
+        for rank in range(world):
+            lens = torch.randint(1, cap + 1, (nseg,), generator=gen).to(torch.int32)
+            lens[-1] = cap
+            q = torch.randn(bsz, hq, d, generator=gen).bfloat16().to(DEV)
+            k = torch.randn(nseg * cap, d, generator=gen).bfloat16().to(DEV)
+            v = torch.randn(nseg * cap, d, generator=gen).bfloat16().to(DEV)
+            local = torch.empty(bsz, hq, d, dtype=torch.bfloat16, device=DEV)
+            ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, cap), dtype=torch.uint8, device=DEV)
+            ops.decode_attn_push(q, k, v, lens.to(DEV), cap, local, ws, hkv, d ** -0.5, cap, out_ptrs, flag_ptrs, world, rank,
+                                 width, rank * hq * d, sync[rank], status)
+            mask = (torch.arange(cap)[None, :] < lens[:, None]).view(-1)
+            cu = np.concatenate([[0], np.cumsum(lens.numpy())]).astype(np.int32)
+            want[:, rank * hq * d:(rank + 1) * hq * d] = orc.varlen_gqa_attention(
+                q.float().cpu().numpy()[:, :, None, :], k.float().cpu()[mask].numpy(), v.float().cpu()[mask].numpy(),
+                cu, bsz, hkv)[:, 0].reshape(bsz, hq * d)
+        for rank in range(world):
+            ops.peer_wait(flags[rank], sync[rank], world, rank, status, max_polls=1000)
+        assert ops.read_status(status) == 0
+        for rank in range(world):
+            peer = 1 - rank
+            assert int(flags[rank][peer]) == call + 1 and int(flags[rank][rank]) == 0   # a rank raises flags on peers only
+            assert sync[rank].tolist() == [0, call + 1, call + 1]
+            assert np.abs(gathered[rank].float().cpu().numpy() - want).max() <= 2e-2, (call, rank)

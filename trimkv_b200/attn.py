@@ -20,6 +20,7 @@ import torch.nn.functional as F
 from . import ops
 
 _workspaces: Dict[torch.device, torch.Tensor] = {}
+_retired = []   # outgrown workspaces: kept alive because a captured CUDA graph may still hold their address
 
 # Optional profiling hook: when set to a list, the decode path appends (start_event, end_event, batch, hkv)
 # around each native attention call.  The benchmark uses it to time the kernel on the launching stream.
@@ -27,8 +28,13 @@ event_log = None
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
+    """Scratch for the split-KV partials, one growing buffer per device.  A buffer that is outgrown is retired, not
+    freed: a decode step captured in a CUDA graph has its address baked in and keeps writing there on replay.  Calls
+    on one device are expected on one stream (they share the buffer)."""
     ws = _workspaces.get(device)
     if ws is None or ws.numel() < nbytes:
+        if ws is not None:
+            _retired.append(ws)
         ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
         _workspaces[device] = ws
     return ws

@@ -39,16 +39,18 @@ def build(force: bool = False, verbose: bool = False) -> str:
     flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
     if verbose:
         flags += ["-Xptxas", "-v"]
-    objs = []
-    for src in SOURCES:
-        obj = os.path.join(CSRC, src.replace(".cu", ".o"))
-        cmd = [nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if verbose or r.returncode != 0:
-            print(" ".join(cmd)); print(r.stdout); print(r.stderr)
-        if r.returncode != 0:
-            raise RuntimeError(f"nvcc failed on {src}")
-        objs.append(obj)
+    objs = [os.path.join(CSRC, src.replace(".cu", ".o")) for src in SOURCES]
+    cmds = [[nvcc, *flags, "-c", os.path.join(CSRC, src), "-o", obj] for src, obj in zip(SOURCES, objs)]
+    procs = [subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for cmd in cmds]
+    failed = []
+    for src, cmd, proc in zip(SOURCES, cmds, procs):       # the translation units are independent: compile them side by side
+        out, err = proc.communicate()
+        if verbose or proc.returncode != 0:
+            print(" ".join(cmd)); print(out); print(err)
+        if proc.returncode != 0:
+            failed.append(src)
+    if failed:
+        raise RuntimeError(f"nvcc failed on {', '.join(failed)}")
     cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

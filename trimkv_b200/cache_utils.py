@@ -25,6 +25,9 @@ from . import ops
 
 __all__ = ["TrimKVCache", "DynamicBudgetTrimKVCache", "BatchedDynamicBudgetTrimKVCache"]
 
+# Longest segment tkv_evict_select / tkv_evict accept (kMaxSelectLen in csrc/tkv_evict.cu).
+MAX_ONE_PIECE_PROMPT = 57000
+
 
 class _LayerViews:
     """List-like accessor (``cache.key_cache[layer]``) that builds views of the slabs on demand."""
@@ -311,6 +314,11 @@ class TrimKVCache:
             pos32 = pos.to(torch.int32).reshape(nseg, n).contiguous()
             kept_idx = kept_cnt = None
             if do_select and m is not None and bsz is not None and n >= m + bsz:
+                if n > MAX_ONE_PIECE_PROMPT:
+                    raise ValueError(
+                        f"a prompt of {n} tokens cannot be reduced to memory_size in one piece (the selection kernel "
+                        f"holds one score per token in shared memory, at most {MAX_ONE_PIECE_PROMPT}); feed it in pieces: "
+                        "model.generate(..., prefill_chunk_size=N) or several forward calls of at most that many tokens")
                 kept_idx = torch.empty(nseg, m, dtype=torch.int32, device=dev)
                 kept_cnt = torch.empty(nseg, dtype=torch.int32, device=dev)
                 ops.evict_select(beta32, pos32, None, n, nseg, self.n_seen_tokens[l] + 1, m, m + bsz, n,
@@ -529,6 +537,19 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
             self._rows[layer_idx] += bsz * h * s
         out = super().update(key_states, value_states, retention_weights, cache_positions, layer_idx, cache_kwargs)
         return out
+
+    def decode_prep(self, layer_idx: int, *args, **kwargs):
+        # One new row per segment: keep the host-side row total in step (compress() triggers on it and the attention
+        # grid is sized by it) before the kwargs of this step are built.
+        while len(self._rows) <= layer_idx:
+            self._rows.append(0)
+        self._rows[layer_idx] += self._batch * self._hkv
+        return super().decode_prep(layer_idx, *args, **kwargs)
+
+    def advance(self, num_tokens: int = 1) -> None:
+        super().advance(num_tokens)
+        for l in range(len(self._rows)):
+            self._rows[l] += self._batch * self._hkv * num_tokens
 
     def _attn_kwargs(self, l: int) -> Dict[str, Any]:
         kw = super()._attn_kwargs(l)

@@ -6,7 +6,6 @@
 // Here the segment table is read on the device; a work item is (segment, chunk of kChunk tokens); each
 // item produces an unnormalised partial output and its (max, sum) in log2 domain, and a combine kernel
 // merges the chunks of a segment.  Per cached token the kernel reads 2*D*elem bytes exactly once.
-#include <cstdlib>
 #include "tkv_common.cuh"
 #include "tkv_attn.cuh"
 
@@ -399,16 +398,11 @@ int launch_decode_attn_combine(const AttnParams& p, int nseg, int G, int head_di
   return check_launch("tkv_decode_attn(combine)");
 }
 
-// Which split kernel serves a problem: the tensor-core one whenever its layout requirements hold, unless the
-// environment variable TKV_ATTN_IMPL=simt asks for the CUDA-core kernel (A/B measurements).
-static bool use_tensor_core_path(int head_dim, int kv_dtype, int G, const void* seg_start, int64_t rows) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("TKV_ATTN_IMPL");
-    forced = (e != nullptr && e[0] == 's') ? 1 : 0;
-  }
-  return forced == 0 && head_dim == 128 && (kv_dtype == TKV_BF16 || kv_dtype == TKV_F16) && G <= 8 && seg_start == nullptr &&
-         rows >= 128;  // the TMA box is 128 rows
+// Which split kernel serves a problem: the tensor-core one whenever its requirements hold (16-bit, head_dim 128,
+// at most 8 query heads per KV head, and at least one 128-row TMA box of rows whose count the caller stated);
+// everything else (head_dim 64, tiny caches, a packed layout of unstated size) runs on the CUDA-core kernel.
+static bool use_tensor_core_path(int head_dim, int kv_dtype, int G, int64_t rows) {
+  return head_dim == 128 && (kv_dtype == TKV_BF16 || kv_dtype == TKV_F16) && G <= 8 && rows >= 128;
 }
 
 int attn_chunk_tokens(int nseg, int max_len) {
@@ -487,9 +481,11 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
   p.k = (const char*)k_cache; p.v = (const char*)v_cache;
   p.seg_len = seg_len; p.seg_start = seg_start; p.cap = cap;
   p.out = (char*)out;
-  const bool tc = use_tensor_core_path(head_dim, kv_dtype, G, seg_start, (int64_t)nseg * cap);
+  // Rows the K/V tensors hold: capacity-strided segments, or the stated size of a packed cache.
+  const int64_t kv_rows = seg_start != nullptr ? (cap > 0 ? cap : 0) : (int64_t)nseg * cap;
+  const bool tc = use_tensor_core_path(head_dim, kv_dtype, G, kv_rows);
   if (q_tokens > 1 && !tc)
-    return fail(TKV_ERR_UNSUPPORTED, "%s: several query tokens need bf16/f16, head_dim 128 and the capacity-strided layout", who);
+    return fail(TKV_ERR_UNSUPPORTED, "%s: several query tokens need bf16/f16, head_dim 128 and K/V tensors of stated size", who);
   p.chunk = tc ? attn_tc_chunk_tokens() : attn_chunk_tokens(nseg, max_len);
   p.nchunks = (max_len + p.chunk - 1) / p.chunk;
   p.q_tokens = q_tokens; p.rows = q_tokens * G; p.q_st = q_st;
@@ -512,8 +508,8 @@ static int decode_attn_impl(const char* who, const void* q, int64_t q_sb, int64_
       if (rc != TKV_OK) return rc;
     }
   }
-  int rc = (q_tokens > 1 && p.rows > 16) ? launch_multi_attn_tc(p, nseg, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream)
-                                         : launch_decode_attn_tc(p, nseg, G, kv_dtype, (int64_t)nseg * cap, (cudaStream_t)stream);
+  int rc = (q_tokens > 1 && p.rows > 16) ? launch_multi_attn_tc(p, nseg, kv_dtype, kv_rows, (cudaStream_t)stream)
+                                         : launch_decode_attn_tc(p, nseg, G, kv_dtype, kv_rows, (cudaStream_t)stream);
   if (rc != TKV_OK) return rc;
   return launch_decode_attn_combine(p, nseg, G, head_dim, kv_dtype, (cudaStream_t)stream, push);
 }
@@ -610,7 +606,9 @@ extern "C" int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int worl
 // loads the library holds these TKV_STATIC_SCRATCH_BYTES until the process exits.
 //
 // The array's name is only a host-side handle in host code; the kernels need its device address, which is
-// looked up once per device with cudaGetSymbolAddress while that device is current.
+// looked up once per device with cudaGetSymbolAddress while that device is current.  The address is remembered per
+// device ordinal for the life of the process: a host that calls cudaDeviceReset (or otherwise replaces the device's
+// primary context) must not call this entry point afterwards, since the remembered address belongs to the old context.
 static __device__ __align__(256) unsigned char g_attn_scratch[TKV_STATIC_SCRATCH_BYTES];
 
 namespace tkv {
@@ -636,7 +634,11 @@ extern "C" int tkv_decode_attn_static(const void* q, int64_t q_sb, int64_t q_sh,
   if ((q_sb * 2) % 16 || (q_sh * 2) % 16)
     return fail(TKV_ERR_ARG, "tkv_decode_attn_static: q strides must be multiples of 16 bytes");
   if (batch == 0) return TKV_OK;
-  const size_t need = tkv_decode_attn_workspace_bytes(batch, hq, hkv, head_dim, max_len);
+  // This entry point always runs the CUDA-core split kernel, so the scratch is sized by that kernel's chunk length
+  // alone (tkv_decode_attn_workspace_bytes also covers the tensor-core kernel's shorter chunks).
+  const int static_chunk = attn_chunk_tokens(batch * hkv, max_len);
+  const size_t need = (size_t)((int64_t)batch * hkv * ((max_len + static_chunk - 1) / static_chunk) * (hq / hkv) *
+                               (head_dim + 2) * sizeof(float) + 256);
   if (need > (size_t)TKV_STATIC_SCRATCH_BYTES)
     return fail(TKV_ERR_UNSUPPORTED,
                 "tkv_decode_attn_static: this problem needs %zu bytes of scratch but the built-in array holds %zu; "

@@ -192,6 +192,15 @@ class GreedyDecoder:
         ops.launch_count = before
         self._restore(snap)
 
+    def release_graph(self) -> None:
+        """Destroys the captured decode graph (the next ``step`` captures again).  Needed before a process group whose
+        collectives the graph recorded is destroyed: the communicator's destruction waits for every graph that
+        captured its work."""
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph.reset()
+            self.graph = None
+
     def step(self, ids: Optional[torch.Tensor] = None, eager: bool = False) -> torch.Tensor:
         if ids is not None:
             self.ids.copy_(ids, non_blocking=True)

@@ -135,13 +135,17 @@ def decode_attn_workspace_bytes_ragged(batch: int, hq: int, hkv: int, head_dim: 
 
 
 def decode_attn(q, k_cache, v_cache, seg_len, seg_start, cap: int, out, workspace, hkv: int, scale: float,
-                max_len: int, status=None, total_len_bound=None) -> None:
+                max_len: int, status=None, total_len_bound=None, packed_rows=None) -> None:
     """q ``[B,Hq,D]`` (any batch/head strides), out ``[B,Hq,D]`` contiguous, workspace uint8.
     ``total_len_bound``: host-known bound on ``seg_len.sum()`` for ragged lengths (sizes the grid by tokens instead of
-    by ``max_len``); the workspace must then have ``decode_attn_workspace_bytes_ragged`` bytes."""
+    by ``max_len``); the workspace must then have ``decode_attn_workspace_bytes_ragged`` bytes.
+    With ``seg_start`` (packed ``[sum n, D]`` K/V) the C entry point takes the packed row count in place of ``cap``:
+    ``packed_rows`` (default: the K tensor's first dimension; 0 = not stated, which selects the CUDA-core kernel)."""
     b, hq, d = q.shape
     if q.stride(2) != 1:
         q = q.contiguous()
+    if seg_start is not None:
+        cap = int(packed_rows) if packed_rows is not None else (k_cache.shape[0] if k_cache.dim() == 2 else 0)
     if total_len_bound is not None:
         rc = lib().tkv_decode_attn_ragged(
             q.data_ptr(), q.stride(0), q.stride(1), k_cache.data_ptr(), v_cache.data_ptr(),
