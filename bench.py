@@ -168,7 +168,7 @@ def shutdown_process_group(decoder=None, limit_s: float = 60.0):
     watchdog bounds the wait and turns a teardown that does not return into exit code 3 instead of a silent stall."""
     import torch.distributed as dist
     if decoder is not None:
-        decoder.release_graph()
+        decoder.close()
     torch.cuda.synchronize()
     dist.barrier()
     torch.cuda.synchronize()
@@ -340,6 +340,35 @@ def run_micro(args):
     times = []
     ws = ops.evict_multi_workspace(nseg, M, args.ctas, dev) if args.ctas > 1 else None
     res["ctas_per_segment"] = args.ctas
+    if args.micro == "prefill":
+        # One layer of the prompt pass: batch x S new tokens, dense causal attention over their own K/V (no cache yet),
+        # the query-resident kernel beside the library attention.  --nseg = batch * 8 KV heads, --M = S.
+        from trimkv_b200.attn import _dense_causal
+        batch, hq, hkv, S = nseg // 8, 16, 8, M
+        k = torch.randn(batch, hkv, S, D, generator=g, device=dev, dtype=torch.bfloat16)
+        v = torch.randn(batch, hkv, S, D, generator=g, device=dev, dtype=torch.bfloat16)
+        qh = torch.randn(batch, hq, S, D, generator=g, device=dev, dtype=torch.bfloat16)
+        out = torch.empty(batch, S, hq, D, device=dev, dtype=torch.bfloat16)
+
+        def avg_ms(fn):
+            for _ in range(args.warmup):
+                fn()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize(); e0.record()
+            for _ in range(args.steps):
+                fn()
+            e1.record(); torch.cuda.synchronize()
+            return e0.elapsed_time(e1) / args.steps
+        ours = avg_ms(lambda: ops.prefill_attn(qh.transpose(1, 2), k, v, None, S, out, hkv, D ** -0.5, S))
+        lib_ms = avg_ms(lambda: _dense_causal(qh, k, v, D ** -0.5))
+        flops = 4.0 * batch * hq * D * S * (S + 1) / 2
+        diff = float((_dense_causal(qh, k, v, D ** -0.5).float() - out.float()).abs().max())
+        res.update({"config": {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16", "prompt_tokens": S},
+                    "causal_flops": flops, "avg_ms": ours, "tflops": flops / (ours * 1e-3) / 1e12,
+                    "library_causal_ms": lib_ms, "library_tflops": flops / (lib_ms * 1e-3) / 1e12,
+                    "max_abs_diff_vs_library": diff})
+        print(json.dumps(res))
+        return
     if args.micro == "multi":
         from trimkv_b200.attn import _dense_causal, _ragged_causal
         batch, hq, hkv, Q = nseg // 8, 16, 8, args.q_tokens
@@ -362,6 +391,10 @@ def run_micro(args):
             e1.record(); torch.cuda.synchronize()
             return e0.elapsed_time(e1) / args.steps
         ours = avg_ms(lambda: ops.decode_attn_multi(q, k, v, lens, cap, out, hkv, D ** -0.5, n, workspace=wsm))
+        out_pf = torch.empty_like(out)
+        resident = avg_ms(lambda: ops.prefill_attn(q, k, v, lens, cap, out_pf, hkv, D ** -0.5, n))
+        res.update({"query_resident_ms": resident, "query_resident_kv_gbs": nseg * n * 4 * D / (resident * 1e-3) / 1e9,
+                    "max_abs_diff_resident_vs_split": float((out_pf.float() - out.float()).abs().max())})
         res.update({"config": {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16", "q_tokens": Q,
                                "query_rows_per_segment": Q * hq // hkv, "cached_tokens": n},
                     "kv_bytes": nseg * n * 4 * D, "avg_ms": ours,
@@ -485,7 +518,7 @@ def run_micro(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi"],
+    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi", "prefill"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)
@@ -650,6 +683,9 @@ def main():
         for _ in range(4):
             tkv_attn.event_log = []
             lens_at_sample.append(cache.get_cache_length(0) + 1)
+            # Keep the GPU busy for a few milliseconds first so that the host queues the step's launches ahead of it;
+            # otherwise the event pairs would also time the host's dispatch gaps between the two attention kernels.
+            torch.cuda._sleep(20_000_000)
             dec.step(eager=True)
             attn_events.append(tkv_attn.event_log)
             tkv_attn.event_log = None
@@ -710,6 +746,12 @@ def main():
             append_micro = micro_cache_phase("append", 4096, 2048, 50, 10, 1, want_cpu, dev)
         append_micro["note"] = "2 MB per launch: bound by launch latency, not by bandwidth"
 
+    # The window holds one eviction per `steps` steps although it fires once per B steps: the same measurement with
+    # the eviction's share scaled to its true rate, for comparison with longer windows.
+    ev1_ms = sum(a.elapsed_time(b) for a, b, _ in evict_events[:len(evict_events) - len(evict_events2)])
+    steady_ms = (ms_total - ev1_ms) / args.steps + ev1_ms / max(1, len(evict_events) - len(evict_events2)) / Bf \
+        if len(evict_events) > len(evict_events2) else ms_total / args.steps
+
     cpu = None
     if want_cpu:
         cores = host_threads()
@@ -732,6 +774,7 @@ def main():
                        "untimed_steps_before_windows": [pre1, pre2],
                        "evictions_in_windows": len(evict_events),
                        "l2": "per-step working set (all weights + every cached K/V row, many GB) exceeds the 126 MB L2; no explicit flush"},
+            "ms_per_step_at_true_eviction_rate": steady_ms,
             "roofline": roofline, "evict": evict, "evict_micro": evict_micro, "append": append_micro, "cpu_baseline": cpu,
             "e2e": {"value": e2e, "unit": "tok/s", "ms_per_step": ms_e2e / args.steps,
                     "h2d_bytes_per_step": B * 8 * world, "d2h_bytes_per_step": B * 8 * world},

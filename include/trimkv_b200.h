@@ -307,6 +307,24 @@ int tkv_peer_wait(const int32_t* flags, int32_t* sync_state, int world, int rank
 /* Lets kernels of the current device store to memory of peer_device (cudaDeviceEnablePeerAccess; a no-op if it is
  * already enabled or peer_device is the current device).  Needed once per peer before tkv_decode_attn_push. */
 int tkv_enable_peer_access(int peer_device);
+/*
+ * Many query tokens per request (a prompt pass, a piece of a chunked prefill) against the cache that already
+ * holds them: what flash_attn_varlen_func(causal=True) computes for the reference when Q > 1
+ * (src/trimkv/attn/flash_attn.py:118-145; for the dense prompt pass, the causal attention of
+ * src/trimkv/attn/__init__.py:15-26).  Same semantics as tkv_decode_attn_multi (segment s holds seg_len[s] tokens
+ * including the q_tokens new ones; query token i sees the first seg_len - q_tokens + i + 1 of them), different
+ * kernel: a block of 128 query rows (token, head) stays resident in shared memory and the segment's K/V are
+ * streamed past it once with an online softmax, so the work per cached token does not grow with q_tokens / 128
+ * re-reads and no workspace or merge step is needed.
+ * q: [batch, q_tokens, hq, D] with element strides (q_sb, q_st, q_sh); out: [batch, q_tokens, hq, D] contiguous.
+ * k_cache / v_cache: capacity-strided [batch*hkv, cap, D]; a dense prompt [batch, hkv, S, D] is the case cap = S.
+ * seg_len: NULL = every segment holds max_len tokens.  Requires bf16/f16 and head_dim 128.
+ */
+int tkv_prefill_attn(const void* q, int64_t q_sb, int64_t q_st, int64_t q_sh,
+                     const void* k_cache, const void* v_cache, const int32_t* seg_len, int64_t cap,
+                     void* out, int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                     float scale, int max_len, int q_tokens, int32_t* status, tkv_stream_t stream);
+
 /* Sharing a device allocation between the rank processes of one box (CUDA IPC; host-only calls, no kernel).
  * tkv_ipc_export: handle (TKV_IPC_HANDLE_BYTES bytes) of the allocation that contains ptr, and ptr's offset in it.
  * tkv_ipc_import: maps an exported allocation into this process with the CURRENT device (peer access to the owning

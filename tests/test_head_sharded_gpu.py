@@ -62,7 +62,7 @@ def _worker(rank, world, port, q):
                                                  cache.kv_positions[0][:, :, :n].cpu().numpy(), n)  # by value
                     # The captured step holds the communicator's collectives; the communicator can only be
                     # destroyed once no such graph is left.
-                    dec.release_graph()
+                    dec.close()
                     del dec
                     torch.cuda.synchronize()
                     dist.barrier()

@@ -586,3 +586,63 @@ def test_push_exchange_two_ranks_emulated_on_one_gpu(ops):
             assert int(flags[rank][peer]) == call + 1 and int(flags[rank][rank]) == 0   # a rank raises flags on peers only
             assert sync[rank].tolist() == [0, call + 1, call + 1]
             assert np.abs(gathered[rank].float().cpu().numpy() - want).max() <= 2e-2, (call, rank)
+
+
+# ---------------------------------------------------------------- query-resident attention (many query tokens)
+@pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 5e-3)])
+@pytest.mark.parametrize("bsz,hq,hkv,cap,ql,lens_spec", [
+    (2, 4, 2, 700, 40, "ragged"),        # 80 query rows: one block, padded
+    (2, 4, 2, 900, 100, "ragged"),       # 200 rows: two blocks, the second partly filled
+    (1, 8, 2, 300, 300, "dense"),        # a prompt pass: seg_len NULL, every token is new, 1200 rows
+    (3, 2, 2, 260, 64, "first"),         # G = 1; one segment holds nothing but the new tokens
+    (1, 16, 8, 1500, 8, "ragged"),       # 16 rows against long segments: many tiles, few rescales
+])
+def test_prefill_attention_vs_oracle(ops, dtype, tol, bsz, hq, hkv, cap, ql, lens_spec):
+    d = 128
+    gen = torch.Generator().manual_seed(41)
+    nseg = bsz * hkv
+    if lens_spec == "dense":
+        lens = [cap] * nseg
+    else:
+        lens = [int(x) for x in torch.randint(ql, cap + 1, (nseg,), generator=gen)]
+        lens[-1] = cap
+        if lens_spec == "first":
+            lens[0] = ql
+    q = (torch.randn(bsz, ql, hq, d, generator=gen) * 1.5).to(dtype).to(DEV)
+    k = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(nseg, cap, d, generator=gen).to(dtype).to(DEV)
+    for s_, n in enumerate(lens):            # rows beyond a segment's length hold garbage that must not leak
+        k[s_, n:] = float("nan")
+        v[s_, n:] = float("inf")
+    ln = None if lens_spec == "dense" else torch.tensor(lens, dtype=torch.int32, device=DEV)
+    out = torch.full((bsz, ql, hq, d), float("nan"), dtype=dtype, device=DEV)
+    status = ops.new_status(DEV)
+    ops.prefill_attn(q, k, v, ln, cap, out, hkv, d ** -0.5, cap, status)
+    assert ops.read_status(status) == 0
+    kp = torch.cat([k[s_, :n] for s_, n in enumerate(lens)]).float().cpu().numpy()
+    vp = torch.cat([v[s_, :n] for s_, n in enumerate(lens)]).float().cpu().numpy()
+    cu = np.concatenate([[0], np.cumsum(lens)]).astype(np.int32)
+    want = orc.varlen_gqa_attention(q.float().cpu().numpy().transpose(0, 2, 1, 3), kp, vp, cu, bsz, hkv)
+    got = out.float().cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() <= tol
+
+
+def test_prefill_attention_strided_queries_and_multi_token_kernels_agree(ops):
+    """The query tensor as the model hands it over ([B,Hq,Q,D] transposed to token-major strides), and the same
+    problem through tkv_decode_attn_multi (32 rows per CTA, split-KV partials): two kernels, one result."""
+    gen = torch.Generator().manual_seed(43)
+    bsz, hq, hkv, d, cap, ql = 2, 4, 2, 128, 1100, 16
+    nseg = bsz * hkv
+    lens = torch.randint(ql, cap + 1, (nseg,), generator=gen).to(torch.int32)
+    q = torch.randn(bsz, hq, ql, d, generator=gen).bfloat16().to(DEV).transpose(1, 2)      # [B,Q,Hq,D] view
+    k = torch.randn(nseg * cap, d, generator=gen).bfloat16().to(DEV)
+    v = torch.randn(nseg * cap, d, generator=gen).bfloat16().to(DEV)
+    ln = lens.to(DEV)
+    a = torch.empty(bsz, ql, hq, d, dtype=torch.bfloat16, device=DEV)
+    b_ = torch.empty_like(a)
+    status = ops.new_status(DEV)
+    ops.prefill_attn(q, k, v, ln, cap, a, hkv, d ** -0.5, cap, status)
+    ops.decode_attn_multi(q, k, v, ln, cap, b_, hkv, d ** -0.5, cap, status=status)
+    assert ops.read_status(status) == 0
+    assert float((a.float() - b_.float()).abs().max()) <= 2e-2

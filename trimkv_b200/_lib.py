@@ -43,6 +43,7 @@ SIGNATURES = {
     "tkv_ipc_close": (I, [P]),
     "tkv_decode_attn_multi_workspace_bytes": (c_size_t, [I, I, I, I, I, I]),
     "tkv_decode_attn_multi": (I, [P, L, L, L, P, P, P, L, P, P, c_size_t, I, I, I, I, I, F, I, I, P, P]),
+    "tkv_prefill_attn": (I, [P, L, L, L, P, P, P, L, P, I, I, I, I, I, F, I, I, P, P]),
     "tkv_decode_attn_static": (I, [P, L, L, P, P, P, P, L, P, I, I, I, I, I, F, I, P, P]),
     "tkv_decode_prep": (I, [P, L, P, P, F, P, P, P, P, I, P, P, P, P, P, P, P, P, L, I, I, I, I, I, I, P, P, P]),
     "tkv_add_rmsnorm": (I, [P, P, P, P, I, I, F, I, I, P, P]),

@@ -8,7 +8,7 @@ import subprocess
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libtrimkv_b200.so")
-SOURCES = ["tkv_abi.cu", "tkv_append.cu", "tkv_evict.cu", "tkv_attn.cu", "tkv_attn_tc.cu", "tkv_attn_multi.cu", "tkv_gemm_tc.cu", "tkv_fused.cu"]
+SOURCES = ["tkv_abi.cu", "tkv_append.cu", "tkv_evict.cu", "tkv_attn.cu", "tkv_attn_tc.cu", "tkv_attn_multi.cu", "tkv_attn_prefill.cu", "tkv_gemm_tc.cu", "tkv_fused.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC", "--use_fast_math=false",

@@ -1,0 +1,402 @@
+// Query-resident varlen GQA attention for many query tokens per request (prompt passes, pieces of a chunked
+// prefill) on tcgen05 + TMEM, K/V streamed once per query block by TMA with an online softmax.
+//
+// What flash_attn_varlen_func(causal=True) computes for the reference when Q > 1
+// (src/trimkv/attn/flash_attn.py:118-145): segment s = (request, KV head) holds seg_len[s] cached tokens including the
+// q_tokens new ones; query row R = token * G + head of the segment sees its first seg_len - q_tokens + token + 1
+// tokens (bottom-right aligned causal mask).
+//
+// One CTA = (segment, block of 128 query rows).  The 128 rows sit on the MMA's M dimension, one TMEM lane and one
+// thread per row, so the softmax never crosses threads:
+//   S[128 rows x 128 tokens]  = Q[128 x 128 dims] . K_tile^T     A = Q (smem, K-major, 128B swizzle, staged once),
+//                                                                B = K tile as TMA wrote it; D in TMEM, two buffers
+//   row max / exp2 / sum      thread = row, tcgen05.ld 32 columns at a time; P rounded to the K/V dtype into smem
+//   O[128 rows x 128 dims]   += P[128 x 128 tokens] . V_tile      A = P (smem, K-major, 128B swizzle), B = V tile read
+//                                                                MN-major from the bytes TMA wrote; D in TMEM
+// O is rescaled in TMEM only when a row's maximum grew by more than 2^8 since the reference maximum was fixed (the
+// weights stay below 2^8 meanwhile, well inside fp32 / bf16 range), which after the first tiles is rare.  S of tile
+// j+1 is issued before the softmax of tile j starts and P.V of tile j runs under the first half of the softmax of
+// tile j+1, K tiles are requested two ahead and V tiles one ahead (two 32 KB stages each).  No workspace, no merge
+// kernel.  Every mbarrier wait is bounded; on expiry the CTA records TKV_DEV_TIMEOUT, drains its copies, frees its
+// TMEM and returns.
+#include <cuda.h>
+#include "tkv_common.cuh"
+#include "tkv_attn.cuh"
+#include "tkv_tc.cuh"
+
+namespace tkv {
+
+constexpr int kPfThreads = 128;
+constexpr int kPfTile = 128;                  // query rows per CTA, cached tokens per tile
+constexpr int kPfTileBytes = 32768;           // 128 rows x 256 B, as two 64-element halves of 16 KB
+constexpr int kPfHalf = 16384;
+constexpr int kPfTmemCols = 512;              // S buffers at columns 0 and 128, O at 256
+constexpr float kPfRescaleGap = 8.0f;         // log2 of the largest weight tolerated before O is rescaled
+
+struct PfSmem {
+  uint64_t bar_k[2], bar_v[2], bar_s[2], bar_o;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int kPfSmemBytes = 6 * kPfTileBytes + (int)sizeof(PfSmem) + 1024;
+
+__device__ __forceinline__ uint32_t pf_idesc(int fmt /*0 f16, 1 bf16*/, int b_mn_major) {
+  // kind::f16, D = f32, M = 128, N = 128, A K-major, B K-major or MN-major
+  return (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)b_mn_major << 16) | ((128u >> 3) << 17) |
+         ((128u >> 4) << 24);
+}
+
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+      "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+        "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])),
+        "r"(__float_as_uint(v[19])), "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])),
+        "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])),
+        "r"(__float_as_uint(v[31]))
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+template <int kDtype>
+__device__ __forceinline__ uint32_t pf_pack2(float a, float b, float& sum) {
+  if (kDtype == TKV_BF16) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    sum += __low2float(v) + __high2float(v);
+    return *reinterpret_cast<const uint32_t*>(&v);
+  }
+  const __half2 v = __floats2half2_rn(a, b);
+  sum += __low2float(v) + __high2float(v);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// Byte offset of 16-byte chunk `c` (0..15: 8 elements each) of row `r` in a 128-row K-major tile with 128-byte swizzle,
+// stored as two 64-element halves.
+__device__ __forceinline__ uint32_t pf_swz(int r, int c) {
+  return (uint32_t)((c >> 3) * kPfHalf + r * 128 + (((c & 7) ^ (r & 7)) << 4));
+}
+
+// grid.x = nblocks * nseg with the query blocks in descending order (the last block of a causal pass sees the most
+// tokens, so the longest CTAs start first).
+template <int kDtype>
+__global__ void __launch_bounds__(kPfThreads, 1)
+prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
+                    int nseg, int nblocks) {
+  extern __shared__ uint8_t smem_raw[];
+  grid_dependency_wait();
+  grid_launch_dependents();
+  const int blk = nblocks - 1 - (int)(blockIdx.x / (unsigned)nseg);
+  const int seg = (int)(blockIdx.x % (unsigned)nseg);
+  const int tid = threadIdx.x, warp = tid >> 5;
+  const int G = p.hq / p.hkv;
+  const int b = seg / p.hkv, h = seg - b * p.hkv;
+  int len = p.seg_len != nullptr ? p.seg_len[seg] : p.max_len;
+  if (p.seg_len != nullptr && len > p.max_len) {
+    if (tid == 0 && blk == 0) report(p.status, TKV_DEV_LEN_BOUND);
+    len = p.max_len;
+  }
+  const int R = blk * kPfTile + tid;                       // this thread's query row of the segment
+  const bool row_valid = R < p.rows;
+  const int token = R / G, head = h * G + (R - token * G);
+  // cached tokens this row may see, and the most any row of this CTA may see (CTA-uniform)
+  const int vis = row_valid ? max(0, min(len, len - p.q_tokens + token + 1)) : 0;
+  const int r_last = min(blk * kPfTile + kPfTile - 1, p.rows - 1);
+  const int vis_max = max(0, min(len, len - p.q_tokens + r_last / G + 1));
+  const int ntiles = (vis_max + kPfTile - 1) / kPfTile;
+  char* const out_row = p.out + (((int64_t)b * p.q_tokens + token) * p.hq + head) * 256;
+  if (ntiles == 0) {                                       // nothing visible (an empty segment): zeros
+    if (row_valid)
+      for (int c = 0; c < 16; ++c) st16(out_row + c * 16, make_uint4(0, 0, 0, 0));
+    return;
+  }
+
+  uint8_t* base = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* q_s = base;
+  uint8_t* p_s = base + kPfTileBytes;
+  uint8_t* k_s = base + 2 * kPfTileBytes;                  // two stages
+  uint8_t* v_s = base + 4 * kPfTileBytes;                  // two stages
+  PfSmem* sm = reinterpret_cast<PfSmem*>(base + 6 * kPfTileBytes);
+  volatile int* abort_flag = &sm->abort_flag;
+  const int64_t row0 = (int64_t)seg * p.cap;
+
+  int k_issued = 0, v_issued = 0;                          // thread 0: tiles whose copies have been started
+  if (tid == 0) {
+    for (int i = 0; i < 2; ++i) { mbar_init(&sm->bar_k[i], 1); mbar_init(&sm->bar_v[i], 1); mbar_init(&sm->bar_s[i], 1); }
+    mbar_init(&sm->bar_o, 1);
+    sm->abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    for (int i = 0; i < 2 && i < ntiles; ++i) {
+      mbar_expect_tx(&sm->bar_k[i], kPfTileBytes);
+      tma_load_2d(k_s + i * kPfTileBytes, &map_k, &sm->bar_k[i], 0, (int)(row0 + i * kPfTile));
+      tma_load_2d(k_s + i * kPfTileBytes + kPfHalf, &map_k, &sm->bar_k[i], 64, (int)(row0 + i * kPfTile));
+      ++k_issued;
+    }
+    mbar_expect_tx(&sm->bar_v[0], kPfTileBytes);
+    tma_load_2d(v_s, &map_v, &sm->bar_v[0], 0, (int)row0);
+    tma_load_2d(v_s + kPfHalf, &map_v, &sm->bar_v[0], 64, (int)row0);
+    v_issued = 1;
+  }
+  __syncwarp();
+  if (warp == 0) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kPfTmemCols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+  }
+  // Q block as the A operand: row = query row, K-major with 128-byte swizzle (the layout TMA gives the K tiles).
+  {
+    const char* qp = p.q + ((int64_t)b * p.q_sb + (int64_t)token * p.q_st + (int64_t)head * p.q_sh) * 2;
+#pragma unroll
+    for (int c = 0; c < 16; ++c)
+      st16(q_s + pf_swz(tid, c), row_valid ? ld16(qp + c * 16) : make_uint4(0, 0, 0, 0));
+  }
+  fence_async_smem();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm->tmem_base;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t idesc_s = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 0);
+  const uint32_t idesc_pv = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 1);
+  const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+
+  // S of tile `j` into S buffer j & 1 (thread 0 only).
+  auto issue_s = [&](int j) -> bool {
+    if (!mbar_wait_or_abort(&sm->bar_k[j & 1], (j >> 1) & 1, abort_flag)) return false;
+    tc_fence_after();
+    const uint32_t k_addr = smem_u32(k_s + (j & 1) * kPfTileBytes);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {   // 16 dims per MMA: 4 steps inside a 128-byte swizzle atom, then the other half
+      const uint32_t off = (k >> 2) * kPfHalf + (k & 3) * 32;
+      umma(tmem + 128 * (j & 1), make_desc(q_addr + off, 16, 1024, 2), make_desc(k_addr + off, 16, 1024, 2), idesc_s, k > 0);
+    }
+    umma_commit(&sm->bar_s[j & 1]);
+    return true;
+  };
+
+  if (tid == 0 && !issue_s(0)) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+  __syncwarp();
+
+  float m_ref = -INFINITY, l_sum = 0.f;     // reference maximum of this row (log2 domain) and its weight sum
+  int done_tiles = 0;
+  for (int j = 0; j < ntiles; ++j) {
+    const int sb = j & 1;
+    const int t0 = j * kPfTile;
+    // ---- S of this tile
+    bool ok = mbar_wait_or_abort(&sm->bar_s[sb], (j >> 1) & 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) { if (*abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); } }
+    tc_fence_after();
+    if (tid == 0 && ok) {
+      // the tensor core works on the next tile's S while this tile's softmax runs; K stage `sb` is free again
+      if (j + 1 < ntiles && !issue_s(j + 1)) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+      if (j + 2 < ntiles && *abort_flag == 0) {
+        mbar_expect_tx(&sm->bar_k[sb], kPfTileBytes);
+        tma_load_2d(k_s + sb * kPfTileBytes, &map_k, &sm->bar_k[sb], 0, (int)(row0 + (j + 2) * kPfTile));
+        tma_load_2d(k_s + sb * kPfTileBytes + kPfHalf, &map_k, &sm->bar_k[sb], 64, (int)(row0 + (j + 2) * kPfTile));
+        ++k_issued;
+      }
+    }
+    __syncwarp();
+    const int limit = vis - t0;             // columns of this tile the row may see (<= 0: none, >= 128: all)
+    const uint32_t s_addr = lane_base + 128 * sb;
+    float m_tile = -INFINITY;
+    if (ok) {
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        float v[32];
+        tmem_ld32(s_addr + c4 * 32, v);
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c4 * 32 + i < limit) m_tile = fmaxf(m_tile, v[i] * p.scale_log2);
+      }
+    }
+    const bool grow = m_tile > m_ref + kPfRescaleGap || (m_ref == -INFINITY && m_tile > -INFINITY);
+    const bool rescale = __any_sync(0xffffffffu, grow);
+    // ---- P.V of the previous tile must be complete before O, the P buffer or its V stage are touched
+    if (j > 0) {
+      bool ok2 = mbar_wait_or_abort(&sm->bar_o, (j - 1) & 1, abort_flag);
+      ok2 = __all_sync(0xffffffffu, ok2);
+      if (!ok2 && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+      ok = ok && ok2;
+      tc_fence_after();
+    }
+    if (tid == 0 && ok && j + 1 < ntiles) {
+      const int vs = (j + 1) & 1;
+      mbar_expect_tx(&sm->bar_v[vs], kPfTileBytes);
+      tma_load_2d(v_s + vs * kPfTileBytes, &map_v, &sm->bar_v[vs], 0, (int)(row0 + (j + 1) * kPfTile));
+      tma_load_2d(v_s + vs * kPfTileBytes + kPfHalf, &map_v, &sm->bar_v[vs], 64, (int)(row0 + (j + 1) * kPfTile));
+      ++v_issued;
+    }
+    __syncwarp();
+    if (ok && rescale) {
+      const float m_new = fmaxf(m_ref, m_tile);
+      if (j > 0) {
+        const float alpha = (m_ref == -INFINITY) ? 1.0f : exp2_weight(m_ref - m_new);   // O of such a row is still zero
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          float o[32];
+          tmem_ld32(lane_base + 256 + c4 * 32, o);
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] *= alpha;
+          tmem_st32(lane_base + 256 + c4 * 32, o);
+        }
+        l_sum *= alpha;
+      }
+      m_ref = m_new;
+    }
+    // ---- P = 2^(s - m_ref), rounded to the K/V dtype; the sum uses the rounded weights
+    if (ok) {
+#pragma unroll
+      for (int c4 = 0; c4 < 4; ++c4) {
+        float v[32];
+        tmem_ld32(s_addr + c4 * 32, v);
+        uint32_t w[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const int col = c4 * 32 + i;
+          const float a = (col < limit) ? exp2_weight(fmaf(v[i], p.scale_log2, -m_ref)) : 0.f;
+          const float bb = (col + 1 < limit) ? exp2_weight(fmaf(v[i + 1], p.scale_log2, -m_ref)) : 0.f;
+          w[i >> 1] = pf_pack2<kDtype>(a, bb, l_sum);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+      }
+      // Rows of the last V tile beyond the segment's length may hold anything (stale rows, another segment): their
+      // weight is zero, but 0 x NaN would poison the product, so they are cleared in shared memory.
+      if (t0 + kPfTile > len) {
+        bool ok3 = mbar_wait_or_abort(&sm->bar_v[sb], (j >> 1) & 1, abort_flag);
+        ok3 = __all_sync(0xffffffffu, ok3);
+        if (!ok3 && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+        ok = ok && ok3;
+        if (ok3 && t0 + tid >= len) {
+          uint8_t* vt = v_s + sb * kPfTileBytes + tid * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) { st16(vt + c * 16, make_uint4(0, 0, 0, 0)); st16(vt + kPfHalf + c * 16, make_uint4(0, 0, 0, 0)); }
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (*abort_flag != 0) break;            // uniform: read after the barrier
+    // ---- O += P . V
+    if (tid == 0) {
+      if (mbar_wait_or_abort(&sm->bar_v[sb], (j >> 1) & 1, abort_flag)) {
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(v_s + sb * kPfTileBytes);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {   // 16 tokens per MMA: along K of P inside the swizzle atom, 2048 B down the V tile
+          const uint64_t ad = make_desc(p_addr + (k >> 2) * kPfHalf + (k & 3) * 32, 16, 1024, 2);
+          const uint64_t bd = make_desc(v_addr + k * 2048, kPfHalf, 1024, 2);
+          umma(tmem + 256, ad, bd, idesc_pv, (j > 0 || k > 0));
+        }
+        umma_commit(&sm->bar_o);
+      } else {
+        *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT);
+      }
+    }
+    __syncwarp();
+    done_tiles = j + 1;
+  }
+  // ---- epilogue: O / sum -> out
+  bool have = done_tiles == ntiles && *abort_flag == 0;
+  have = __all_sync(0xffffffffu, have);
+  if (have) {
+    bool ok = mbar_wait_or_abort(&sm->bar_o, (ntiles - 1) & 1, abort_flag);
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
+    have = ok;
+  }
+  tc_fence_after();
+  if (have) {
+    const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
+#pragma unroll
+    for (int c4 = 0; c4 < 4; ++c4) {
+      float o[32];
+      tmem_ld32(lane_base + 256 + c4 * 32, o);
+      if (row_valid) {
+        uint32_t w[16];
+        float unused = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) w[i >> 1] = pf_pack2<kDtype>(o[i] * inv, o[i + 1] * inv, unused);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          st16(out_row + (c4 * 4 + c) * 16, make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+      }
+    }
+  }
+  // An aborting CTA drains the copies it started before its shared memory is released.
+  if (tid == 0 && *abort_flag != 0) {
+    for (int i = max(0, k_issued - 2); i < k_issued; ++i) mbar_wait(&sm->bar_k[i & 1], (i >> 1) & 1);
+    for (int i = max(0, v_issued - 2); i < v_issued; ++i) mbar_wait(&sm->bar_v[i & 1], (i >> 1) & 1);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols));
+}
+
+template <int kDtype>
+static int launch_prefill(const CUtensorMap& mk, const CUtensorMap& mv, const AttnParams& p, int nseg, int nblocks,
+                          cudaStream_t st) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(prefill_attn_kernel<kDtype>, cudaFuncAttributeMaxDynamicSharedMemorySize, kPfSmemBytes);
+    if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_prefill_attn: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  cudaError_t e = launch_pdl(prefill_attn_kernel<kDtype>, dim3((unsigned)((int64_t)nseg * nblocks)), dim3(kPfThreads),
+                             (size_t)kPfSmemBytes, st, mk, mv, p, nseg, nblocks);
+  if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_prefill_attn: %s", cudaGetErrorString(e));
+  return check_launch("tkv_prefill_attn");
+}
+
+}  // namespace tkv
+
+extern "C" int tkv_prefill_attn(const void* q, int64_t q_sb, int64_t q_st, int64_t q_sh,
+                                const void* k_cache, const void* v_cache, const int32_t* seg_len, int64_t cap,
+                                void* out, int batch, int hq, int hkv, int head_dim, int kv_dtype,
+                                float scale, int max_len, int q_tokens, int32_t* status, tkv_stream_t stream) {
+  using namespace tkv;
+  if (!q || !k_cache || !v_cache || !out) return fail(TKV_ERR_ARG, "tkv_prefill_attn: NULL pointer argument");
+  if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || max_len <= 0 || q_tokens < 1 || cap < max_len)
+    return fail(TKV_ERR_ARG, "tkv_prefill_attn: bad sizes batch=%d hq=%d hkv=%d max_len=%d q_tokens=%d cap=%lld", batch, hq,
+                hkv, max_len, q_tokens, (long long)cap);
+  if (head_dim != 128 || (kv_dtype != TKV_BF16 && kv_dtype != TKV_F16))
+    return fail(TKV_ERR_UNSUPPORTED, "tkv_prefill_attn: head_dim=%d dtype=%d (supported: 128, bf16/f16)", head_dim, kv_dtype);
+  if (!aligned16(q) || !aligned16(k_cache) || !aligned16(v_cache) || !aligned16(out))
+    return fail(TKV_ERR_ARG, "tkv_prefill_attn: pointers must be 16-byte aligned");
+  if ((q_sb * 2) % 16 || (q_st * 2) % 16 || (q_sh * 2) % 16)
+    return fail(TKV_ERR_ARG, "tkv_prefill_attn: q strides must be multiples of 16 bytes");
+  if (batch == 0) return TKV_OK;
+  const int nseg = batch * hkv, G = hq / hkv;
+  const int64_t rows = (int64_t)q_tokens * G;
+  const int64_t nblocks = (rows + kPfTile - 1) / kPfTile;
+  if ((int64_t)nseg * nblocks > INT32_MAX || (int64_t)nseg * cap < kPfTile || (int64_t)nseg * cap + kPfTile > INT32_MAX)
+    return fail(TKV_ERR_UNSUPPORTED, "tkv_prefill_attn: %lld query blocks x %d segments, %lld cache rows", (long long)nblocks,
+                nseg, (long long)nseg * cap);
+  AttnParams p;
+  p.q = (const char*)q; p.q_sb = q_sb; p.q_sh = q_sh; p.q_st = q_st;
+  p.k = (const char*)k_cache; p.v = (const char*)v_cache;
+  p.seg_len = seg_len; p.seg_start = nullptr; p.cap = cap;
+  p.out = (char*)out;
+  p.part_ml = nullptr; p.part_o = nullptr; p.chunk = kPfTile; p.nchunks = 0;
+  p.hq = hq; p.hkv = hkv; p.max_len = max_len;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.status = status;
+  p.work = nullptr; p.work_count = nullptr; p.work_capacity = 0;
+  p.q_tokens = q_tokens; p.rows = (int)rows;
+  if (rows > INT32_MAX) return fail(TKV_ERR_UNSUPPORTED, "tkv_prefill_attn: too many query rows per segment");
+  CUtensorMap mk, mv;
+  int rc = make_map_2d(&mk, k_cache, 128, (int64_t)nseg * cap, 64, 128, kv_dtype);
+  if (rc != TKV_OK) return rc;
+  rc = make_map_2d(&mv, v_cache, 128, (int64_t)nseg * cap, 64, 128, kv_dtype);
+  if (rc != TKV_OK) return rc;
+  return kv_dtype == TKV_BF16 ? launch_prefill<TKV_BF16>(mk, mv, p, nseg, (int)nblocks, (cudaStream_t)stream)
+                              : launch_prefill<TKV_F16>(mk, mv, p, nseg, (int)nblocks, (cudaStream_t)stream);
+}

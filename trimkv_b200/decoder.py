@@ -201,6 +201,13 @@ class GreedyDecoder:
             self.graph.reset()
             self.graph = None
 
+    def close(self) -> None:
+        """Releases what ties this decoder to other ranks: the captured graph and, in the head-sharded mode that
+        pushes over NVLink, the mappings of the peers' exchange blocks (collective: every rank calls it)."""
+        self.release_graph()
+        if hasattr(self.fused, "close"):
+            self.fused.close()
+
     def step(self, ids: Optional[torch.Tensor] = None, eager: bool = False) -> torch.Tensor:
         if ids is not None:
             self.ids.copy_(ids, non_blocking=True)
@@ -261,6 +268,11 @@ class HeadShardedDecodeStep(FusedDecodeStep):
                 h0 = self.rank * self.hkv_l
                 self.local.append((w[rows].contiguous(), None if bias is None else bias[rows].contiguous(),
                                    g.linear2.weight[h0:h0 + self.hkv_l].contiguous(), g.bias[h0:h0 + self.hkv_l].contiguous()))
+
+    def close(self) -> None:
+        if self._xchg is not None:
+            self._xchg.close()
+            self._xchg = None
 
     def _attend_and_push(self, l, q_out, k, v, kw, scaling):
         """Attention of this rank's heads, merged straight into every rank's gathered buffer; returns the local one

@@ -180,6 +180,20 @@ def decode_attn_multi(q, k_cache, v_cache, seg_len, cap: int, out, hkv: int, sca
     _count(2)
 
 
+def prefill_attn(q, k_cache, v_cache, seg_len, cap: int, out, hkv: int, scale: float, max_len: int, status=None):
+    """q ``[B,Q,Hq,D]`` (any batch/token/head strides) against capacity-strided caches that already hold the Q new
+    tokens (``seg_len`` None: every segment holds ``max_len`` tokens, e.g. a dense prompt with ``cap`` = S); out
+    ``[B,Q,Hq,D]`` contiguous; bottom-right aligned causal mask per segment.  Query-resident kernel, no workspace."""
+    b, ql, hq, d = q.shape
+    if q.stride(3) != 1:
+        q = q.contiguous()
+    rc = lib().tkv_prefill_attn(
+        q.data_ptr(), q.stride(0), q.stride(1), q.stride(2), k_cache.data_ptr(), v_cache.data_ptr(), _ptr(seg_len), cap,
+        out.data_ptr(), b, hq, hkv, d, dtype_code(k_cache.dtype), float(scale), max_len, ql, _ptr(status), _stream(q))
+    check(rc, "tkv_prefill_attn")
+    _count(1)
+
+
 def decode_attn_push(q, k_cache, v_cache, seg_len, cap: int, out, workspace, hkv: int, scale: float, max_len: int,
                      peer_out, peer_flags, world: int, rank: int, row_stride: int, col_offset: int, sync_state,
                      status=None) -> None:
@@ -209,18 +223,33 @@ def ipc_export(t: torch.Tensor):
     return handle.raw, int(off.value)
 
 
-_ipc_bases = {}   # (device, handle) -> base address: an allocation is mapped once per process and device
+_ipc_bases = {}   # (device, handle) -> [base address, users]: an allocation is mapped once per process and device
 
 
 def ipc_import(handle: bytes) -> int:
-    """Maps an exported allocation with the current device; returns its base address in this process."""
+    """Maps an exported allocation with the current device; returns its base address in this process.  A handle that
+    is already mapped is not opened again (one mapping per handle and process); ``ipc_release`` undoes one import."""
     import ctypes
     key = (torch.cuda.current_device(), handle)
     if key not in _ipc_bases:
         base = ctypes.c_void_p(0)
         check(lib().tkv_ipc_import(ctypes.create_string_buffer(handle, 64), ctypes.byref(base)), "tkv_ipc_import")
-        _ipc_bases[key] = int(base.value)
-    return _ipc_bases[key]
+        _ipc_bases[key] = [int(base.value), 0]
+    _ipc_bases[key][1] += 1
+    return _ipc_bases[key][0]
+
+
+def ipc_release(handle: bytes) -> None:
+    """Drops one user of an imported allocation; the mapping is closed when the last one is gone."""
+    import ctypes
+    key = (torch.cuda.current_device(), handle)
+    entry = _ipc_bases.get(key)
+    if entry is None:
+        return
+    entry[1] -= 1
+    if entry[1] <= 0:
+        del _ipc_bases[key]
+        check(lib().tkv_ipc_close(ctypes.c_void_p(entry[0])), "tkv_ipc_close")
 
 
 def peer_wait(flags, sync_state, world: int, rank: int, status=None, max_polls: int = 0) -> None:

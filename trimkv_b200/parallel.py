@@ -83,21 +83,47 @@ class PeerExchange:
         esize = torch.empty((), dtype=dtype).element_size()
         buf_bytes = -(-batch * width * esize // 256) * 256
         flag_off = nbuf * buf_bytes
-        self._block = torch.zeros(flag_off + 256, dtype=torch.uint8, device=device)
+        # The block gets an allocation of its own (a private pool): the IPC handle exports the whole allocation a
+        # pointer lies in, and the peers must be able to write to this block and to nothing else of this process.
+        self._device = torch.device(device)
+        self._pool = torch.cuda.MemPool()
+        with torch.cuda.use_mem_pool(self._pool, device=self._device):
+            self._block = torch.zeros(flag_off + 256, dtype=torch.uint8, device=self._device)
         self.buffers = [self._block[i * buf_bytes: i * buf_bytes + batch * width * esize].view(dtype).view(batch, width)
                         for i in range(nbuf)]
         self.flags = self._block[flag_off: flag_off + 4 * self.world].view(torch.int32)
         self.sync = torch.zeros(3, dtype=torch.int32, device=device)   # CTA counter, exchanges sent, received
         torch.cuda.synchronize(device)
         everyone = [None] * self.world
-        dist.all_gather_object(everyone, ops.ipc_export(self._block), group=group)
-        bases = []
-        with torch.cuda.device(device):
+        try:
+            mine = ops.ipc_export(self._block)
+        except ops._lib.TrimKVNativeError as e:
+            raise RuntimeError("the exchange block could not be exported over CUDA IPC (not supported with the "
+                               "allocator's expandable_segments setting)") from e
+        dist.all_gather_object(everyone, mine, group=group)
+        bases, self._imported = [], []
+        with torch.cuda.device(self._device):
             for r, (handle, offset) in enumerate(everyone):
-                bases.append(self._block.data_ptr() if r == self.rank else ops.ipc_import(handle) + offset)
+                if r == self.rank:
+                    bases.append(self._block.data_ptr())
+                else:
+                    bases.append(ops.ipc_import(handle) + offset)
+                    self._imported.append(handle)
         self.out_ptrs = [(ctypes.c_void_p * self.world)(*[b + i * buf_bytes for b in bases]) for i in range(nbuf)]
         self.flag_ptrs = (ctypes.c_void_p * self.world)(*[b + flag_off for b in bases])
         dist.barrier(group=group)   # nobody pushes before every rank has zeroed and mapped its block
 
     def buffer(self, i: int) -> torch.Tensor:
         return self.buffers[i]
+
+    def close(self) -> None:
+        """Unmaps the peers' blocks.  Collective: every rank calls it once no exchange is in flight (the barrier makes
+        sure nobody unmaps a block a peer is still writing to)."""
+        if getattr(self, "_imported", None) is None:
+            return
+        torch.cuda.synchronize(self._device)
+        dist.barrier(group=self.group)
+        with torch.cuda.device(self._device):
+            for handle in self._imported:
+                ops.ipc_release(handle)
+        self._imported = None
