@@ -372,7 +372,7 @@ def run_micro(args):
     if args.micro == "multi":
         from trimkv_b200.attn import _dense_causal, _ragged_causal
         batch, hq, hkv, Q = nseg // 8, 16, 8, args.q_tokens
-        n, cap = M + Q, M + 256
+        n, cap = M + Q, M + max(256, Q)
         k = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
         v = torch.randn(nseg * cap, D, generator=g, device=dev, dtype=torch.bfloat16)
         lens = torch.full((nseg,), n, device=dev, dtype=torch.int32)
@@ -545,6 +545,8 @@ def main():
                     help="requests per step of the host-core arm (--impl reference; 0 = the full batch if host memory allows)")
     ap.add_argument("--cpu-sample-batch", type=int, default=2, help="requests in the cpu_baseline sample of the native arm")
     ap.add_argument("--cpu-steps", type=int, default=12)
+    ap.add_argument("--no-evict-window", action="store_true",
+                    help="do not advance the cache so that an eviction falls inside the timed windows (profiling runs)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -630,7 +632,7 @@ def main():
             """Untimed steps until the cache is `steps_before_trigger` tokens short of M+B, so that a timed window
             of any length holds an all-layer eviction (it fires once per B steps; a short window would miss it)."""
             n = 0
-            while (M + Bf - cache.get_cache_length(0)) % Bf != steps_before_trigger % Bf and n < Bf:
+            while not args.no_evict_window and (M + Bf - cache.get_cache_length(0)) % Bf != steps_before_trigger % Bf and n < Bf:
                 dec.step(); n += 1
             return n
 

@@ -419,6 +419,17 @@ int tkv_skinny_gemm_splits(int m, int n, int k);
 int tkv_skinny_gemm(const void* x, const void* w, float* partial, int m, int n, int k, int dtype,
                     int32_t* status, tkv_stream_t stream);
 
+/*
+ * tkv_skinny_gemm whose activation operand is computed instead of loaded: x[m, k] = SiLU(gate_up[m, :k]) *
+ * gate_up[m, k:2k], i.e. tkv_silu_mul and the down projection of Qwen3MLP.forward in one kernel
+ * (src/trimkv/models/qwen3/modeling_trimkv_qwen3.py:120-122; Phi-3's gate|up output has the same layout,
+ * src/trimkv/models/phi3/modeling_trimkv_phi3.py:102-108).  gate_up: [m, 2k] row-major, model dtype, as one GEMM
+ * over the concatenated gate/up weights produces it (bias already added).  Same partial-sum output and rounding
+ * (SiLU rounded, product rounded) as the two separate calls.
+ */
+int tkv_skinny_gemm_swiglu(const void* gate_up, const void* w, float* partial, int m, int n, int k, int dtype,
+                           int32_t* status, tkv_stream_t stream);
+
 /* Blocks until `stream` is idle, then returns *status (a TKV_DEV_* code) and clears it. */
 int tkv_read_status(int32_t* status, tkv_stream_t stream);
 

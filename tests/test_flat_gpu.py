@@ -209,15 +209,18 @@ def test_flat_budget_bf16_scores(golden_dir, ci):
     check_flat_bf16_case(g, ci, lens, lambda l: packed[l][3][:, 0].cpu().numpy().astype(np.int32), score_of)
 
 
-@pytest.mark.parametrize("Q", [5, 24, 150])
-def test_multi_token_query_over_ragged_cache(Q):
+@pytest.mark.parametrize("Q,resident_min_ctas", [(5, 96), (24, 96), (150, 96), (24, 1), (150, 1)])
+def test_multi_token_query_over_ragged_cache(Q, resident_min_ctas, monkeypatch):
     """A second prompt (Q > 1) appended to a budget-sharing cache whose heads differ in length: bottom-right aligned
-    causal attention per segment, against the per-segment restatement.  Q = 5 (10 query rows per segment) runs on
-    the decode kernel, Q = 24 (48 rows) on the 32-rows-per-CTA kernel for the ragged cache and through the library's
-    causal attention for the uniform one, Q = 150 through the library attention (with a mask built from the lengths
-    where they differ)."""
-    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, TrimKVCache
+    causal attention per segment, against the per-segment restatement.  With the default routing (8 segments, too few
+    CTAs for the query-resident kernel to be preferred) Q = 5 (10 query rows per segment) runs on the decode kernel,
+    Q = 24 (48 rows) on the 32-rows-per-CTA kernel for the ragged cache and through the library's causal attention for
+    the uniform one, Q = 150 (300 rows) on the query-resident kernel for the ragged cache (the library would need a
+    materialised mask) and through the library for the uniform one; with the CTA threshold lowered to 1 the
+    query-resident kernel serves both caches for Q = 24 and Q = 150."""
+    from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, TrimKVCache, attn as attn_mod
     from trimkv_b200.attn import TRIMKV_ATTENTION_IMPLEMENTATIONS
+    monkeypatch.setattr(attn_mod, "RESIDENT_MIN_CTAS", resident_min_ctas)
     attn = TRIMKV_ATTENTION_IMPLEMENTATIONS["db_attn_flash_batched"]
     gen = torch.Generator().manual_seed(9)
     B, H, G, D, S, M, Bf = 2, 4, 2, 128, 400, 64, 8

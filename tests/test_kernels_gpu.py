@@ -408,6 +408,28 @@ def test_skinny_gemm_partials_sum_to_the_product(ops, m, n, k):
     assert float((got - want).abs().max()) <= 1e-3 * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("m,n,k", [(32, 2048, 6144), (5, 384, 512), (16, 256, 64)])
+def test_skinny_gemm_with_swiglu_prologue(ops, dtype, m, n, k):
+    """SiLU(gate) * up computed inside the GEMM: the activation tile is bit-identical to tkv_silu_mul's output, so the
+    partial sums equal those of tkv_skinny_gemm fed that output, and the sum is the eager product."""
+    gen = torch.Generator().manual_seed(m + n + k)
+    gu = torch.randn(m, 2 * k, generator=gen).to(dtype).to(DEV)
+    w = (torch.randn(n, k, generator=gen) * 0.05).to(dtype).to(DEV)
+    splits = ops.skinny_gemm_splits(m, n, k)
+    status = ops.new_status(DEV)
+    fused = torch.full((splits, m, n), float("nan"), dtype=torch.float32, device=DEV)
+    assert ops.skinny_gemm_swiglu(gu, w, fused, status) == splits
+    act = torch.empty(m, k, dtype=dtype, device=DEV)
+    ops.silu_mul(gu, act)
+    two_step = torch.empty_like(fused)
+    ops.skinny_gemm(act, w, two_step, status)
+    assert ops.read_status(status) == 0
+    assert torch.equal(fused, two_step)
+    eager = (torch.nn.functional.silu(gu[:, :k]) * gu[:, k:]).float() @ w.float().t()
+    assert float((fused.sum(0) - eager).abs().max()) <= 2e-3 * max(1.0, float(eager.abs().max()))
+
+
 def test_consumers_accept_gemm_partials(ops):
     """add_rmsnorm and silu_mul fed with fp32 partials + bias equal the same kernels fed with the rounded sum."""
     gen = torch.Generator().manual_seed(4)

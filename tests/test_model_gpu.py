@@ -190,12 +190,13 @@ def test_generate_matches_cpu_restatement():
     assert mismatched_rows <= 6, mismatched_rows  # of 40 steps x 2 layers x 4 segments
 
 
-@pytest.mark.parametrize("use_graph,tc_gemm", [(False, False), (True, False), (True, True)])
-def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, monkeypatch):
-    """The fused kernels (add+RMSNorm, decode_prep, SiLU*up) against the PyTorch-op layer on the same weights."""
+@pytest.mark.parametrize("use_graph,tc_gemm,fused_down", [(False, False, False), (True, False, False), (True, True, False),
+                                                         (True, False, True)])
+def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, fused_down):
+    """The fused kernels (add+RMSNorm, decode_prep, SiLU*up; optionally the tensor-core GEMMs, or SiLU*up inside the
+    down projection) against the PyTorch-op layer on the same weights."""
     from trimkv_b200 import TrimKVCache
     from trimkv_b200.decoder import GreedyDecoder
-    monkeypatch.setenv("TKV_TC_GEMM", "1" if tc_gemm else "0")
     model, cfg = _tiny(memory_size=64, buffer_size=8, layers=3)
     model = model.to(DEV)
     gen = torch.Generator().manual_seed(9)
@@ -205,7 +206,7 @@ def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, monkeypatch):
         for fused in (False, True):
             cache = TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size)
             out = model(input_ids=prompt, past_key_values=cache, logits_to_keep=1)
-            dec = GreedyDecoder(model, cache, use_graph=use_graph and fused, fused=fused)
+            dec = GreedyDecoder(model, cache, use_graph=use_graph and fused, fused=fused, tc_gemm=tc_gemm, fused_down=fused_down)
             dec.ids.copy_(out.logits[:, -1].argmax(-1, keepdim=True))
             toks, logits = [], []
             forced = torch.randint(0, cfg.vocab_size, (30, 3, 1), generator=torch.Generator().manual_seed(1)).to(DEV)
@@ -265,11 +266,14 @@ def test_flat_budget_cache_through_the_fused_decoder(strategy):
     assert same >= 0.9, same   # a near-tie in bf16 may move a row between heads; the lengths then differ by one
 
 
-def test_chunked_prefill_matches_cpu_restatement():
-    """The prompt fed in pieces (multi-token queries against the cache, eviction after every piece, capacity growing
+@pytest.mark.parametrize("resident_min_ctas", [96, 1])
+def test_chunked_prefill_matches_cpu_restatement(resident_min_ctas, monkeypatch):
+    """(Second parameter value: the query-resident kernel serves every piece instead of the 32-row split-KV kernel or
+    the library.)  The prompt fed in pieces (multi-token queries against the cache, eviction after every piece, capacity growing
     past M+B while a piece is appended): logits of every piece within 2e-2 of the eager CPU path fed the same pieces."""
     from oracle.qwen3_oracle import EagerTrimKVCache, OracleQwen3
-    from trimkv_b200 import TrimKVCache
+    from trimkv_b200 import TrimKVCache, attn as attn_mod
+    monkeypatch.setattr(attn_mod, "RESIDENT_MIN_CTAS", resident_min_ctas)
     torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
     model, cfg = _tiny(memory_size=96, buffer_size=16, layers=2)
     ref = OracleQwen3(model.state_dict(), cfg, dtype=torch.bfloat16)

@@ -50,6 +50,7 @@ SIGNATURES = {
     "tkv_silu_mul": (I, [P, P, I, I, I, I, P, P]),
     "tkv_skinny_gemm_splits": (I, [I, I, I]),
     "tkv_skinny_gemm": (I, [P, P, P, I, I, I, I, P, P]),
+    "tkv_skinny_gemm_swiglu": (I, [P, P, P, I, I, I, I, P, P]),
     "tkv_read_status": (I, [P, P]),
 }
 

@@ -40,16 +40,26 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     return ws
 
 
-# Query rows per segment (new tokens x query heads per KV head) up to which multi-token queries go to the hand-written
-# kernels, from timings on B200 (batch 32, 16/8 heads, about 4100 cached tokens per head, ms per layer):
-#   rows  16: decode kernel 0.19        | library causal attention 0.35 | library attention with a length mask 0.47
-#   rows  32: 32-rows-per-CTA kernel 0.24 | 0.36 | 0.55
-#   rows  64: 0.46 | 0.36 | 0.77        rows 256: 1.8 | 0.64 | 2.3
-# (the kernel reads the K/V chunk once per 32 rows, about 0.23 ms a pass).  Caches whose segments share one length
-# leave the kernels beyond one pass (the causal library path needs no mask), caches with differing head lengths
-# beyond 256 rows.
+# Several query tokens against a materialised cache (a piece of a chunked prefill, a follow-up prompt, multi-token
+# decoding).  Timings on B200, batch 32, 16/8 heads, about 4100 cached tokens per head, ms per layer, by query rows per
+# segment (new tokens x query heads per KV head):
+#   rows   split-KV kernels (16 / 32 rows per CTA)   query-resident kernel   library causal   library with a length mask
+#    16        0.19                                     0.25                    0.35             0.48
+#    64        0.46                                     0.18                    0.37             0.78
+#   128        0.90                                     0.17                    0.37             1.20
+#   256        1.79                                     0.33                    0.64             2.30
+#  1024        7.57                                     1.19                    0.89             7.92
+# The split-KV kernels re-read the K/V chunk once per 16 / 32 rows but spread a segment over many CTAs; the
+# query-resident kernel reads K/V once per 128 rows with one CTA per (segment, block of 128 rows).  So: up to 16 rows
+# the decode kernel; beyond, the query-resident kernel whenever it gets enough CTAs to fill the GPU, up to 512 rows where
+# all heads have one length (the library's causal kernel wins from about 1000 rows) and without limit where the lengths
+# differ between heads (the library would need a materialised mask); with few segments the 32-row split-KV kernel up to
+# the limits below, then the library.  A dense prompt pass (no cache yet) stays with the library, which is about three
+# times faster there (1.4 PFLOP/s against 0.5 for the query-resident kernel at 8192 tokens).
 MULTI_TOKEN_MAX_ROWS_UNIFORM = 32
 MULTI_TOKEN_MAX_ROWS_RAGGED = 256
+RESIDENT_MIN_CTAS = 96
+RESIDENT_MAX_ROWS_UNIFORM = 512
 
 
 def _dense_causal(query, key, value, scaling):
@@ -102,15 +112,19 @@ def tkv_attention_forward(
         hkv = key.shape[1]
         uniform = head_lens is not None and flash_attn_kwargs.get("uniform_lengths", False)
         limit = MULTI_TOKEN_MAX_ROWS_UNIFORM if uniform else MULTI_TOKEN_MAX_ROWS_RAGGED
-        if (head_lens is not None and ql * (hq // hkv) <= limit and dim == 128
+        rows = ql * (hq // hkv)
+        if (head_lens is not None and dim == 128
                 and query.dtype in (torch.bfloat16, torch.float16) and key.stride(3) == 1 and key.stride(2) == dim
                 and key.stride(0) == hkv * key.stride(1) and key.shape[0] * key.stride(0) // dim >= 128):
-            # New tokens against the materialised cache (a piece of a chunked prefill, a follow-up prompt, multi-token
-            # decoding): the tensor-core kernels with the (token, head) query rows on the N dimension.
-            out = torch.empty(bsz, ql, hq, dim, dtype=query.dtype, device=query.device)
-            ops.decode_attn_multi(query.transpose(1, 2), key, value, head_lens, key.stride(1) // dim, out, hkv, scaling,
-                                  key.shape[2], status=flash_attn_kwargs.get("status"))
-            return out, None, None
+            # New tokens against the materialised cache: the tensor-core kernels (see the table above).
+            resident = rows > 16 and (not uniform or rows <= RESIDENT_MAX_ROWS_UNIFORM) and (
+                bsz * hkv * -(-rows // 128) >= RESIDENT_MIN_CTAS or (not uniform and rows > limit))
+            if resident or rows <= limit:
+                out = torch.empty(bsz, ql, hq, dim, dtype=query.dtype, device=query.device)
+                run = ops.prefill_attn if resident else ops.decode_attn_multi
+                run(query.transpose(1, 2), key, value, head_lens, key.stride(1) // dim, out, hkv, scaling,
+                    key.shape[2], status=flash_attn_kwargs.get("status"))
+                return out, None, None
         if head_lens is not None and not flash_attn_kwargs.get("uniform_lengths", False):
             return _ragged_causal(query, key, value, head_lens, scaling), None, None
         return _dense_causal(query, key, value, scaling), None, None

@@ -192,12 +192,20 @@ constexpr int kMergeEarly = 32;   // partial outputs per thread requested before
 // Requests this thread's dimension of the first kMergeEarly chunk partials of (segment, row g).  Nothing here depends
 // on the segment's length, so the loads go out together with the length load; chunks beyond the live ones are
 // read too (the workspace covers nchunks per segment) and discarded by merge_partials.
+//
+// That pays while most of the requested chunks exist (segments of one length: the decode benchmark has 17 chunks of
+// which 16-17 are live).  Where the grid allows many more chunks than a typical segment has (ragged lengths: up to 32
+// chunks for a mean of 11), the blind loads would mostly fetch stale partials, so beyond kMergeBlind chunks the length is
+// read first and only the live chunks are requested: one more dependent round trip, a third of the traffic.
+constexpr int kMergeBlind = 24;
 template <int kD>
 __device__ __forceinline__ void load_partials_early(const AttnParams& p, int seg, int g, int d, float (&early)[kMergeEarly]) {
   const int64_t it0 = ((int64_t)seg * p.nchunks) * p.rows + g;
+  int live = p.nchunks;
+  if (p.nchunks > kMergeBlind) live = (min(p.seg_len[seg], p.max_len) + p.chunk - 1) / p.chunk;
 #pragma unroll
   for (int c = 0; c < kMergeEarly; ++c)
-    early[c] = (p.nchunks > 1 && c < p.nchunks) ? p.part_o[(it0 + (int64_t)c * p.rows) * kD + d] : 0.f;
+    early[c] = (p.nchunks > 1 && c < live) ? p.part_o[(it0 + (int64_t)c * p.rows) * kD + d] : 0.f;
 }
 
 template <int kD>

@@ -10,7 +10,8 @@
 // thread per row, so the softmax never crosses threads:
 //   S[128 rows x 128 tokens]  = Q[128 x 128 dims] . K_tile^T     A = Q (smem, K-major, 128B swizzle, staged once),
 //                                                                B = K tile as TMA wrote it; D in TMEM, two buffers
-//   row max / exp2 / sum      thread = row, tcgen05.ld 32 columns at a time; P rounded to the K/V dtype into smem
+//   row max / exp2 / sum      thread = row, its 128 scores read from TMEM once and held in registers; P rounded to the
+//                             K/V dtype into smem
 //   O[128 rows x 128 dims]   += P[128 x 128 tokens] . V_tile      A = P (smem, K-major, 128B swizzle), B = V tile read
 //                                                                MN-major from the bytes TMA wrote; D in TMEM
 // O is rescaled in TMEM only when a row's maximum grew by more than 2^8 since the reference maximum was fixed (the
@@ -63,15 +64,27 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 32 consecutive TMEM columns of this thread's lane into v[0..32), without waiting: several of these are issued back to
+// back and completed by one pf_wait_ld(), so that a row of S costs one TMEM round trip instead of four.
+__device__ __forceinline__ void pf_ld32_nowait(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+      "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void pf_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 template <int kDtype>
-__device__ __forceinline__ uint32_t pf_pack2(float a, float b, float& sum) {
+__device__ __forceinline__ uint32_t pf_pack2(float a, float b) {
   if (kDtype == TKV_BF16) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
-    sum += __low2float(v) + __high2float(v);
     return *reinterpret_cast<const uint32_t*>(&v);
   }
   const __half2 v = __floats2half2_rn(a, b);
-  sum += __low2float(v) + __high2float(v);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
@@ -81,8 +94,11 @@ __device__ __forceinline__ uint32_t pf_swz(int r, int c) {
   return (uint32_t)((c >> 3) * kPfHalf + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
-// grid.x = nblocks * nseg with the query blocks in descending order (the last block of a causal pass sees the most
-// tokens, so the longest CTAs start first).
+// grid.x = nseg * nblocks, segment-major: the query blocks of one segment are neighbours in launch order, so they run
+// at the same time and the K/V tiles they all stream are fetched from HBM once and then found in L2 (with the blocks of
+// different segments side by side instead, a long causal pass re-read its K/V from HBM once per block and was bound
+// by that).  Within a segment the blocks go in descending order: the last block of a causal pass sees the most tokens,
+// so the longest CTAs start first.
 template <int kDtype>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
@@ -90,8 +106,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   grid_dependency_wait();
   grid_launch_dependents();
-  const int blk = nblocks - 1 - (int)(blockIdx.x / (unsigned)nseg);
-  const int seg = (int)(blockIdx.x % (unsigned)nseg);
+  const int seg = (int)(blockIdx.x / (unsigned)nblocks);
+  const int blk = nblocks - 1 - (int)(blockIdx.x % (unsigned)nblocks);
   const int tid = threadIdx.x, warp = tid >> 5;
   const int G = p.hq / p.hkv;
   const int b = seg / p.hkv, h = seg - b * p.hkv;
@@ -203,15 +219,26 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     __syncwarp();
     const int limit = vis - t0;             // columns of this tile the row may see (<= 0: none, >= 128: all)
     const uint32_t s_addr = lane_base + 128 * sb;
+    // The row's 128 scores stay in registers from here to the exponentials: one TMEM round trip per tile.
+    uint32_t sv[128];
     float m_tile = -INFINITY;
     if (ok) {
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        float v[32];
-        tmem_ld32(s_addr + c4 * 32, v);
+      for (int c4 = 0; c4 < 4; ++c4) pf_ld32_nowait(s_addr + c4 * 32, sv + c4 * 32);
+      pf_wait_ld();
+      if (limit >= kPfTile) {                 // every column visible (all tiles but those on the causal diagonal)
+        // four independent chains: with one warp per scheduler nothing else hides the latency of a serial maximum
+        float mr[4] = {__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]), __uint_as_float(sv[3])};
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c4 * 32 + i < limit) m_tile = fmaxf(m_tile, v[i] * p.scale_log2);
+        for (int i = 4; i < 128; i += 4) {
+          mr[0] = fmaxf(mr[0], __uint_as_float(sv[i])); mr[1] = fmaxf(mr[1], __uint_as_float(sv[i + 1]));
+          mr[2] = fmaxf(mr[2], __uint_as_float(sv[i + 2])); mr[3] = fmaxf(mr[3], __uint_as_float(sv[i + 3]));
+        }
+        m_tile = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * p.scale_log2;   // the scale is positive (checked on the host)
+      } else {
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+          if (i < limit) m_tile = fmaxf(m_tile, __uint_as_float(sv[i]) * p.scale_log2);
       }
     }
     const bool grow = m_tile > m_ref + kPfRescaleGap || (m_ref == -INFINITY && m_tile > -INFINITY);
@@ -248,24 +275,43 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       }
       m_ref = m_new;
     }
-    // ---- P = 2^(s - m_ref), rounded to the K/V dtype; the sum uses the rounded weights
+    // ---- P = 2^(s - m_ref) rounded to the K/V dtype for the tensor core; the row sum is taken in fp32
     if (ok) {
+      const float neg_m = -m_ref;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};     // independent partial sums, for the same reason as the maxima
+      if (limit >= kPfTile) {
 #pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) {
-        float v[32];
-        tmem_ld32(s_addr + c4 * 32, v);
-        uint32_t w[16];
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t w[16];
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const int col = c4 * 32 + i;
-          const float a = (col < limit) ? exp2_weight(fmaf(v[i], p.scale_log2, -m_ref)) : 0.f;
-          const float bb = (col + 1 < limit) ? exp2_weight(fmaf(v[i + 1], p.scale_log2, -m_ref)) : 0.f;
-          w[i >> 1] = pf_pack2<kDtype>(a, bb, l_sum);
+          for (int i = 0; i < 32; i += 2) {
+            const float a = exp2_weight(fmaf(__uint_as_float(sv[c4 * 32 + i]), p.scale_log2, neg_m));
+            const float bb = exp2_weight(fmaf(__uint_as_float(sv[c4 * 32 + i + 1]), p.scale_log2, neg_m));
+            ls[(i >> 1) & 3] += a + bb;
+            w[i >> 1] = pf_pack2<kDtype>(a, bb);
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
         }
+      } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
-          st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            const int col = c4 * 32 + i;
+            const float a = (col < limit) ? exp2_weight(fmaf(__uint_as_float(sv[col]), p.scale_log2, neg_m)) : 0.f;
+            const float bb = (col + 1 < limit) ? exp2_weight(fmaf(__uint_as_float(sv[col + 1]), p.scale_log2, neg_m)) : 0.f;
+            ls[(i >> 1) & 3] += a + bb;
+            w[i >> 1] = pf_pack2<kDtype>(a, bb);
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+        }
       }
+      l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // Rows of the last V tile beyond the segment's length may hold anything (stale rows, another segment): their
       // weight is zero, but 0 x NaN would poison the product, so they are cleared in shared memory.
       if (t0 + kPfTile > len) {
@@ -322,9 +368,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
       tmem_ld32(lane_base + 256 + c4 * 32, o);
       if (row_valid) {
         uint32_t w[16];
-        float unused = 0.f;
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) w[i >> 1] = pf_pack2<kDtype>(o[i] * inv, o[i + 1] * inv, unused);
+        for (int i = 0; i < 32; i += 2) w[i >> 1] = pf_pack2<kDtype>(o[i] * inv, o[i + 1] * inv);
 #pragma unroll
         for (int c = 0; c < 4; ++c)
           st16(out_row + (c4 * 4 + c) * 16, make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
@@ -364,6 +409,7 @@ extern "C" int tkv_prefill_attn(const void* q, int64_t q_sb, int64_t q_st, int64
                                 float scale, int max_len, int q_tokens, int32_t* status, tkv_stream_t stream) {
   using namespace tkv;
   if (!q || !k_cache || !v_cache || !out) return fail(TKV_ERR_ARG, "tkv_prefill_attn: NULL pointer argument");
+  if (!(scale > 0.f)) return fail(TKV_ERR_ARG, "tkv_prefill_attn: scale must be positive");
   if (batch < 0 || hq <= 0 || hkv <= 0 || hq % hkv != 0 || max_len <= 0 || q_tokens < 1 || cap < max_len)
     return fail(TKV_ERR_ARG, "tkv_prefill_attn: bad sizes batch=%d hq=%d hkv=%d max_len=%d q_tokens=%d cap=%lld", batch, hq,
                 hkv, max_len, q_tokens, (long long)cap);

@@ -203,8 +203,20 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
   const int64_t off = (int64_t)blockIdx.x * cols * 2;
   const int nvec = cols / 8;  // 16-byte vectors per row
   float ss = 0.f;
+  // Rows of up to 256 * kKeep vectors (hidden size 8192) stay in registers between the two passes, and the norm
+  // weights (they do not depend on the preceding kernel's output, but their load is cheap) are requested up front.
+  constexpr int kKeep = 4;
+  const bool in_regs = nvec <= 256 * kKeep;
+  uint4 keep[kKeep], wkeep[kKeep];
+  if (in_regs) {
+#pragma unroll
+    for (int j = 0; j < kKeep; ++j) {
+      const int i = threadIdx.x + j * 256;
+      if (i < nvec) wkeep[j] = ld16(reinterpret_cast<const char*>(weight) + (int64_t)i * 16);
+    }
+  }
   // Pass 1: update the residual stream and accumulate the sum of squares.
-  for (int i = threadIdx.x; i < nvec; i += 256) {
+  for (int i = threadIdx.x, j = 0; i < nvec; i += 256, ++j) {
     uint4 r = ld16(residual + off + (int64_t)i * 16);
     if (delta != nullptr && in_splits > 0) {
       float d[8];
@@ -226,7 +238,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
     }
     const uint32_t ws[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-    for (int j = 0; j < 4; ++j) { const float a = T::lo(ws[j]), c = T::hi(ws[j]); ss += a * a + c * c; }
+    for (int q = 0; q < 4; ++q) { const float a = T::lo(ws[q]), c = T::hi(ws[q]); ss += a * a + c * c; }
+    if (in_regs) {
+#pragma unroll
+      for (int q = 0; q < kKeep; ++q) if (q == j) keep[q] = r;
+    }
   }
   ss = warp_sum(ss);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
@@ -235,10 +251,16 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
 #pragma unroll
   for (int i = 0; i < 8; ++i) tot += red[i];
   const float rstd = rsqrtf(tot / (float)cols + eps);
-  // Pass 2: the row was just written/read by this CTA, so it comes from L1/L2.
-  for (int i = threadIdx.x; i < nvec; i += 256) {
-    const uint4 r = ld16(residual + off + (int64_t)i * 16);
-    const uint4 wv = ld16(reinterpret_cast<const char*>(weight) + (int64_t)i * 16);
+  // Pass 2: from the registers, or (longer rows) from L1/L2 where this CTA has just written the row.
+  for (int i = threadIdx.x, j = 0; i < nvec; i += 256, ++j) {
+    uint4 r, wv;
+    if (in_regs) {
+#pragma unroll
+      for (int q = 0; q < kKeep; ++q) if (q == j) { r = keep[q]; wv = wkeep[q]; }
+    } else {
+      r = ld16(residual + off + (int64_t)i * 16);
+      wv = ld16(reinterpret_cast<const char*>(weight) + (int64_t)i * 16);
+    }
     uint4 o;
     o.x = T::pack(T::lo(wv.x) * T::round(T::lo(r.x) * rstd), T::hi(wv.x) * T::round(T::hi(r.x) * rstd));
     o.y = T::pack(T::lo(wv.y) * T::round(T::lo(r.y) * rstd), T::hi(wv.y) * T::round(T::hi(r.y) * rstd));

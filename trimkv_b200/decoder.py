@@ -34,7 +34,7 @@ class FusedDecodeStep:
         return (head_dim_of(cfg) == 128 and rotary_dim_of(cfg) == 128 and cfg.retention_gate == "rg"
                 and getattr(cfg, "hidden_act", "silu") == "silu")
 
-    def __init__(self, model, cache: TrimKVCache):
+    def __init__(self, model, cache: TrimKVCache, tc_gemm: bool = False, fused_down: bool = False):
         cfg = model.config
         if not self.supports(model):
             raise NotImplementedError("fused decode step needs head_dim 128 (fully rotated), retention_gate 'rg' and SiLU")
@@ -69,10 +69,13 @@ class FusedDecodeStep:
                 gu, gu_bias = fuse([mlp.gate_up_proj] if hasattr(mlp, "gate_up_proj") else [mlp.gate_proj, mlp.up_proj])
                 self.layers.append((layer, w, bias, gu, gu_bias))
         self.hq, self.hkv, self.eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps
-        # tkv_skinny_gemm for the four per-layer projections.  Off by default: at 32 rows these GEMMs are bound by
-        # launch and pipeline-fill latency, and the tensor-core kernel only matches cuBLAS (5-12 us per call either
-        # way on B200) while its fp32 partials make the consumers slower; TKV_TC_GEMM=1 switches it on.
-        self.use_tc_gemm = os.environ.get("TKV_TC_GEMM", "0") == "1"
+        # tc_gemm: tkv_skinny_gemm for the four per-layer projections instead of the library GEMMs.  Off by default: at 32
+        # rows these GEMMs are bound by launch and pipeline-fill latency, and the tensor-core kernel only matches cuBLAS
+        # (5-12 us per call either way on B200) while its fp32 partials make the consumers slower.
+        # fused_down: the MLP's activation and down projection as one kernel (tkv_skinny_gemm_swiglu) instead of
+        # tkv_silu_mul + a library GEMM.  Off by default: measured 4.47 ms per decode step against 4.11 ms (Qwen3-1.7B
+        # shape, batch 32): converting the activation tiles inside the GEMM's pipeline costs more than the launch it saves.
+        self.use_tc_gemm, self.fused_down = tc_gemm, fused_down
         self._partials = {}
 
     def _gemm(self, x, w, tag):
@@ -122,12 +125,21 @@ class FusedDecodeStep:
             gu, s3 = self._gemm(h, w_gu, "gu")
             if s3 == 0:
                 gu = F.linear(h, w_gu, b_gu)
+            d_bias = layer.mlp.down_proj.bias
+            w_down = layer.mlp.down_proj.weight
+            d_splits = ops.skinny_gemm_splits(bsz, w_down.shape[0], w_down.shape[1]) if (self.fused_down and s3 == 0) else 0
+            if d_splits:
+                delta = self._partials.get(("down_swiglu", bsz))
+                if delta is None:
+                    delta = torch.empty(d_splits, bsz, w_down.shape[0], dtype=torch.float32, device=x.device)
+                    self._partials[("down_swiglu", bsz)] = delta
+                ops.skinny_gemm_swiglu(gu, w_down, delta, self.cache._status)
+                continue
             act = torch.empty(bsz, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
             ops.silu_mul(gu, act, s3, b_gu if s3 else None)
-            d_bias = layer.mlp.down_proj.bias
-            delta, d_splits = self._gemm(act, layer.mlp.down_proj.weight, "down")
+            delta, d_splits = self._gemm(act, w_down, "down")
             if d_splits == 0:
-                delta = F.linear(act, layer.mlp.down_proj.weight, d_bias)
+                delta = F.linear(act, w_down, d_bias)
         ops.add_rmsnorm(x, delta, m.norm.weight, h, self.eps, d_splits, d_bias if d_splits else None)
         return F.linear(h, self.model.lm_head.weight)
 
@@ -140,13 +152,13 @@ class GreedyDecoder:
     """
 
     def __init__(self, model, cache: TrimKVCache, use_graph: bool = True, fused: bool = True, head_shard_group=None,
-                 fused_gather: bool = False):
+                 fused_gather: bool = False, tc_gemm: bool = False, fused_down: bool = False):
         self.model, self.cache, self.cfg = model, cache, model.config
         self.fused = None
         if head_shard_group is not None:
             self.fused = HeadShardedDecodeStep(model, cache, head_shard_group, fused_gather=fused_gather)
         elif fused and FusedDecodeStep.supports(model) and model.lm_head.weight.dtype in (torch.bfloat16, torch.float16):
-            self.fused = FusedDecodeStep(model, cache)
+            self.fused = FusedDecodeStep(model, cache, tc_gemm=tc_gemm, fused_down=fused_down)
         dev = model.device
         self.batch = cache._batch
         self.ids = torch.zeros(self.batch, 1, dtype=torch.int64, device=dev)

@@ -311,6 +311,22 @@ def skinny_gemm(x, w, partial, status=None) -> int:
     return skinny_gemm_splits(m, n, k)
 
 
+def skinny_gemm_swiglu(gate_up, w, partial, status=None) -> int:
+    """:func:`skinny_gemm` over ``x = SiLU(gate_up[:, :K]) * gate_up[:, K:]`` computed inside the kernel
+    (``gate_up [M, 2K]``, ``w [N, K]``): the MLP's activation and down projection in one launch."""
+    m, two_k = gate_up.shape
+    n, k = w.shape
+    if two_k != 2 * k:
+        raise ValueError(f"gate_up has {two_k} columns, the weight wants 2 x {k}")
+    if not (gate_up.is_contiguous() and w.is_contiguous() and partial.is_contiguous() and partial.dtype == torch.float32):
+        raise ValueError("skinny_gemm_swiglu wants contiguous gate_up, w and an fp32 contiguous partial buffer")
+    rc = lib().tkv_skinny_gemm_swiglu(gate_up.data_ptr(), w.data_ptr(), partial.data_ptr(), m, n, k,
+                                      dtype_code(gate_up.dtype), _ptr(status), _stream(gate_up))
+    check(rc, "tkv_skinny_gemm_swiglu")
+    _count(1)
+    return skinny_gemm_splits(m, n, k)
+
+
 def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group: int, nseg: int, cap: int,
              q_idx: int, max_len: int, keep_cnt, protect_last: int = 0, memory_size: int = 1, trigger_len: int = 0,
              kept_idx_out=None, kept_stride: int = 0, status=None, knorm: bool = False, score_dtype: int = 0,
