@@ -471,11 +471,18 @@ def run_micro(args):
         res["token_bound"] = bound
         ws = torch.empty(ops.decode_attn_workspace_bytes(batch, hq, hkv, D, cap) if bound is None else
                          ops.decode_attn_workspace_bytes_ragged(batch, hq, hkv, D, cap, bound), dtype=torch.uint8, device=dev)
+        seg_start = None
+        if args.packed:   # the live rows of every segment back to back, as the reference's flat caches hold them
+            mask = (torch.arange(cap, device=dev)[None, :] < lens[:, None]).view(-1)
+            bufs = [(kk[mask].contiguous(), vv[mask].contiguous()) for kk, vv in bufs]
+            cu = torch.zeros(nseg + 1, dtype=torch.int32, device=dev); cu[1:] = lens.cumsum(0)
+            seg_start = cu[:-1].contiguous()
+            res["layout"] = "packed"
         for i in range(args.warmup + args.steps):
             k, v = bufs[i % nbuf]
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
-            ops.decode_attn(q, k, v, lens, None, cap, out, ws, hkv, D ** -0.5, cap, None, total_len_bound=bound)
+            ops.decode_attn(q, k, v, lens, seg_start, cap, out, ws, hkv, D ** -0.5, cap, None, total_len_bound=bound)
             e1.record()
             if i >= args.warmup:
                 times.append((e0, e1))
@@ -486,7 +493,8 @@ def run_micro(args):
         try:
             from flash_attn.flash_attn_interface import flash_attn_varlen_func
             mask = (torch.arange(cap, device=dev)[None, :] < lens[:, None]).view(-1)
-            packs = [(kk[mask].unsqueeze(1).contiguous(), vv[mask].unsqueeze(1).contiguous()) for kk, vv in bufs]
+            packs = ([(kk.unsqueeze(1), vv.unsqueeze(1)) for kk, vv in bufs] if args.packed else
+                     [(kk[mask].unsqueeze(1).contiguous(), vv[mask].unsqueeze(1).contiguous()) for kk, vv in bufs])
             cu_k = torch.zeros(nseg + 1, dtype=torch.int32, device=dev); cu_k[1:] = lens.cumsum(0)
             cu_q = torch.arange(0, nseg + 1, dtype=torch.int32, device=dev)
             pq = q.view(batch, hkv, hq // hkv, D).reshape(nseg, hq // hkv, D).contiguous()
@@ -524,6 +532,8 @@ def main():
     ap.add_argument("--M", type=int, default=4096)
     ap.add_argument("--nseg", type=int, default=2048)
     ap.add_argument("--q-tokens", type=int, default=16, help="multi microbenchmark: new tokens per request")
+    ap.add_argument("--packed", action="store_true",
+                    help="attention microbenchmark: the reference's packed [sum n, D] layout (seg_start = cu_seqlens_k)")
     ap.add_argument("--token-bound", action="store_true",
                     help="attention microbenchmark: size the grid by the total token count (ragged lengths)")
     ap.add_argument("--ctas", type=int, default=1, help="CTAs sharing one segment in the eviction microbenchmarks")

@@ -16,7 +16,6 @@ from .modeling_trimkv import (GatedMLP, TrimKVAttention, TrimKVDecoderLayer, Tri
 class TrimKVLlamaConfig(LlamaConfig):
     """Flag surface and defaults of ``TrimKVLlamaConfig`` (configuration_trimkv_llama.py:26-60)."""
 
-    model_type = "trimkv_llama_b200"
     _flags = dict(retention_gate_bias_init=10.0, retention_weight=1.0, memory_size=2048, retention_gate="rg",
                   base_loss="fwkl", attn_impl="rg_attn_flex", compress_memory=True, compress_strategy="alpha",
                   floor_budget_ratio=0.0, buffer_size=1, trainable_params=None, max_seq_len=20480,

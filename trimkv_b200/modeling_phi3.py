@@ -17,7 +17,6 @@ from .modeling_trimkv import TrimKVAttention, TrimKVDecoderLayer, TrimKVForCausa
 class TrimKVPhi3Config(Phi3Config):
     """Flag surface and defaults of ``TrimKVPhi3Config`` (configuration_trimkv_phi3.py:10-41)."""
 
-    model_type = "trimkv_phi3_b200"
     _flags = dict(retention_gate_bias_init=10.0, retention_weight=1.0, memory_size=1024, retention_gate="rg",
                   base_loss="fwkl", attn_impl="rg_attn_flex", compress_memory=False, compress_strategy="alpha",
                   floor_budget_ratio=0.0, buffer_size=1, trainable_params=None, max_seq_len=20480,

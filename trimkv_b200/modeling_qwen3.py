@@ -23,7 +23,6 @@ class TrimKVQwen3Config(Qwen3Config):
     """Flag surface and defaults of ``TrimKVQwen3Config`` (configuration_trimkv_qwen3.py:10-47).  The shape
     defaults are those of the Qwen3-1.7B architecture; ``attn_implementation`` defaults to this library's kernels."""
 
-    model_type = "trimkv_qwen3_b200"
     _flags = dict(retention_gate_bias_init=10.0, retention_weight=1.0, memory_size=1024, retention_gate="rg",
                   base_loss="fwkl", attn_impl="rg_attn_flex", compress_memory=True, compress_strategy="alpha",
                   floor_budget_ratio=0.0, alpha_threshold=0.0, buffer_size=128, trainable_params=None,
