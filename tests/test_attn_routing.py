@@ -36,18 +36,19 @@ def _call(bsz, hq, hkv, ql, n, cap, uniform, dense=False):
 
 
 @pytest.mark.parametrize("bsz,hq,hkv,ql,uniform,want", [
-    (32, 16, 8, 8, True, "split_kv"),            # 16 rows: the decode kernel's multi-token form
+    (32, 16, 8, 3, True, "split_kv"),            # 6 rows: the decode kernel's multi-token form
+    (32, 16, 8, 8, True, "query_resident"),      # 16 rows, 256 CTAs
     (32, 16, 8, 32, True, "query_resident"),     # 64 rows, 256 CTAs
     (32, 16, 8, 128, True, "query_resident"),    # 256 rows, 512 CTAs
-    (32, 16, 8, 512, True, "library_causal"),    # 1024 rows on a uniform cache: the library's causal kernel wins
-    (32, 16, 8, 512, False, "query_resident"),   # ... but not where the lengths differ (it would need a mask)
+    (32, 16, 8, 1024, True, "library_causal"),   # 2048 rows on a uniform cache: the library's causal kernel is ahead
+    (32, 16, 8, 1024, False, "query_resident"),  # ... but not where the lengths differ (it would need a mask)
     (2, 4, 2, 12, True, "split_kv"),             # 24 rows, 4 segments: too few CTAs for the query-resident kernel
     (2, 4, 2, 40, True, "library_causal"),       # 80 rows, few segments, uniform
     (2, 4, 2, 40, False, "split_kv"),            # 80 rows, few segments, ragged: 32-row kernel up to 256 rows
     (2, 4, 2, 150, False, "query_resident"),     # 300 rows, ragged: never a materialised mask
 ])
 def test_multi_token_routing(routes, bsz, hq, hkv, ql, uniform, want):
-    _call(bsz, hq, hkv, ql, n=600, cap=640, uniform=uniform)
+    _call(bsz, hq, hkv, ql, n=max(600, ql), cap=max(640, ql), uniform=uniform)
     assert routes == [want]
 
 

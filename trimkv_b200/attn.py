@@ -44,22 +44,22 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
 # decoding).  Timings on B200, batch 32, 16/8 heads, about 4100 cached tokens per head, ms per layer, by query rows per
 # segment (new tokens x query heads per KV head):
 #   rows   split-KV kernels (16 / 32 rows per CTA)   query-resident kernel   library causal   library with a length mask
-#    16        0.19                                     0.25                    0.35             0.48
-#    64        0.46                                     0.18                    0.37             0.78
-#   128        0.90                                     0.17                    0.37             1.20
-#   256        1.79                                     0.33                    0.64             2.30
-#  1024        7.57                                     1.19                    0.89             7.92
+#    16        0.19                                     0.16                    0.35             0.47
+#    64        0.46                                     0.13                    0.37             0.78
+#   128        0.90                                     0.13                    0.37             1.20
+#   256        1.79                                     0.23                    0.64             2.29
+#  1024        7.58                                     0.79                    0.90             7.91
 # The split-KV kernels re-read the K/V chunk once per 16 / 32 rows but spread a segment over many CTAs; the
-# query-resident kernel reads K/V once per 128 rows with one CTA per (segment, block of 128 rows).  So: up to 16 rows
-# the decode kernel; beyond, the query-resident kernel whenever it gets enough CTAs to fill the GPU, up to 512 rows where
-# all heads have one length (the library's causal kernel wins from about 1000 rows) and without limit where the lengths
-# differ between heads (the library would need a materialised mask); with few segments the 32-row split-KV kernel up to
-# the limits below, then the library.  A dense prompt pass (no cache yet) stays with the library, which is about three
-# times faster there (1.4 PFLOP/s against 0.5 for the query-resident kernel at 8192 tokens).
+# query-resident kernel reads K/V once per 128 rows with one CTA per (segment, block of 128 rows).  So: the
+# query-resident kernel whenever it gets enough CTAs to fill the GPU, up to 1024 rows where all heads have one length
+# (the library's causal kernel catches up around there and is ahead on whole prompts) and without limit where the
+# lengths differ between heads (the library would need a materialised mask); with few segments the split-KV kernels up
+# to the limits below, then the library.  A dense prompt pass (no cache yet) stays with the library, which is about twice
+# as fast there (1.44 PFLOP/s against 0.77 for the query-resident kernel at 8192 tokens).
 MULTI_TOKEN_MAX_ROWS_UNIFORM = 32
 MULTI_TOKEN_MAX_ROWS_RAGGED = 256
 RESIDENT_MIN_CTAS = 96
-RESIDENT_MAX_ROWS_UNIFORM = 512
+RESIDENT_MAX_ROWS_UNIFORM = 1024
 
 
 def _dense_causal(query, key, value, scaling):
@@ -117,7 +117,7 @@ def tkv_attention_forward(
                 and query.dtype in (torch.bfloat16, torch.float16) and key.stride(3) == 1 and key.stride(2) == dim
                 and key.stride(0) == hkv * key.stride(1) and key.shape[0] * key.stride(0) // dim >= 128):
             # New tokens against the materialised cache: the tensor-core kernels (see the table above).
-            resident = rows > 16 and (not uniform or rows <= RESIDENT_MAX_ROWS_UNIFORM) and (
+            resident = rows > 8 and (not uniform or rows <= RESIDENT_MAX_ROWS_UNIFORM) and (
                 bsz * hkv * -(-rows // 128) >= RESIDENT_MIN_CTAS or (not uniform and rows > limit))
             if resident or rows <= limit:
                 out = torch.empty(bsz, ql, hq, dim, dtype=query.dtype, device=query.device)

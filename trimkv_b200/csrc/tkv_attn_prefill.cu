@@ -27,7 +27,8 @@
 
 namespace tkv {
 
-constexpr int kPfThreads = 128;
+constexpr int kPfSoftmaxThreads = 256;         // two threads per query row: columns 0..63 and 64..127 of a tile
+constexpr int kPfThreads = kPfSoftmaxThreads + 32;   // plus one warp that issues the TMA copies and the MMAs
 constexpr int kPfTile = 128;                  // query rows per CTA, cached tokens per tile
 constexpr int kPfTileBytes = 32768;           // 128 rows x 256 B, as two 64-element halves of 16 KB
 constexpr int kPfHalf = 16384;
@@ -35,9 +36,10 @@ constexpr int kPfTmemCols = 512;              // S buffers at columns 0 and 128,
 constexpr float kPfRescaleGap = 8.0f;         // log2 of the largest weight tolerated before O is rescaled
 
 struct PfSmem {
-  uint64_t bar_k[2], bar_v[2], bar_s[2], bar_o;
+  uint64_t bar_k[2], bar_v[2], bar_s[2], bar_o, bar_p, bar_x;
   uint32_t tmem_base;
   int abort_flag;
+  float red[2][2][kPfTile];                   // [tile parity][column half][row]: row maxima, at the end row sums
 };
 constexpr int kPfSmemBytes = 6 * kPfTileBytes + (int)sizeof(PfSmem) + 1024;
 
@@ -64,8 +66,8 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
-// 32 consecutive TMEM columns of this thread's lane into v[0..32), without waiting: several of these are issued back to
-// back and completed by one pf_wait_ld(), so that a row of S costs one TMEM round trip instead of four.
+// 32 consecutive TMEM columns of this thread's lane, without waiting: several of these are issued back to back and
+// completed by one pf_wait_ld(), so that a thread's share of a row of S costs one TMEM round trip.
 __device__ __forceinline__ void pf_ld32_nowait(uint32_t taddr, uint32_t* r) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -77,6 +79,9 @@ __device__ __forceinline__ void pf_ld32_nowait(uint32_t taddr, uint32_t* r) {
       : "r"(taddr));
 }
 __device__ __forceinline__ void pf_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void pf_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 
 template <int kDtype>
 __device__ __forceinline__ uint32_t pf_pack2(float a, float b) {
@@ -99,6 +104,13 @@ __device__ __forceinline__ uint32_t pf_swz(int r, int c) {
 // different segments side by side instead, a long causal pass re-read its K/V from HBM once per block and was bound
 // by that).  Within a segment the blocks go in descending order: the last block of a causal pass sees the most tokens,
 // so the longest CTAs start first.
+//
+// Roles: warps 0-7 are the softmax warps.  TMEM lane = query row, and a warp may only touch the 32 lanes of its
+// quadrant (warp index mod 4), so row r is shared by thread r (columns 0..63 of every tile, dims 0..63 of O) and thread
+// 128 + r (the other halves); the two exchange their row maximum through shared memory once per tile.  Warp 8 issues
+// every TMA copy and every MMA (one lane), so no softmax warp ever waits for a copy.  All hand-offs are mbarriers with
+// bounded waits: bar_s (S of a tile is in TMEM), bar_x (all 256 partial maxima are in shared memory), bar_p (all of P
+// is in shared memory and O has been rescaled if it had to be), bar_o (P.V of a tile has completed).
 template <int kDtype>
 __global__ void __launch_bounds__(kPfThreads, 1)
 prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v, AttnParams p,
@@ -109,6 +121,8 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   const int seg = (int)(blockIdx.x / (unsigned)nblocks);
   const int blk = nblocks - 1 - (int)(blockIdx.x % (unsigned)nblocks);
   const int tid = threadIdx.x, warp = tid >> 5;
+  const bool is_ctrl = warp == 8;
+  const int row = tid & (kPfTile - 1), half = (tid >> 7) & 1;
   const int G = p.hq / p.hkv;
   const int b = seg / p.hkv, h = seg - b * p.hkv;
   int len = p.seg_len != nullptr ? p.seg_len[seg] : p.max_len;
@@ -116,18 +130,18 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     if (tid == 0 && blk == 0) report(p.status, TKV_DEV_LEN_BOUND);
     len = p.max_len;
   }
-  const int R = blk * kPfTile + tid;                       // this thread's query row of the segment
-  const bool row_valid = R < p.rows;
+  const int R = blk * kPfTile + row;                       // this thread's query row of the segment
+  const bool row_valid = !is_ctrl && R < p.rows;
   const int token = R / G, head = h * G + (R - token * G);
   // cached tokens this row may see, and the most any row of this CTA may see (CTA-uniform)
   const int vis = row_valid ? max(0, min(len, len - p.q_tokens + token + 1)) : 0;
   const int r_last = min(blk * kPfTile + kPfTile - 1, p.rows - 1);
   const int vis_max = max(0, min(len, len - p.q_tokens + r_last / G + 1));
   const int ntiles = (vis_max + kPfTile - 1) / kPfTile;
-  char* const out_row = p.out + (((int64_t)b * p.q_tokens + token) * p.hq + head) * 256;
+  char* const out_row = p.out + (((int64_t)b * p.q_tokens + token) * p.hq + head) * 256 + half * 128;
   if (ntiles == 0) {                                       // nothing visible (an empty segment): zeros
     if (row_valid)
-      for (int c = 0; c < 16; ++c) st16(out_row + c * 16, make_uint4(0, 0, 0, 0));
+      for (int c = 0; c < 8; ++c) st16(out_row + c * 16, make_uint4(0, 0, 0, 0));
     return;
   }
 
@@ -140,167 +154,188 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   volatile int* abort_flag = &sm->abort_flag;
   const int64_t row0 = (int64_t)seg * p.cap;
 
-  int k_issued = 0, v_issued = 0;                          // thread 0: tiles whose copies have been started
-  if (tid == 0) {
+  int k_issued = 0, v_issued = 0;                          // control lane: tiles whose copies have been started
+  auto load_k = [&](int j) {
+    const int st = j & 1;
+    mbar_expect_tx(&sm->bar_k[st], kPfTileBytes);
+    tma_load_2d(k_s + st * kPfTileBytes, &map_k, &sm->bar_k[st], 0, (int)(row0 + j * kPfTile));
+    tma_load_2d(k_s + st * kPfTileBytes + kPfHalf, &map_k, &sm->bar_k[st], 64, (int)(row0 + j * kPfTile));
+    ++k_issued;
+  };
+  auto load_v = [&](int j) {
+    const int st = j & 1;
+    mbar_expect_tx(&sm->bar_v[st], kPfTileBytes);
+    tma_load_2d(v_s + st * kPfTileBytes, &map_v, &sm->bar_v[st], 0, (int)(row0 + j * kPfTile));
+    tma_load_2d(v_s + st * kPfTileBytes + kPfHalf, &map_v, &sm->bar_v[st], 64, (int)(row0 + j * kPfTile));
+    ++v_issued;
+  };
+  if (tid == kPfSoftmaxThreads) {
     for (int i = 0; i < 2; ++i) { mbar_init(&sm->bar_k[i], 1); mbar_init(&sm->bar_v[i], 1); mbar_init(&sm->bar_s[i], 1); }
     mbar_init(&sm->bar_o, 1);
+    mbar_init(&sm->bar_p, kPfSoftmaxThreads);
+    mbar_init(&sm->bar_x, kPfSoftmaxThreads);
     sm->abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    for (int i = 0; i < 2 && i < ntiles; ++i) {
-      mbar_expect_tx(&sm->bar_k[i], kPfTileBytes);
-      tma_load_2d(k_s + i * kPfTileBytes, &map_k, &sm->bar_k[i], 0, (int)(row0 + i * kPfTile));
-      tma_load_2d(k_s + i * kPfTileBytes + kPfHalf, &map_k, &sm->bar_k[i], 64, (int)(row0 + i * kPfTile));
-      ++k_issued;
-    }
-    mbar_expect_tx(&sm->bar_v[0], kPfTileBytes);
-    tma_load_2d(v_s, &map_v, &sm->bar_v[0], 0, (int)row0);
-    tma_load_2d(v_s + kPfHalf, &map_v, &sm->bar_v[0], 64, (int)row0);
-    v_issued = 1;
+    for (int i = 0; i < 2 && i < ntiles; ++i) load_k(i);
+    load_v(0);
   }
   __syncwarp();
-  if (warp == 0) {
+  if (is_ctrl) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm->tmem_base)), "r"(kPfTmemCols));
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
-  }
-  // Q block as the A operand: row = query row, K-major with 128-byte swizzle (the layout TMA gives the K tiles).
-  {
-    const char* qp = p.q + ((int64_t)b * p.q_sb + (int64_t)token * p.q_st + (int64_t)head * p.q_sh) * 2;
+  } else {
+    // Q block as the A operand: row = query row, K-major with 128-byte swizzle (the layout TMA gives the K tiles);
+    // each of the row's two threads stages its 64 dims.
+    const char* qp = p.q + ((int64_t)b * p.q_sb + (int64_t)token * p.q_st + (int64_t)head * p.q_sh) * 2 + half * 128;
 #pragma unroll
-    for (int c = 0; c < 16; ++c)
-      st16(q_s + pf_swz(tid, c), row_valid ? ld16(qp + c * 16) : make_uint4(0, 0, 0, 0));
+    for (int c = 0; c < 8; ++c)
+      st16(q_s + pf_swz(row, half * 8 + c), row_valid ? ld16(qp + c * 16) : make_uint4(0, 0, 0, 0));
   }
   fence_async_smem();
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
-  const uint32_t idesc_s = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 0);
-  const uint32_t idesc_pv = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 1);
-  const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
 
-  // S of tile `j` into S buffer j & 1 (thread 0 only).
-  auto issue_s = [&](int j) -> bool {
-    if (!mbar_wait_or_abort(&sm->bar_k[j & 1], (j >> 1) & 1, abort_flag)) return false;
-    tc_fence_after();
-    const uint32_t k_addr = smem_u32(k_s + (j & 1) * kPfTileBytes);
+  if (is_ctrl) {
+    // ------------------------------------------------------------------------------------ TMA + MMA issue (one lane)
+    if (tid == kPfSoftmaxThreads) {
+      const uint32_t idesc_s = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 0);
+      const uint32_t idesc_pv = pf_idesc(kDtype == TKV_BF16 ? 1 : 0, 1);
+      const uint32_t q_addr = smem_u32(q_s), p_addr = smem_u32(p_s);
+      auto issue_s = [&](int j) -> bool {       // S of tile j into S buffer j & 1
+        if (!mbar_wait_or_abort(&sm->bar_k[j & 1], (j >> 1) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint32_t k_addr = smem_u32(k_s + (j & 1) * kPfTileBytes);
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {   // 16 dims per MMA: 4 steps inside a 128-byte swizzle atom, then the other half
-      const uint32_t off = (k >> 2) * kPfHalf + (k & 3) * 32;
-      umma(tmem + 128 * (j & 1), make_desc(q_addr + off, 16, 1024, 2), make_desc(k_addr + off, 16, 1024, 2), idesc_s, k > 0);
-    }
-    umma_commit(&sm->bar_s[j & 1]);
-    return true;
-  };
-
-  if (tid == 0 && !issue_s(0)) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
-  __syncwarp();
-
-  float m_ref = -INFINITY, l_sum = 0.f;     // reference maximum of this row (log2 domain) and its weight sum
-  int done_tiles = 0;
-  for (int j = 0; j < ntiles; ++j) {
-    const int sb = j & 1;
-    const int t0 = j * kPfTile;
-    // ---- S of this tile
-    bool ok = mbar_wait_or_abort(&sm->bar_s[sb], (j >> 1) & 1, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok) { if (*abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); } }
-    tc_fence_after();
-    if (tid == 0 && ok) {
-      // the tensor core works on the next tile's S while this tile's softmax runs; K stage `sb` is free again
-      if (j + 1 < ntiles && !issue_s(j + 1)) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
-      if (j + 2 < ntiles && *abort_flag == 0) {
-        mbar_expect_tx(&sm->bar_k[sb], kPfTileBytes);
-        tma_load_2d(k_s + sb * kPfTileBytes, &map_k, &sm->bar_k[sb], 0, (int)(row0 + (j + 2) * kPfTile));
-        tma_load_2d(k_s + sb * kPfTileBytes + kPfHalf, &map_k, &sm->bar_k[sb], 64, (int)(row0 + (j + 2) * kPfTile));
-        ++k_issued;
+        for (int k = 0; k < 8; ++k) {   // 16 dims per MMA: 4 steps inside a 128-byte swizzle atom, then the other half
+          const uint32_t off = (k >> 2) * kPfHalf + (k & 3) * 32;
+          umma(tmem + 128 * (j & 1), make_desc(q_addr + off, 16, 1024, 2), make_desc(k_addr + off, 16, 1024, 2), idesc_s, k > 0);
+        }
+        umma_commit(&sm->bar_s[j & 1]);
+        return true;
+      };
+      bool ok = issue_s(0);
+      for (int j = 0; j < ntiles && ok; ++j) {
+        // S of the next tile: its buffer was read for tile j-1, whose P has been waited for below (bar_p) already
+        if (j + 1 < ntiles) ok = issue_s(j + 1);
+        // V of the next tile goes where V of tile j-1 was: free once P.V of tile j-1 has completed
+        if (ok && j + 1 < ntiles) {
+          if (j > 0) ok = mbar_wait_or_abort(&sm->bar_o, (j - 1) & 1, abort_flag);
+          if (ok) load_v(j + 1);
+        }
+        // K two tiles ahead goes where K of this tile is: free once S of this tile has completed
+        if (ok && j + 2 < ntiles) {
+          ok = mbar_wait_or_abort(&sm->bar_s[j & 1], (j >> 1) & 1, abort_flag);
+          if (ok) load_k(j + 2);
+        }
+        // O += P . V once the softmax warps have written all of P (and rescaled O if they had to)
+        if (ok) ok = mbar_wait_or_abort(&sm->bar_p, j & 1, abort_flag);
+        if (ok) ok = mbar_wait_or_abort(&sm->bar_v[j & 1], (j >> 1) & 1, abort_flag);
+        if (ok) {
+          tc_fence_after();
+          const uint32_t v_addr = smem_u32(v_s + (j & 1) * kPfTileBytes);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {   // 16 tokens per MMA: along K of P inside the swizzle atom, 2048 B down the V tile
+            const uint64_t ad = make_desc(p_addr + (k >> 2) * kPfHalf + (k & 3) * 32, 16, 1024, 2);
+            const uint64_t bd = make_desc(v_addr + k * 2048, kPfHalf, 1024, 2);
+            umma(tmem + 256, ad, bd, idesc_pv, (j > 0 || k > 0));
+          }
+          umma_commit(&sm->bar_o);
+        }
       }
+      if (!ok && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
     }
     __syncwarp();
-    const int limit = vis - t0;             // columns of this tile the row may see (<= 0: none, >= 128: all)
-    const uint32_t s_addr = lane_base + 128 * sb;
-    // The row's 128 scores stay in registers from here to the exponentials: one TMEM round trip per tile.
-    uint32_t sv[128];
-    float m_tile = -INFINITY;
-    if (ok) {
-#pragma unroll
-      for (int c4 = 0; c4 < 4; ++c4) pf_ld32_nowait(s_addr + c4 * 32, sv + c4 * 32);
+  } else {
+    // ------------------------------------------------------------------------------------------------ softmax warps
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    float m_ref = -INFINITY, l_sum = 0.f;   // reference maximum of the row (log2 domain), weight sum of this thread's columns
+    bool alive = true;                      // warp-uniform
+    for (int j = 0; j < ntiles && alive; ++j) {
+      const int sb = j & 1;
+      const int t0 = j * kPfTile;
+      bool ok = mbar_wait_or_abort(&sm->bar_s[sb], (j >> 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      tc_fence_after();
+      const int limit = vis - t0 - half * 64;   // columns of this thread's half the row may see (<= 0: none, >= 64: all)
+      const uint32_t s_addr = lane_base + 128 * sb + 64 * half;
+      uint32_t sv[64];                           // the scores stay in registers from here to the exponentials
+      pf_ld32_nowait(s_addr, sv);
+      pf_ld32_nowait(s_addr + 32, sv + 32);
       pf_wait_ld();
-      if (limit >= kPfTile) {                 // every column visible (all tiles but those on the causal diagonal)
-        // four independent chains: with one warp per scheduler nothing else hides the latency of a serial maximum
+      float m_part = -INFINITY;
+      if (limit >= 64) {                         // every column visible (all tiles but those on the causal diagonal)
         float mr[4] = {__uint_as_float(sv[0]), __uint_as_float(sv[1]), __uint_as_float(sv[2]), __uint_as_float(sv[3])};
 #pragma unroll
-        for (int i = 4; i < 128; i += 4) {
+        for (int i = 4; i < 64; i += 4) {
           mr[0] = fmaxf(mr[0], __uint_as_float(sv[i])); mr[1] = fmaxf(mr[1], __uint_as_float(sv[i + 1]));
           mr[2] = fmaxf(mr[2], __uint_as_float(sv[i + 2])); mr[3] = fmaxf(mr[3], __uint_as_float(sv[i + 3]));
         }
-        m_tile = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * p.scale_log2;   // the scale is positive (checked on the host)
+        m_part = fmaxf(fmaxf(mr[0], mr[1]), fmaxf(mr[2], mr[3])) * p.scale_log2;   // the scale is positive (checked on the host)
       } else {
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
-          if (i < limit) m_tile = fmaxf(m_tile, __uint_as_float(sv[i]) * p.scale_log2);
+        for (int i = 0; i < 64; ++i)
+          if (i < limit) m_part = fmaxf(m_part, __uint_as_float(sv[i]) * p.scale_log2);
       }
-    }
-    const bool grow = m_tile > m_ref + kPfRescaleGap || (m_ref == -INFINITY && m_tile > -INFINITY);
-    const bool rescale = __any_sync(0xffffffffu, grow);
-    // ---- P.V of the previous tile must be complete before O, the P buffer or its V stage are touched
-    if (j > 0) {
-      bool ok2 = mbar_wait_or_abort(&sm->bar_o, (j - 1) & 1, abort_flag);
-      ok2 = __all_sync(0xffffffffu, ok2);
-      if (!ok2 && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
-      ok = ok && ok2;
-      tc_fence_after();
-    }
-    if (tid == 0 && ok && j + 1 < ntiles) {
-      const int vs = (j + 1) & 1;
-      mbar_expect_tx(&sm->bar_v[vs], kPfTileBytes);
-      tma_load_2d(v_s + vs * kPfTileBytes, &map_v, &sm->bar_v[vs], 0, (int)(row0 + (j + 1) * kPfTile));
-      tma_load_2d(v_s + vs * kPfTileBytes + kPfHalf, &map_v, &sm->bar_v[vs], 64, (int)(row0 + (j + 1) * kPfTile));
-      ++v_issued;
-    }
-    __syncwarp();
-    if (ok && rescale) {
-      const float m_new = fmaxf(m_ref, m_tile);
+      // the row's other half
+      sm->red[sb][half][row] = m_part;
+      pf_arrive(&sm->bar_x);
+      ok = mbar_wait_or_abort(&sm->bar_x, j & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { alive = false; break; }
+      const float m_tile = fmaxf(m_part, sm->red[sb][half ^ 1][row]);
+      const bool grow = m_tile > m_ref + kPfRescaleGap || (m_ref == -INFINITY && m_tile > -INFINITY);
+      const bool rescale = __any_sync(0xffffffffu, grow);   // the row's two warps hold the same values and decide alike
+      // ---- P.V of the previous tile must be complete before O or the P buffer are touched
       if (j > 0) {
-        const float alpha = (m_ref == -INFINITY) ? 1.0f : exp2_weight(m_ref - m_new);   // O of such a row is still zero
-#pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
-          float o[32];
-          tmem_ld32(lane_base + 256 + c4 * 32, o);
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] *= alpha;
-          tmem_st32(lane_base + 256 + c4 * 32, o);
-        }
-        l_sum *= alpha;
+        ok = mbar_wait_or_abort(&sm->bar_o, (j - 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        tc_fence_after();
       }
-      m_ref = m_new;
-    }
-    // ---- P = 2^(s - m_ref) rounded to the K/V dtype for the tensor core; the row sum is taken in fp32
-    if (ok) {
-      const float neg_m = -m_ref;
-      float ls[4] = {0.f, 0.f, 0.f, 0.f};     // independent partial sums, for the same reason as the maxima
-      if (limit >= kPfTile) {
+      if (rescale) {
+        const float m_new = fmaxf(m_ref, m_tile);
+        if (j > 0) {
+          const float alpha = (m_ref == -INFINITY) ? 1.0f : exp2_weight(m_ref - m_new);   // O of such a row is still zero
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
+          for (int c2 = 0; c2 < 2; ++c2) {       // this thread's 64 dims of the row
+            float o[32];
+            tmem_ld32(lane_base + 256 + 64 * half + c2 * 32, o);
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] *= alpha;
+            tmem_st32(lane_base + 256 + 64 * half + c2 * 32, o);
+          }
+          l_sum *= alpha;
+        }
+        m_ref = m_new;
+      }
+      // ---- P = 2^(s - m_ref) rounded to the K/V dtype for the tensor core; the row sum is taken in fp32
+      const float neg_m = -m_ref;
+      float ls[4] = {0.f, 0.f, 0.f, 0.f};
+      if (limit >= 64) {
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const float a = exp2_weight(fmaf(__uint_as_float(sv[c4 * 32 + i]), p.scale_log2, neg_m));
-            const float bb = exp2_weight(fmaf(__uint_as_float(sv[c4 * 32 + i + 1]), p.scale_log2, neg_m));
+            const float a = exp2_weight(fmaf(__uint_as_float(sv[c2 * 32 + i]), p.scale_log2, neg_m));
+            const float bb = exp2_weight(fmaf(__uint_as_float(sv[c2 * 32 + i + 1]), p.scale_log2, neg_m));
             ls[(i >> 1) & 3] += a + bb;
             w[i >> 1] = pf_pack2<kDtype>(a, bb);
           }
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+            st16(p_s + pf_swz(row, half * 8 + c2 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
         }
       } else {
 #pragma unroll
-        for (int c4 = 0; c4 < 4; ++c4) {
+        for (int c2 = 0; c2 < 2; ++c2) {
           uint32_t w[16];
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            const int col = c4 * 32 + i;
+            const int col = c2 * 32 + i;
             const float a = (col < limit) ? exp2_weight(fmaf(__uint_as_float(sv[col]), p.scale_log2, neg_m)) : 0.f;
             const float bb = (col + 1 < limit) ? exp2_weight(fmaf(__uint_as_float(sv[col + 1]), p.scale_log2, neg_m)) : 0.f;
             ls[(i >> 1) & 3] += a + bb;
@@ -308,82 +343,70 @@ prefill_attn_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
           }
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            st16(p_s + pf_swz(tid, c4 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
+            st16(p_s + pf_swz(row, half * 8 + c2 * 4 + c), make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
         }
       }
       l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
       // Rows of the last V tile beyond the segment's length may hold anything (stale rows, another segment): their
-      // weight is zero, but 0 x NaN would poison the product, so they are cleared in shared memory.
+      // weight is zero, but 0 x NaN would poison the product, so they are cleared in shared memory (a thread clears
+      // its half of the token row with its own index).
       if (t0 + kPfTile > len) {
-        bool ok3 = mbar_wait_or_abort(&sm->bar_v[sb], (j >> 1) & 1, abort_flag);
-        ok3 = __all_sync(0xffffffffu, ok3);
-        if (!ok3 && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
-        ok = ok && ok3;
-        if (ok3 && t0 + tid >= len) {
-          uint8_t* vt = v_s + sb * kPfTileBytes + tid * 128;
+        ok = mbar_wait_or_abort(&sm->bar_v[sb], (j >> 1) & 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        if (t0 + row >= len) {
+          uint8_t* vt = v_s + sb * kPfTileBytes + half * kPfHalf + row * 128;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) { st16(vt + c * 16, make_uint4(0, 0, 0, 0)); st16(vt + kPfHalf + c * 16, make_uint4(0, 0, 0, 0)); }
+          for (int c = 0; c < 8; ++c) st16(vt + c * 16, make_uint4(0, 0, 0, 0));
         }
       }
+      fence_async_smem();
+      tc_fence_before();
+      pf_arrive(&sm->bar_p);
     }
-    fence_async_smem();
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    if (*abort_flag != 0) break;            // uniform: read after the barrier
-    // ---- O += P . V
-    if (tid == 0) {
-      if (mbar_wait_or_abort(&sm->bar_v[sb], (j >> 1) & 1, abort_flag)) {
-        tc_fence_after();
-        const uint32_t v_addr = smem_u32(v_s + sb * kPfTileBytes);
+    // ---- epilogue: O / sum -> out
+    if (alive) {
+      bool ok = mbar_wait_or_abort(&sm->bar_o, (ntiles - 1) & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      alive = ok;
+    }
+    if (alive) {
+      tc_fence_after();
+      sm->red[ntiles & 1][half][row] = l_sum;
+      pf_arrive(&sm->bar_x);
+      bool ok = mbar_wait_or_abort(&sm->bar_x, ntiles & 1, abort_flag);
+      ok = __all_sync(0xffffffffu, ok);
+      alive = ok;
+    }
+    if (alive) {
+      const float total = l_sum + sm->red[ntiles & 1][half ^ 1][row];
+      const float inv = total > 0.f ? 1.0f / total : 0.f;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {   // 16 tokens per MMA: along K of P inside the swizzle atom, 2048 B down the V tile
-          const uint64_t ad = make_desc(p_addr + (k >> 2) * kPfHalf + (k & 3) * 32, 16, 1024, 2);
-          const uint64_t bd = make_desc(v_addr + k * 2048, kPfHalf, 1024, 2);
-          umma(tmem + 256, ad, bd, idesc_pv, (j > 0 || k > 0));
+      for (int c2 = 0; c2 < 2; ++c2) {
+        float o[32];
+        tmem_ld32(lane_base + 256 + 64 * half + c2 * 32, o);
+        if (row_valid) {
+          uint32_t w[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) w[i >> 1] = pf_pack2<kDtype>(o[i] * inv, o[i + 1] * inv);
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            st16(out_row + (c2 * 4 + c) * 16, make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
         }
-        umma_commit(&sm->bar_o);
-      } else {
-        *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT);
       }
+    } else if ((tid & 31) == 0 && *abort_flag == 0) {
+      *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT);
     }
-    __syncwarp();
-    done_tiles = j + 1;
-  }
-  // ---- epilogue: O / sum -> out
-  bool have = done_tiles == ntiles && *abort_flag == 0;
-  have = __all_sync(0xffffffffu, have);
-  if (have) {
-    bool ok = mbar_wait_or_abort(&sm->bar_o, (ntiles - 1) & 1, abort_flag);
-    ok = __all_sync(0xffffffffu, ok);
-    if (!ok && *abort_flag == 0) { *abort_flag = 1; report(p.status, TKV_DEV_TIMEOUT); }
-    have = ok;
-  }
-  tc_fence_after();
-  if (have) {
-    const float inv = l_sum > 0.f ? 1.0f / l_sum : 0.f;
-#pragma unroll
-    for (int c4 = 0; c4 < 4; ++c4) {
-      float o[32];
-      tmem_ld32(lane_base + 256 + c4 * 32, o);
-      if (row_valid) {
-        uint32_t w[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) w[i >> 1] = pf_pack2<kDtype>(o[i] * inv, o[i + 1] * inv);
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          st16(out_row + (c4 * 4 + c) * 16, make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]));
-      }
-    }
-  }
-  // An aborting CTA drains the copies it started before its shared memory is released.
-  if (tid == 0 && *abort_flag != 0) {
-    for (int i = max(0, k_issued - 2); i < k_issued; ++i) mbar_wait(&sm->bar_k[i & 1], (i >> 1) & 1);
-    for (int i = max(0, v_issued - 2); i < v_issued; ++i) mbar_wait(&sm->bar_v[i & 1], (i >> 1) & 1);
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols));
+  // An aborting CTA drains the copies it started before its shared memory is released.
+  if (tid == kPfSoftmaxThreads && *abort_flag != 0) {
+    for (int i = max(0, k_issued - 2); i < k_issued; ++i) mbar_wait(&sm->bar_k[i & 1], (i >> 1) & 1);
+    for (int i = max(0, v_issued - 2); i < v_issued; ++i) mbar_wait(&sm->bar_v[i & 1], (i >> 1) & 1);
+  }
+  __syncthreads();
+  if (is_ctrl) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kPfTmemCols));
 }
 
 template <int kDtype>
