@@ -86,6 +86,21 @@ def test_argument_errors_are_reported_without_a_gpu(built):
     assert rc == -1                                                            # unknown K/V dtype
     rc = lib.tkv_group_budget(ptr, ptr, ptr, 100, 1, 4000, 1, 0, 1, 10, 0, 0.0, 0, 0, 0, None, ptr, None, None)
     assert rc == -2 and b"segments per group" in lib.tkv_last_error()
+    # the query-resident attention: head_dim 128 and 16-bit only, positive scale, capacity at least the stated length
+    ok = (ptr, 4096, 2048, 128, ptr, ptr, None)
+    assert lib.tkv_prefill_attn(*ok, 300, ptr, 1, 16, 8, 64, 0, 0.1, 300, 8, None, None) == -2      # head_dim 64
+    assert lib.tkv_prefill_attn(*ok, 300, ptr, 1, 16, 8, 128, 2, 0.1, 300, 8, None, None) == -2     # fp32
+    assert lib.tkv_prefill_attn(*ok, 300, ptr, 1, 16, 8, 128, 0, 0.0, 300, 8, None, None) == -1     # scale
+    assert lib.tkv_prefill_attn(*ok, 200, ptr, 1, 16, 8, 128, 0, 0.1, 300, 8, None, None) == -1     # cap < max_len
+    assert lib.tkv_prefill_attn(None, 4096, 2048, 128, ptr, ptr, None, 300, ptr, 1, 16, 8, 128, 0, 0.1, 300, 8, None, None) == -1
+    assert lib.tkv_prefill_attn(*ok, 300, ptr, 0, 16, 8, 128, 0, 0.1, 300, 8, None, None) == 0      # empty batch: nothing to do
+    # the GEMM with the SwiGLU prologue shares the envelope of tkv_skinny_gemm
+    assert lib.tkv_skinny_gemm_swiglu(ptr, ptr, ptr, 33, 2048, 6144, 0, None, None) == -2            # more than 32 rows
+    assert lib.tkv_skinny_gemm_swiglu(ptr, ptr, ptr, 8, 2048, 100, 0, None, None) == -2              # k not a multiple of 64
+    assert lib.tkv_skinny_gemm_swiglu(None, ptr, ptr, 8, 2048, 128, 0, None, None) == -1
+    # the allocation-free attention refuses what does not fit its built-in scratch before touching the device
+    rc = lib.tkv_decode_attn_static(ptr, 8192, 128, ptr, ptr, ptr, None, 8192, ptr, 256, 64, 8, 128, 0, 1.0, 8192, None, None)
+    assert rc == -2 and b"built-in array" in lib.tkv_last_error()
 
 
 def test_cpu_tensors_are_refused():
