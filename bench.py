@@ -555,6 +555,10 @@ def main():
                     help="requests per step of the host-core arm (--impl reference; 0 = the full batch if host memory allows)")
     ap.add_argument("--cpu-sample-batch", type=int, default=2, help="requests in the cpu_baseline sample of the native arm")
     ap.add_argument("--cpu-steps", type=int, default=12)
+    ap.add_argument("--cache", default="per-head", choices=["per-head", "batched-budget"],
+                    help="per-head: TrimKVCache (the benchmark's configuration).  batched-budget: "
+                         "BatchedDynamicBudgetTrimKVCache with strategy 'alpha', the token budget shared between the heads "
+                         "and layers of a request (ragged head lengths; evictions are not bracketed in this mode)")
     ap.add_argument("--no-evict-window", action="store_true",
                     help="do not advance the cache so that an eviction falls inside the timed windows (profiling runs)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
@@ -596,7 +600,13 @@ def main():
     B, P, M, Bf = wl["batch"], wl["prompt"], wl["memory_size"], wl["buffer_size"]
     gen = torch.Generator().manual_seed(1000 + rank)
     prompt = torch.randint(0, cfg.vocab_size, (B, P), generator=gen).pin_memory()
-    cache = TrimKVCache(device=dev, memory_size=M, buffer_size=Bf, num_layers=cfg.num_hidden_layers)
+    flat = args.cache == "batched-budget"
+    if flat:
+        from trimkv_b200 import BatchedDynamicBudgetTrimKVCache
+        cache = BatchedDynamicBudgetTrimKVCache(device=dev)
+        args.no_evict_window = True
+    else:
+        cache = TrimKVCache(device=dev, memory_size=M, buffer_size=Bf, num_layers=cfg.num_hidden_layers)
     with torch.inference_mode():
         out = model(input_ids=prompt.to(dev, non_blocking=True), past_key_values=cache, logits_to_keep=1)
         first = out.logits[:, -1].argmax(-1, keepdim=True)
@@ -655,7 +665,7 @@ def main():
             w0 = time.time()
             e0.record()
             for i in range(args.steps):
-                if cache.get_cache_length(0) + 1 >= M + Bf:
+                if not flat and cache.get_cache_length(0) + 1 >= M + Bf:
                     n_before = cache.get_cache_length(0) + 1
                     comp, cfg.compress_memory = cfg.compress_memory, False
                     step_fn()
@@ -694,7 +704,8 @@ def main():
         attn_events, lens_at_sample = [], []
         for _ in range(4):
             tkv_attn.event_log = []
-            lens_at_sample.append(cache.get_cache_length(0) + 1)
+            # tokens per segment at this step (the budget-sharing cache keeps the layer's total on the host)
+            lens_at_sample.append(cache._rows[0] / (B * cfg.num_key_value_heads) + 1 if flat else cache.get_cache_length(0) + 1)
             # Keep the GPU busy for a few milliseconds first so that the host queues the step's launches ahead of it;
             # otherwise the event pairs would also time the host's dispatch gaps between the two attention kernels.
             torch.cuda._sleep(20_000_000)
@@ -782,7 +793,7 @@ def main():
             "config": {"workload": args.workload, "global_batch": B * (1 if sharded else world), "batch_per_gpu": B, "prompt_len": P,
                        "memory_size": M, "buffer_size": Bf, "parallelism": ((f"kv-head-shard x{world}" + (" (merge kernel pushes to peers)" if args.fused_gather else " (NCCL all-gather)"))
                                        if sharded else f"batch-partition x{world}"),
-                       "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
+                       "cache": args.cache, "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
                        "untimed_steps_before_windows": [pre1, pre2],
                        "evictions_in_windows": len(evict_events),
                        "l2": "per-step working set (all weights + every cached K/V row, many GB) exceeds the 126 MB L2; no explicit flush"},

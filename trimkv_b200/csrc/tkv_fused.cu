@@ -198,13 +198,11 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
                                                           int64_t split_stride, const void* in_bias) {
   using T = T16<kDtype>;
   __shared__ float red[8];
-  grid_dependency_wait();
-  grid_launch_dependents();  // a following weight-streaming GEMM may start fetching weights; it waits before reading `out`
   const int64_t off = (int64_t)blockIdx.x * cols * 2;
   const int nvec = cols / 8;  // 16-byte vectors per row
   float ss = 0.f;
-  // Rows of up to 256 * kKeep vectors (hidden size 8192) stay in registers between the two passes, and the norm
-  // weights (they do not depend on the preceding kernel's output, but their load is cheap) are requested up front.
+  // Rows of up to 256 * kKeep vectors (hidden size 8192) stay in registers between the two passes.  The norm weights
+  // do not depend on the preceding kernel, so they are requested before the dependency wait and arrive under it.
   constexpr int kKeep = 4;
   const bool in_regs = nvec <= 256 * kKeep;
   uint4 keep[kKeep], wkeep[kKeep];
@@ -215,6 +213,8 @@ __global__ void __launch_bounds__(256) add_rmsnorm_kernel(char* residual, const 
       if (i < nvec) wkeep[j] = ld16(reinterpret_cast<const char*>(weight) + (int64_t)i * 16);
     }
   }
+  grid_dependency_wait();
+  grid_launch_dependents();  // a following weight-streaming GEMM may start fetching weights; it waits before reading `out`
   // Pass 1: update the residual stream and accumulate the sum of squares.
   for (int i = threadIdx.x, j = 0; i < nvec; i += 256, ++j) {
     uint4 r = ld16(residual + off + (int64_t)i * 16);
