@@ -559,6 +559,9 @@ def main():
                     help="per-head: TrimKVCache (the benchmark's configuration).  batched-budget: "
                          "BatchedDynamicBudgetTrimKVCache with strategy 'alpha', the token budget shared between the heads "
                          "and layers of a request (ragged head lengths; evictions are not bracketed in this mode)")
+    ap.add_argument("--blas", default="default", choices=["default", "cublas", "cublaslt"],
+                    help="which library entry torch uses for the dense GEMMs of the decode step (torch.backends.cuda."
+                         "preferred_blas_library); the GEMMs are library code either way")
     ap.add_argument("--no-evict-window", action="store_true",
                     help="do not advance the cache so that an eviction falls inside the timed windows (profiling runs)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
@@ -588,6 +591,8 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
 
+    if args.blas != "default":
+        torch.backends.cuda.preferred_blas_library(args.blas)
     from trimkv_b200 import TrimKVCache, attn as tkv_attn, build as tkv_build, ops
     from trimkv_b200.decoder import GreedyDecoder
     if not os.path.exists(tkv_build.LIB) and local == 0:
@@ -793,7 +798,7 @@ def main():
             "config": {"workload": args.workload, "global_batch": B * (1 if sharded else world), "batch_per_gpu": B, "prompt_len": P,
                        "memory_size": M, "buffer_size": Bf, "parallelism": ((f"kv-head-shard x{world}" + (" (merge kernel pushes to peers)" if args.fused_gather else " (NCCL all-gather)"))
                                        if sharded else f"batch-partition x{world}"),
-                       "cache": args.cache, "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
+                       "cache": args.cache, "blas": args.blas, "cuda_graph": dec.use_graph, "fused_layer_kernels": dec.fused is not None,
                        "untimed_steps_before_windows": [pre1, pre2],
                        "evictions_in_windows": len(evict_events),
                        "l2": "per-step working set (all weights + every cached K/V row, many GB) exceeds the 126 MB L2; no explicit flush"},
