@@ -31,6 +31,7 @@ CASES = {
     "qwen3_rg2": ("qwen3", {"retention_gate": "rg2"}, 24),
     "qwen3_rg3": ("qwen3", {"retention_gate": "rg3"}, 24),
     "llama_rg2": ("llama", {"retention_gate": "rg2"}, 24),
+    "phi3_partial_rotary": ("phi3", {"partial_rotary_factor": 0.5}, 24),
 }
 
 
