@@ -114,6 +114,7 @@ def evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group
     assert not knorm and score_dtype == 0 and scores is None, "the emulation covers strategy 'alpha' in fp32"
     k2, v2 = k_cache.view(-1, k_cache.shape[-1]), v_cache.view(-1, v_cache.shape[-1])
     b1, p1, ln = beta_cache.view(-1), pos_cache.view(-1), seg_len.view(-1)
+    keep_cnt = keep_cnt.view(-1) if keep_cnt is not None else None
     for seg in range(nseg):
         n = int(ln[seg])
         if n > max_len:
@@ -153,3 +154,24 @@ def evict_multi(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, gr
     multi_calls.append((nseg, ctas))
     evict_ex(k_cache, v_cache, beta_cache, pos_cache, seg_len, cu_seqlens, group, nseg, cap, q_idx, max_len, None,
              protect_last, memory_size, trigger_len, kept_idx_out, 0, status, knorm)
+
+
+def group_budget(beta_cache, pos_cache, seg_len, cap, groups, inner, n_outer, outer_stride, q_idx, k_total, keep_cnt,
+                 threshold=None, floor_mode=0, floor_cnt=0, status=None, score_dtype=0, scores=None):
+    """Keep counts under a shared budget (fp32 scores; the contract of tkv_group_budget), from the oracle's
+    concatenated top-k: group g = segments {g*inner + o*outer_stride + i}, o outer, i inner."""
+    assert score_dtype == 0 and scores is None, "the emulation covers fp32 scores without key norms"
+    beta, pos, ln, keep = beta_cache.reshape(-1), pos_cache.reshape(-1), seg_len.reshape(-1), keep_cnt.view(-1)
+    for g in range(groups):
+        segs = [g * inner + o * outer_stride + i for o in range(n_outer) for i in range(inner)]
+        sc = []
+        for s in segs:
+            n = int(ln[s])
+            sc.append(orc.retention_scores(beta[s * cap:s * cap + n].numpy(), pos[s * cap:s * cap + n].numpy(), q_idx))
+        counts = orc._group_keep_counts(sc, k_total=k_total, threshold=threshold, bucketize_attribution=(floor_mode == 1))
+        for s, c, x in zip(segs, counts, sc):
+            if floor_mode == 1:
+                c = min(len(x), c + floor_cnt)
+            elif floor_mode == 2:
+                c = max(c, min(floor_cnt, len(x)))
+            keep[s] = c

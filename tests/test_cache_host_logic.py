@@ -20,6 +20,12 @@ def host_cache(monkeypatch):
     return cache_utils.TrimKVCache
 
 
+@pytest.fixture
+def host_flat_caches(host_cache):
+    from trimkv_b200 import cache_utils
+    return cache_utils.BatchedDynamicBudgetTrimKVCache, cache_utils.DynamicBudgetTrimKVCache
+
+
 @pytest.mark.parametrize("eager_handoff", [False, True])
 def test_config1_lockstep_host_logic(host_cache, golden_dir, eager_handoff):
     """benchmark-spec configs[0] (batch 1, 8 KV heads, fp32, M 512, B 128, 4096-token prefill + 256 steps) through the
@@ -105,3 +111,36 @@ def test_one_piece_prompt_beyond_the_selection_limit_is_refused_with_advice(host
     cache.update(k, k, torch.zeros(1, 1, n), torch.arange(n), 0)
     with pytest.raises(ValueError, match="prefill_chunk_size"):
         cache.compress(memory_size=64, buffer_size=8)
+
+
+@pytest.mark.parametrize("ci", range(7))
+def test_flat_budget_classes_host_logic(host_flat_caches, golden_dir, ci):
+    """The budget-sharing classes' own decisions (when a layer or a request fires, the group shapes and budgets they ask
+    for, the floor arithmetic they pass on, the read-back after an eviction) against the reference's classes: head
+    lengths after every step and kept positions at three steps, for `alpha`, `layer_wise_alpha` (with and without a
+    floor), `alpha_threshold` and the batch-1 class."""
+    batched_cls, single_cls = host_flat_caches
+    g = np.load(os.path.join(golden_dir, "flat_budget.npz"))
+    L, B, H, D, S, T, M, Bf = [int(x) for x in g["meta"]]
+    kind, strategy, floor, thr = str(g["cases"][ci]).split("|")
+    floor, thr = float(floor), float(thr)
+    logb = torch.from_numpy(g[f"c{ci}_logb"])
+    bsz = logb.shape[1]
+    cache = (batched_cls if kind == "batched" else single_cls)(device="cpu")
+    for t in range(T + 1):
+        lo, hi = (0, S) if t == 0 else (S + t - 1, S + t)
+        for l in range(L):
+            k = emu.on_device((torch.arange(lo, hi, dtype=torch.float32)[None, None, :, None] + 1000 * l)
+                              .expand(bsz, H, hi - lo, D).contiguous())
+            cache.update(k, (-k).contiguous(), logb[l, :, :, lo:hi].contiguous(), torch.arange(lo, hi), l)
+        cache.compress(strategy=strategy, memory_size=M, buffer_size=Bf, floor_budget_ratio=floor, alpha_threshold=thr,
+                       num_layers=L, num_key_value_heads=H)
+        got = torch.stack([cache.head_lens[l] for l in range(L)]).numpy()
+        assert np.array_equal(got, g[f"c{ci}_lens"][t]), (ci, t)
+        assert cache.get_total_cached_tokens() == int(g[f"c{ci}_lens"][t].sum())
+        if t in (0, T // 2, T):
+            for l in range(L):
+                kp, vp, bp, pp = cache.packed(l)
+                assert np.array_equal(pp[:, 0].numpy(), g[f"c{ci}_pos_t{t}_l{l}"]), (ci, t, l)
+                assert torch.equal(torch.Tensor(kp[:, 0]), pp[:, 0].float() + 1000.0 * l)
+    cache.check_status()
