@@ -351,6 +351,7 @@ def run_micro(args):
     attn  : one layer of decode attention, batch x 8 KV heads, lengths lognormal(median 2048, sigma 1) in [64, 8192].
     append: one token per segment.
     steady: append every step, evict only the segments that reached M+B.
+    generate: generate() of the model classes on --workload, HF loop against fused_decode=True (wall clock per token).
     multi : --q-tokens new tokens per request against M cached ones (a piece of a chunked prefill, multi-token
             decoding): the multi-token kernels beside the library attention, causal and with a length mask.
     Each timed launch works on data that was not touched by the previous one (buffers rotate; each is > L2).
@@ -426,6 +427,33 @@ def run_micro(args):
                     "library_causal_ms": avg_ms(lambda: _dense_causal(qh, k4, v4, D ** -0.5)),
                     "library_masked_ms": avg_ms(lambda: _ragged_causal(qh, k4, v4, lens, D ** -0.5)),
                     "max_abs_diff_vs_library": float((_dense_causal(qh, k4, v4, D ** -0.5).float() - out.float()).abs().max())})
+        print(json.dumps(res))
+        return
+    if args.micro == "generate":
+        # What a user of the model classes sees: tokens per second of generate() after the prompt pass, through the HF
+        # loop over the module-by-module forward and through the fused, graph-replayed step (fused_decode=True).
+        wl = WORKLOADS[args.workload]
+        model, cfg = build_model(wl, dev)
+        ids = torch.randint(0, cfg.vocab_size, (wl["batch"], wl["prompt"]), generator=g, device=dev)
+        mask = torch.ones_like(ids)
+        n_new = max(8, min(64, args.steps))
+
+        def wall(n, **kw):
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            out = model.generate(ids, attention_mask=mask, max_new_tokens=n, do_sample=False, **kw)
+            torch.cuda.synchronize()
+            assert out.shape == (wl["batch"], wl["prompt"] + n)
+            return time.perf_counter() - t0
+
+        res.update({"config": {"workload": args.workload, "batch": wl["batch"], "prompt": wl["prompt"],
+                               "M": wl["memory_size"], "B": wl["buffer_size"], "new_tokens": n_new},
+                    "timing": "wall clock of generate(max_new_tokens=4+n) minus generate(max_new_tokens=4), per token"})
+        for name, kw in (("hf_generate", {}), ("fused_decode", {"fused_decode": True})):
+            wall(4, **kw)                                   # warm-up: workspaces, kernel attributes, fused weights
+            short, full = wall(4, **kw), wall(4 + n_new, **kw)
+            ms = (full - short) / n_new * 1e3
+            res[name] = {"ms_per_step": ms, "tok_per_s": wl["batch"] / (ms * 1e-3), "prompt_pass_and_4_tokens_s": short}
         print(json.dumps(res))
         return
     if args.micro == "steady":
@@ -572,7 +600,7 @@ def run_micro(args):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi", "prefill"],
+    ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi", "prefill", "generate"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
     ap.add_argument("--attn-shape", default="config4", choices=["config4", "config2"])
     ap.add_argument("--M", type=int, default=4096)

@@ -228,6 +228,43 @@ def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, fused_down):
     assert float((b0 - b1).abs().max()) <= 1e-2
 
 
+def test_generate_with_fused_decode():
+    """``generate(..., fused_decode=True)``: greedy decoding through the fused, graph-replayed step.  The module path,
+    fed the tokens it chose, must rate each of them within twice the paths' logit tolerance of its own best token; a
+    second call reuses the fused weights."""
+    from trimkv_b200 import TrimKVCache
+    from trimkv_b200.decoder import GreedyDecoder
+    model, cfg = _tiny(memory_size=64, buffer_size=8, layers=3)
+    model = model.to(DEV)
+    new_tokens, plen = 40, 100
+    prompt = torch.randint(0, cfg.vocab_size, (3, plen), generator=torch.Generator().manual_seed(4)).to(DEV)
+    cache = TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size)
+    ids = model.generate(prompt, max_new_tokens=new_tokens, fused_decode=True, past_key_values=cache)
+    assert ids.shape == (3, plen + new_tokens) and torch.equal(ids[:, :plen], prompt)
+    assert cache.get_seq_length() == plen + new_tokens - 1
+    assert cache.get_cache_length(0) < cfg.memory_size + cfg.buffer_size
+    cache.check_status()
+    with torch.inference_mode():
+        ref_cache = TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size)
+        logits = model(input_ids=prompt, past_key_values=ref_cache, logits_to_keep=1).logits[:, -1].float()
+        dec = GreedyDecoder(model, ref_cache, use_graph=False, fused=False)
+        for t in range(new_tokens):
+            chosen = ids[:, plen + t: plen + t + 1]
+            gap = logits.max(-1, keepdim=True).values - logits.gather(-1, chosen)
+            assert float(gap.max()) <= 4e-2, (t, float(gap.max()))
+            if t + 1 < new_tokens:
+                dec.step(chosen, eager=True)
+                logits = dec.logits.float()
+    fused = {k: v[0].data_ptr() for k, v in model._tkv_fused_weights.items()}
+    again = model.generate(prompt, max_new_tokens=new_tokens, fused_decode=True,
+                           past_key_values=TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size))
+    assert torch.equal(again, ids)
+    assert fused == {k: v[0].data_ptr() for k, v in model._tkv_fused_weights.items()}
+    assert model.generate(prompt, max_new_tokens=5, fused_decode=True).shape == (3, plen + 5)   # cache made by the model
+    with pytest.raises(NotImplementedError):
+        model.float().generate(prompt, max_new_tokens=2, fused_decode=True)
+
+
 @pytest.mark.parametrize("strategy", ["alpha", "layer_wise_alpha"])
 def test_flat_budget_cache_through_the_fused_decoder(strategy):
     """A budget-sharing flat cache stepped by the fused decode step (decode_prep instead of update) across several

@@ -41,11 +41,22 @@ class FusedDecodeStep:
         self.model, self.cache, self.cfg = model, cache, cfg
         self.layers = []
 
+        fused_before = model.__dict__.setdefault("_tkv_fused_weights", {})   # a second decoder of this model reuses them
+
         def fuse(parts):
             """One weight (and bias) for several Linear modules that read the same input; the modules' parameters
             become views of the fused storage."""
             if len(parts) == 1:
                 return parts[0].weight, parts[0].bias
+            key = tuple(id(m) for m in parts)
+            if key in fused_before:
+                w, bias = fused_before[key]
+                off, same = 0, True
+                for m in parts:      # still the views made below (nobody loaded or moved the weights since)?
+                    same = same and m.weight.data_ptr() == w[off:].data_ptr() and m.weight.dtype == w.dtype
+                    off += m.weight.shape[0]
+                if same and off == w.shape[0]:
+                    return w, bias
             w = torch.cat([m.weight for m in parts], 0).contiguous()
             bias = None
             if any(m.bias is not None for m in parts):
@@ -58,6 +69,7 @@ class FusedDecodeStep:
                 if m.bias is not None:
                     m.bias.data = bias[off:off + n]
                 off += n
+            fused_before[key] = (w, bias)
             return w, bias
 
         with torch.no_grad():

@@ -428,12 +428,13 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
             if (c.compress_memory and c.compress_strategy == "alpha") else {}
         return TrimKVCache(max_seq_len=c.max_seq_len, device=device or self.device, **hints)
 
-    def generate(self, inputs=None, *args, prefill_chunk_size=None, **kwargs):
+    def generate(self, inputs=None, *args, prefill_chunk_size=None, fused_decode=False, **kwargs):
         """HF ``generate`` with a ``TrimKVCache`` (the reference's usage, examples/test_qwen3.py:51-55); a cache is
-        created if none is passed.  ``prefill_chunk_size`` selects ``generate_greedy`` (chunked prompt pass)."""
-        if prefill_chunk_size:
+        created if none is passed.  ``prefill_chunk_size`` (chunked prompt pass) or ``fused_decode=True`` (the fused
+        CUDA decode step replayed from a CUDA graph) select ``generate_greedy`` instead of the HF loop."""
+        if prefill_chunk_size or fused_decode:
             ids = inputs if inputs is not None else kwargs.pop("input_ids")
-            return self.generate_greedy(ids, prefill_chunk_size=prefill_chunk_size,
+            return self.generate_greedy(ids, prefill_chunk_size=prefill_chunk_size, fused_decode=fused_decode,
                                         **{k: v for k, v in kwargs.items()
                                            if k in ("max_new_tokens", "past_key_values", "eos_token_id")})
         if kwargs.get("past_key_values") is None:
@@ -443,8 +444,13 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
 
     @torch.inference_mode()
     def generate_greedy(self, input_ids, max_new_tokens=16, past_key_values=None, eos_token_id=None,
-                        prefill_chunk_size=None):
+                        prefill_chunk_size=None, fused_decode=False):
         """Greedy decoding without the HF machinery; returns ``[B, prompt + new]`` token ids.
+
+        ``fused_decode``: decode through ``decoder.GreedyDecoder`` (ten fused launches per layer, one CUDA graph per
+        step, the next token fed back on the device) instead of the module-by-module forward.  Same arithmetic up to
+        the summation order of the kernels, several times faster; needs a CUDA model in bf16/f16 of a shape the fused
+        step covers (``FusedDecodeStep.supports``) and raises otherwise.
 
         ``prefill_chunk_size``: feed the prompt in pieces of that many tokens, evicting after each piece (the model
         calls ``compress`` at the end of every forward), so that a prompt much longer than ``memory_size`` never has
@@ -461,6 +467,27 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
         tokens = [input_ids]
         nxt = out.logits[:, -1].argmax(-1, keepdim=True)
         done = torch.zeros_like(nxt, dtype=torch.bool)
+        if fused_decode:
+            from .decoder import FusedDecodeStep, GreedyDecoder
+            if not (input_ids.is_cuda and FusedDecodeStep.supports(self)
+                    and self.lm_head.weight.dtype in (torch.bfloat16, torch.float16)):
+                raise NotImplementedError("fused_decode needs a CUDA model in bf16/f16 with head_dim 128, the 'rg' gate and SiLU")
+            dec = GreedyDecoder(self, past_key_values, use_graph=True, fused=True)
+            dec.ids.copy_(nxt)
+            try:
+                for i in range(max_new_tokens):
+                    tokens.append(nxt)
+                    if eos_token_id is not None:
+                        done |= nxt == eos_token_id
+                        if bool(done.all()):
+                            break
+                    if i + 1 == max_new_tokens:
+                        break
+                    nxt = dec.step(eager=(i < 2)).clone()   # two plain steps size the workspaces before the capture
+            finally:
+                dec.release_graph()
+                past_key_values.static_views = False
+            return torch.cat(tokens, dim=1)
         for i in range(max_new_tokens):
             tokens.append(nxt)
             if eos_token_id is not None:
