@@ -22,6 +22,7 @@ constexpr int kMaxSelectLen = 57000;         // keys must fit in 227 KB of share
 
 constexpr int kEvictThreadsWide = 512;       // for long segments, whose key array allows fewer CTAs per SM
 constexpr int kMoveThreads = 256;            // evict_move_kernel: its staging area limits CTAs per SM, so each is wide
+constexpr int kMoveGridCtas = 148 * 4;       // evict_move_kernel: blocks in its grid (they loop over the evicting segments)
 constexpr int kEvictThreadsPlan = 1024;      // selection only (plan mode): few segments, so each gets a full CTA
 struct SelectScratch {
   int hist[256];
@@ -215,6 +216,8 @@ struct EvictParams {
   // moves} go to global memory and nothing is moved here.
   int32_t* plan; int32_t* plan_kept; int64_t plan_stride;
   int32_t* plan_tail; int ctas, tail_max;   // plan_tail[seg, c]: first row of CTA c's range that it must stage
+  int32_t* fired_count; int32_t* fired;     // segments that evict, in the order they finished selecting; *fired_count
+                                            // holds their number minus one (the workspace is preset to 0xFF bytes)
 };
 
 template <int kThreads>
@@ -263,7 +266,10 @@ __global__ void __launch_bounds__(kThreads, 1024 / kThreads) evict_inplace_kerne
     for (int j = threadIdx.x; j < m; j += kThreads) p.kept_idx_out[(int64_t)seg * p.m + j] = kept[j];
   if (p.plan != nullptr) {
     for (int j = j0 + threadIdx.x; j < m; j += kThreads) p.plan_kept[(int64_t)seg * p.plan_stride + j] = kept[j];
-    if (threadIdx.x == 0) { p.plan[2 * seg] = m; p.plan[2 * seg + 1] = min(j0, m); }
+    if (threadIdx.x == 0) {
+      p.plan[2 * seg] = m; p.plan[2 * seg + 1] = min(j0, m);
+      p.fired[atomicAdd(p.fired_count, 1) + 1] = seg;
+    }
     if ((int)threadIdx.x < p.ctas) {
       // First row of the range whose source the right neighbour may overwrite (kept is ascending).  The last CTA
       // with rows has no such neighbour: sources at or beyond m are written by nobody.
@@ -333,6 +339,7 @@ struct MoveParams {
   int64_t cap; int row_vecs; int ctas; int tail_max;
   const int32_t* plan; const int32_t* plan_tail; const int32_t* kept; int64_t kept_stride;
   int32_t* flags; int32_t* status;
+  const int32_t* fired_count; const int32_t* fired;
 };
 
 __device__ __forceinline__ int ld_acquire(const int32_t* p) {
@@ -344,11 +351,9 @@ __device__ __forceinline__ void st_release(int32_t* p, int v) {
   asm volatile("st.release.gpu.global.b32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-__global__ void __launch_bounds__(kMoveThreads) evict_move_kernel(MoveParams p) {
+// CTA c's share of one evicting segment.  Every return is taken by the whole CTA.
+__device__ __forceinline__ void move_segment_part(const MoveParams& p, const int seg, const int c, uint4* tail_kv, int& s_ok) {
   constexpr int kThreads = kMoveThreads;
-  extern __shared__ __align__(16) uint4 tail_kv[];   // [tail_max][2 * row_vecs], then beta[tail_max], pos[tail_max]
-  __shared__ int s_ok;
-  const int seg = blockIdx.y, c = blockIdx.x;
   const int m = p.plan[2 * seg];
   if (m < 0) return;                                  // this segment keeps everything
   const int j0 = p.plan[2 * seg + 1];
@@ -463,6 +468,20 @@ __global__ void __launch_bounds__(kMoveThreads) evict_move_kernel(MoveParams p) 
     p.beta[row0 + jt + r] = tail_beta[r]; p.pos[row0 + jt + r] = tail_pos[r];
   }
   if (c == 0 && threadIdx.x == 0) p.seg_len[seg] = m;
+}
+
+// Grid (ctas, Y): the CTAs with blockIdx.y = y take the evicting segments fired[y], fired[y + Y], ... in turn, so the
+// grid is sized by the SMs and not by the segments: when one segment in a hundred evicts (the steady state), a grid of
+// ctas x nseg blocks would spend its time launching blocks that find nothing to do.  CTA (c, y) still waits only for
+// CTA (c-1, y) working on the same segment, which has a lower block index and handles its segments in the same order.
+__global__ void __launch_bounds__(kMoveThreads) evict_move_kernel(MoveParams p) {
+  extern __shared__ __align__(16) uint4 tail_kv[];   // [tail_max][2 * row_vecs], then beta[tail_max], pos[tail_max]
+  __shared__ int s_ok;
+  const int count = *p.fired_count + 1;
+  for (int i = blockIdx.y; i < count; i += gridDim.y) {
+    move_segment_part(p, p.fired[i], blockIdx.x, tail_kv, s_ok);
+    __syncthreads();   // the staging area and s_ok are reused by the next segment
+  }
 }
 
 struct SelectParams {
@@ -622,10 +641,12 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   p.score_dtype = score_dtype; p.scores = scores;
   p.kept_idx_out = kept_idx_out; p.status = status;
   p.plan = nullptr; p.plan_kept = nullptr; p.plan_stride = 0; p.plan_tail = nullptr; p.ctas = 1; p.tail_max = 0;
+  p.fired_count = nullptr; p.fired = nullptr;
   MoveParams mp;
   size_t move_smem = 0;
   if (ctas > 1) {
-    // Workspace: flags [nseg, ctas] | plan [nseg, 2] | plan_tail [nseg, ctas] | kept [nseg, memory_size], all int32.
+    // Workspace: flags [nseg, ctas] | plan [nseg, 2] | fired count [1] | fired [nseg] | plan_tail [nseg, ctas] |
+    // kept [nseg, memory_size], all int32.
     if (keep_cnt != nullptr) return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: per-segment keep counts are not supported");
     if (ctas > kEvictMaxCtas || nseg > 65535)
       return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: ctas_per_segment=%d (limit %d), nseg=%d (limit 65535)", ctas, kEvictMaxCtas, nseg);
@@ -637,13 +658,15 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
     if (mp.tail_max <= 0 || move_smem > 200 * 1024)
       return fail(TKV_ERR_UNSUPPORTED, "tkv_evict_multi: max_len - memory_size = %d rows do not fit the staging area", mp.tail_max);
     int32_t* w = (int32_t*)workspace;
-    mp.flags = w; p.plan = w + (int64_t)nseg * ctas; p.plan_tail = p.plan + 2 * (int64_t)nseg;
+    mp.flags = w; p.plan = w + (int64_t)nseg * ctas; p.fired_count = p.plan + 2 * (int64_t)nseg; p.fired = p.fired_count + 1;
+    p.plan_tail = p.fired + nseg; mp.fired_count = p.fired_count; mp.fired = p.fired;
     p.plan_kept = p.plan_tail + (int64_t)nseg * ctas; p.plan_stride = memory_size;
     p.ctas = ctas; p.tail_max = mp.tail_max; mp.plan_tail = p.plan_tail;
     mp.k = p.k; mp.v = p.v; mp.beta = p.beta; mp.pos = p.pos; mp.seg_len = seg_len; mp.cap = cap; mp.row_vecs = p.row_vecs;
     mp.ctas = ctas; mp.plan = p.plan; mp.kept = p.plan_kept; mp.kept_stride = memory_size; mp.status = status;
-    // flags = -1 (not raised), plan = -1 (segment keeps everything) until the selection says otherwise
-    cudaError_t e = cudaMemsetAsync(workspace, 0xFF, ((size_t)nseg * ctas + 2 * (size_t)nseg) * 4, (cudaStream_t)stream);
+    // flags = -1 (not raised), plan = -1 (segment keeps everything), fired count = -1 (none) until the selection says
+    // otherwise
+    cudaError_t e = cudaMemsetAsync(workspace, 0xFF, ((size_t)nseg * ctas + 2 * (size_t)nseg + 1) * 4, (cudaStream_t)stream);
     if (e != cudaSuccess) return fail(TKV_ERR_LAUNCH, "tkv_evict_multi: memset: %s", cudaGetErrorString(e));
   }
   const size_t smem = (size_t)max_len * 4;
@@ -664,7 +687,8 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
   if (ctas > 1) {
     rc = set_smem(evict_move_kernel, move_smem, "tkv_evict_multi");
     if (rc != TKV_OK) return rc;
-    evict_move_kernel<<<dim3((unsigned)ctas, (unsigned)nseg), kMoveThreads, move_smem, (cudaStream_t)stream>>>(mp);
+    const int rows_y = nseg < kMoveGridCtas / ctas ? nseg : kMoveGridCtas / ctas;
+    evict_move_kernel<<<dim3((unsigned)ctas, (unsigned)rows_y), kMoveThreads, move_smem, (cudaStream_t)stream>>>(mp);
     rc = check_launch("tkv_evict_multi");
     if (rc != TKV_OK) return rc;
   }
@@ -673,7 +697,7 @@ static int evict_impl(void* k_cache, void* v_cache, float* beta_cache, int32_t* 
 
 extern "C" int64_t tkv_evict_multi_workspace_bytes(int nseg, int memory_size, int ctas_per_segment) {
   if (nseg < 0 || memory_size <= 0 || ctas_per_segment <= 0) return 0;
-  return (2 * (int64_t)nseg * ctas_per_segment + 2 * (int64_t)nseg + (int64_t)nseg * memory_size) * 4;
+  return (2 * (int64_t)nseg * ctas_per_segment + 3 * (int64_t)nseg + 1 + (int64_t)nseg * memory_size) * 4;
 }
 
 extern "C" int tkv_evict_multi(void* k_cache, void* v_cache, float* beta_cache, int32_t* pos_cache,
