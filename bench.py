@@ -431,7 +431,8 @@ def run_micro(args):
         return
     if args.micro == "generate":
         # What a user of the model classes sees: tokens per second of generate() after the prompt pass, through the HF
-        # loop over the module-by-module forward and through the fused, graph-replayed step (fused_decode=True).
+        # loop over the module-by-module forward, the HF loop with config.fused_decode_step (the fused step, launched
+        # from Python), and the fused, graph-replayed step (fused_decode=True).
         wl = WORKLOADS[args.workload]
         model, cfg = build_model(wl, dev)
         ids = torch.randint(0, cfg.vocab_size, (wl["batch"], wl["prompt"]), generator=g, device=dev)
@@ -449,7 +450,9 @@ def run_micro(args):
         res.update({"config": {"workload": args.workload, "batch": wl["batch"], "prompt": wl["prompt"],
                                "M": wl["memory_size"], "B": wl["buffer_size"], "new_tokens": n_new},
                     "timing": "wall clock of generate(max_new_tokens=4+n) minus generate(max_new_tokens=4), per token"})
-        for name, kw in (("hf_generate", {}), ("fused_decode", {"fused_decode": True})):
+        for name, kw, flag in (("hf_generate", {}, False), ("hf_generate_fused_step", {}, True),
+                               ("fused_decode", {"fused_decode": True}, False)):
+            model.config.fused_decode_step = flag           # True: one-token forward passes run as the fused CUDA step
             wall(4, **kw)                                   # warm-up: workspaces, kernel attributes, fused weights
             short, full = wall(4, **kw), wall(4 + n_new, **kw)
             ms = (full - short) / n_new * 1e3

@@ -144,3 +144,26 @@ def test_flat_budget_classes_host_logic(host_flat_caches, golden_dir, ci):
                 assert np.array_equal(pp[:, 0].numpy(), g[f"c{ci}_pos_t{t}_l{l}"]), (ci, t, l)
                 assert torch.equal(torch.Tensor(kp[:, 0]), pp[:, 0].float() + 1000.0 * l)
     cache.check_status()
+
+
+def test_caches_are_freed_by_their_last_reference(host_flat_caches, host_cache):
+    """No reference cycle inside a cache: gigabytes of slabs must not wait for the cycle collector."""
+    import gc
+    import weakref
+    gc.collect()
+    gc.disable()
+    try:
+        for cls in (host_cache,) + tuple(host_flat_caches):
+            c = cls(device="cpu")
+            k = emu.on_device(torch.randn(1, 2, 10, 16))
+            c.update(k, k.clone(), emu.on_device(torch.zeros(1, 2, 10)), torch.arange(10), 0)
+            c.compress(strategy="alpha", memory_size=4, buffer_size=2, num_layers=1, num_key_value_heads=2)
+            views = c.key_cache
+            assert views[0].shape[-1] == 16
+            alive = weakref.ref(c)
+            del c
+            assert alive() is None, cls.__name__
+            with pytest.raises(ReferenceError):
+                views[0]
+    finally:
+        gc.enable()

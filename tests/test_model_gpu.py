@@ -228,6 +228,75 @@ def test_fused_decode_step_matches_module_path(use_graph, tc_gemm, fused_down):
     assert float((b0 - b1).abs().max()) <= 1e-2
 
 
+def _module_path_rates_choices(model, cfg, prompt, ids, new_tokens):
+    """The module path, fed the tokens another path chose greedily, must rate each of them within twice the paths'
+    logit tolerance of its own best token."""
+    from trimkv_b200 import TrimKVCache
+    from trimkv_b200.decoder import GreedyDecoder
+    plen = prompt.shape[1]
+    with torch.inference_mode():
+        ref_cache = TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size)
+        logits = model(input_ids=prompt, past_key_values=ref_cache, logits_to_keep=1).logits[:, -1].float()
+        dec = GreedyDecoder(model, ref_cache, use_graph=False, fused=False)
+        for t in range(new_tokens):
+            chosen = ids[:, plen + t: plen + t + 1]
+            gap = logits.max(-1, keepdim=True).values - logits.gather(-1, chosen)
+            assert float(gap.max()) <= 4e-2, (t, float(gap.max()))
+            if t + 1 < new_tokens:
+                dec.step(chosen, eager=True)
+                logits = dec.logits.float()
+
+
+def test_hf_generate_through_the_fused_step():
+    """``config.fused_decode_step = True``: HF ``generate`` (greedy, then sampling) whose one-token forward passes run
+    as the fused CUDA step; without the flag the module path runs and no fused step is built."""
+    from trimkv_b200 import TrimKVCache
+    model, cfg = _tiny(memory_size=64, buffer_size=8, layers=3)
+    model = model.to(DEV)
+    new_tokens, plen = 40, 100
+    prompt = torch.randint(0, cfg.vocab_size, (3, plen), generator=torch.Generator().manual_seed(6)).to(DEV)
+    mask = torch.ones_like(prompt)
+    kw = dict(attention_mask=mask, max_new_tokens=new_tokens, pad_token_id=0)
+    model.generation_config.eos_token_id = model.config.eos_token_id = None      # no early stop
+    plain = TrimKVCache(device=DEV)
+    model.generate(prompt, do_sample=False, past_key_values=plain, **kw)
+    assert "_fused_step" not in plain.__dict__
+    model.config.fused_decode_step = True
+    cache = TrimKVCache(device=DEV)
+    ids = model.generate(prompt, do_sample=False, past_key_values=cache, **kw)
+    assert "_fused_step" in cache.__dict__
+    assert ids.shape == (3, plen + new_tokens) and torch.equal(ids[:, :plen], prompt)
+    assert cache.get_seq_length() == plen + new_tokens - 1
+    assert cache.get_cache_length(0) < cfg.memory_size + cfg.buffer_size
+    cache.check_status()
+    _module_path_rates_choices(model, cfg, prompt, ids, new_tokens)
+    assert model.config.fused_decode_step is True                  # the module-path decoder put the flag back
+    torch.manual_seed(0)
+    cache = TrimKVCache(device=DEV)
+    sampled = model.generate(prompt, do_sample=True, temperature=0.8, top_k=20, past_key_values=cache, **kw)
+    assert sampled.shape == (3, plen + new_tokens) and int(sampled.max()) < cfg.vocab_size
+    cache.check_status()
+    # a forward pass the fused step does not cover takes the module path
+    out = model(input_ids=ids[:, -1:], past_key_values=cache, output_hidden_states=True)
+    assert out.logits.shape == (3, 1, cfg.vocab_size)
+    # a cache that carries a fused step is still freed by its last reference (no cycle for the collector to find)
+    import gc
+    import weakref
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.inference_mode():
+            c = TrimKVCache(device=DEV)
+            model(input_ids=prompt, past_key_values=c, logits_to_keep=1)
+            model(input_ids=prompt[:, :1], past_key_values=c)
+        assert "_fused_step" in c.__dict__
+        alive = weakref.ref(c)
+        del c
+        assert alive() is None
+    finally:
+        gc.enable()
+
+
 def test_generate_with_fused_decode():
     """``generate(..., fused_decode=True)``: greedy decoding through the fused, graph-replayed step.  The module path,
     fed the tokens it chose, must rate each of them within twice the paths' logit tolerance of its own best token; a
@@ -244,17 +313,7 @@ def test_generate_with_fused_decode():
     assert cache.get_seq_length() == plen + new_tokens - 1
     assert cache.get_cache_length(0) < cfg.memory_size + cfg.buffer_size
     cache.check_status()
-    with torch.inference_mode():
-        ref_cache = TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size)
-        logits = model(input_ids=prompt, past_key_values=ref_cache, logits_to_keep=1).logits[:, -1].float()
-        dec = GreedyDecoder(model, ref_cache, use_graph=False, fused=False)
-        for t in range(new_tokens):
-            chosen = ids[:, plen + t: plen + t + 1]
-            gap = logits.max(-1, keepdim=True).values - logits.gather(-1, chosen)
-            assert float(gap.max()) <= 4e-2, (t, float(gap.max()))
-            if t + 1 < new_tokens:
-                dec.step(chosen, eager=True)
-                logits = dec.logits.float()
+    _module_path_rates_choices(model, cfg, prompt, ids, new_tokens)
     fused = {k: v[0].data_ptr() for k, v in model._tkv_fused_weights.items()}
     again = model.generate(prompt, max_new_tokens=new_tokens, fused_decode=True,
                            past_key_values=TrimKVCache(device=DEV, memory_size=cfg.memory_size, buffer_size=cfg.buffer_size))

@@ -17,6 +17,7 @@ There is no CPU path: tensors must live on a CUDA device.
 """
 from __future__ import annotations
 
+import weakref
 from typing import Any, Dict, Iterable, List, Optional, Tuple
 
 import torch
@@ -33,7 +34,16 @@ class _LayerViews:
     """List-like accessor (``cache.key_cache[layer]``) that builds views of the slabs on demand."""
 
     def __init__(self, cache: "TrimKVCache", kind: str):
-        self._cache, self._kind = cache, kind
+        # Weak: the cache owns these accessors, and a reference back would make every cache (gigabytes of slabs) wait
+        # for the cycle collector instead of being freed when its last user drops it.
+        self._ref, self._kind = weakref.ref(cache), kind
+
+    @property
+    def _cache(self) -> "TrimKVCache":
+        cache = self._ref()
+        if cache is None:
+            raise ReferenceError("the cache this accessor belongs to no longer exists")
+        return cache
 
     def __len__(self):
         return len(self._cache)

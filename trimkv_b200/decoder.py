@@ -8,6 +8,7 @@ eviction (`cache.compress`) stays outside the graph because the host decides whe
 from __future__ import annotations
 
 import os
+import weakref
 from typing import Optional
 
 import torch
@@ -38,7 +39,9 @@ class FusedDecodeStep:
         cfg = model.config
         if not self.supports(model):
             raise NotImplementedError("fused decode step needs head_dim 128 (fully rotated), retention_gate 'rg' and SiLU")
-        self.model, self.cache, self.cfg = model, cache, cfg
+        # The cache is held weakly: a step may be stored on its cache (TrimKVForCausalLM.forward does), and a strong
+        # reference back would keep gigabytes of slabs alive until the cycle collector happens to run.
+        self.model, self._cache, self.cfg = model, weakref.ref(cache), cfg
         self.layers = []
 
         fused_before = model.__dict__.setdefault("_tkv_fused_weights", {})   # a second decoder of this model reuses them
@@ -89,6 +92,13 @@ class FusedDecodeStep:
         # shape, batch 32): converting the activation tiles inside the GEMM's pipeline costs more than the launch it saves.
         self.use_tc_gemm, self.fused_down = tc_gemm, fused_down
         self._partials = {}
+
+    @property
+    def cache(self) -> TrimKVCache:
+        cache = self._cache()
+        if cache is None:
+            raise RuntimeError("the cache this decode step was built for no longer exists")
+        return cache
 
     def _gemm(self, x, w, tag):
         """x [B, K] @ w [N, K].T through the weight-streaming tensor-core kernel; returns (partials, splits), or
@@ -185,11 +195,12 @@ class GreedyDecoder:
             self.logits = self.fused(self.ids, self.pos)
         else:
             compress, cfg.compress_memory = cfg.compress_memory, False  # eviction is driven from step()
+            auto, cfg.fused_decode_step = getattr(cfg, "fused_decode_step", False), False   # this branch is the module path
             try:
                 out = self.model(input_ids=self.ids, past_key_values=self.cache, cache_position=self.pos,
                                  logits_to_keep=1)
             finally:
-                cfg.compress_memory = compress
+                cfg.compress_memory, cfg.fused_decode_step = compress, auto
             self.logits = out.logits[:, -1]
         self.next_ids.copy_(self.logits.argmax(-1, keepdim=True))
         self.ids.copy_(self.next_ids)

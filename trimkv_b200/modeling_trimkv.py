@@ -371,13 +371,17 @@ class TrimKVModel(TrimKVPreTrainedModel):
         for layer in self.layers[: self.config.num_hidden_layers]:
             hidden_states = layer(hidden_states, position_embeddings, past_key_values, cache_position)
         hidden_states = self.norm(hidden_states)
+        self.compress_after_forward(past_key_values)
+        return BaseModelOutputWithPast(last_hidden_state=hidden_states, past_key_values=past_key_values)
+
+    def compress_after_forward(self, past_key_values) -> None:
+        """The eviction check that ends every forward pass (modeling_trimkv_qwen3.py:751-760)."""
         if self.config.compress_memory:
             extra = {name: getattr(self.config, name) for name in self.compress_extra}
             past_key_values.compress(
                 strategy=self.config.compress_strategy, memory_size=self.config.memory_size,
                 buffer_size=self.config.buffer_size, floor_budget_ratio=self.config.floor_budget_ratio,
                 num_layers=self.config.num_hidden_layers, num_key_value_heads=self.config.num_key_value_heads, **extra)
-        return BaseModelOutputWithPast(last_hidden_state=hidden_states, past_key_values=past_key_values)
 
 
 class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
@@ -409,8 +413,39 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
     def set_decoder(self, decoder):
         self.model = decoder
 
+    def _fused_step_for(self, input_ids, past_key_values, inputs_embeds, kwargs):
+        """The fused CUDA decode step for this call, or None.  Opt-in (``config.fused_decode_step = True``): a forward
+        pass of one new token per request on a cache that holds the prompt then runs as ten fused launches per layer
+        (``decoder.FusedDecodeStep``) instead of module by module, under HF ``generate`` as under a hand-written loop;
+        same arithmetic up to the summation order of the kernels.  Anything the fused step does not cover (other
+        shapes or dtypes, ``inputs_embeds``, hidden-state or attention outputs, CPU) takes the module path."""
+        if not getattr(self.config, "fused_decode_step", False) or input_ids is None or inputs_embeds is not None:
+            return None
+        if input_ids.dim() != 2 or input_ids.shape[1] != 1 or not input_ids.is_cuda or self.training:
+            return None
+        if kwargs.get("output_attentions") or kwargs.get("output_hidden_states") or kwargs.get("labels") is not None:
+            return None
+        cache = past_key_values
+        if (not isinstance(cache, TrimKVCache) or cache.get_seq_length() == 0
+                or getattr(cache, "_batch", None) != input_ids.shape[0]):
+            return None
+        from .decoder import FusedDecodeStep
+        if self.lm_head.weight.dtype not in (torch.bfloat16, torch.float16) or not FusedDecodeStep.supports(self):
+            return None
+        step = cache.__dict__.get("_fused_step")
+        if step is None or step.model is not self:
+            step = cache.__dict__["_fused_step"] = FusedDecodeStep(self, cache)
+        return step
+
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None, inputs_embeds=None,
                 use_cache=None, cache_position=None, logits_to_keep=0, **kwargs):
+        step = self._fused_step_for(input_ids, past_key_values, inputs_embeds, kwargs)
+        if step is not None:
+            pos = cache_position[-1:] if cache_position is not None else torch.full(
+                (1,), past_key_values.get_seq_length(), device=input_ids.device)
+            logits = step(input_ids, pos.to(torch.int64))
+            self.model.compress_after_forward(past_key_values)
+            return CausalLMOutputWithPast(logits=logits[:, None, :], past_key_values=past_key_values)
         out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
                          past_key_values=past_key_values, inputs_embeds=inputs_embeds, use_cache=use_cache,
                          cache_position=cache_position)
