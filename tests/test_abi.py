@@ -70,7 +70,7 @@ def test_argument_errors_are_reported_without_a_gpu(built):
     rc = lib.tkv_evict_multi(ptr, ptr, ptr, ptr, ptr, None, 1, 1, 4224, 128, 0, 1, 4096, 4224, 4224, 0, 0, 4, None, 0,
                              None, None, None)
     assert rc == -1 and b"workspace" in lib.tkv_last_error()
-    assert lib.tkv_evict_multi_workspace_bytes(8, 4096, 16) == (2 * 8 * 16 + 2 * 8 + 8 * 4096) * 4
+    assert lib.tkv_evict_multi_workspace_bytes(8, 4096, 16) == (2 * 8 * 16 + 3 * 8 + 1 + 8 * 4096) * 4
     # the ragged entry point's workspace holds the dense workspace plus one 8-byte item per possible chunk
     dense = lib.tkv_decode_attn_workspace_bytes(64, 32, 8, 128, 8192)
     ragged = lib.tkv_decode_attn_ragged_workspace_bytes(64, 32, 8, 128, 8192, 1_000_000)

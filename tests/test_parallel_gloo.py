@@ -90,7 +90,10 @@ def _shard_worker(rank, world, port, q):
         torch.manual_seed(0)
         model = TrimKVQwen3ForCausalLM(cfg).eval()
         hkv_l, hq_l, d = cfg.num_key_value_heads // world, cfg.num_attention_heads // world, 128
-        step = HeadShardedDecodeStep(model, types.SimpleNamespace(_hkv=hkv_l), group=None)
+        class _CacheStub:                      # what the step reads of a cache at construction (it holds it weakly)
+            _hkv = hkv_l
+        stub = _CacheStub()
+        step = HeadShardedDecodeStep(model, stub, group=None)
         h = torch.randn(3, cfg.hidden_size)
         ok = True
         for l, (layer, w, bias, _, _) in enumerate(step.layers):
