@@ -99,3 +99,71 @@ def test_ranges_shorter_than_the_largest_displacement_are_unsafe():
     outcomes = [simulate(700, 600, 32, 8, seed, enforce_min=False) for seed in range(60)]
     assert any(o is not None for o in outcomes)
     assert all(simulate(700, 600, 32, 8, seed) is None for seed in range(60))
+
+
+def simulate_grid(nseg_evicting, n, m, ctas, rows_y, resident, tile_rows, seed):
+    """The whole move kernel: a grid of ctas x rows_y blocks, block (c, y) taking the evicting segments y, y + rows_y, ...
+    in turn (``evict_move_kernel``'s loop over the list written by the selection kernel), with at most ``resident``
+    blocks on the device at once, dispatched in index order as earlier ones finish."""
+    rng = random.Random(seed)
+    nprng = np.random.default_rng(seed)
+    kept, mem, progs_of = [], [], {}
+    for s in range(nseg_evicting):
+        kp = np.sort(nprng.choice(n, size=m, replace=False))
+        moved = np.nonzero(kp != np.arange(m))[0]
+        j0 = int(moved[0]) if moved.size else m
+        kept.append(kp); mem.append(np.arange(n))
+        for c in range(ctas):
+            progs_of[(s, c)] = cta_program(kp, m, j0, ctas, n - m, tile_rows, c)
+    blocks = [(c, y) for y in range(rows_y) for c in range(ctas)]            # linear block index: x fastest
+    prog = {}
+    for (c, y) in blocks:
+        steps = [("start", None, None)]
+        for s in range(y, nseg_evicting, rows_y):
+            steps += [(kind, rows, s) for kind, rows in progs_of[(s, c)] if kind != "start"]
+        prog[(c, y)] = steps
+    pc = {b: 0 for b in blocks}
+    flag, held = set(), {b: dict() for b in blocks}
+    dispatched, next_block = [], 0
+    while True:
+        dispatched = [b for b in dispatched if pc[b] < len(prog[b])]
+        while len(dispatched) < resident and next_block < len(blocks):
+            dispatched.append(blocks[next_block]); next_block += 1
+        if not dispatched:
+            break
+        runnable = []
+        for b in dispatched:
+            kind, _, s = prog[b][pc[b]]
+            if kind == "wait" and (s, b[0] - 1) not in flag:
+                continue
+            runnable.append(b)
+        assert runnable, "dead-lock"
+        b = rng.choice(runnable)
+        kind, rows, s = prog[b][pc[b]]
+        if kind == "load":
+            for j in rows:
+                if mem[s][kept[s][j]] != kept[s][j]:
+                    return f"block {b} read row {kept[s][j]} of segment {s} after it was overwritten"
+                held[b][(s, j)] = mem[s][kept[s][j]]
+        elif kind == "store":
+            for j in rows:
+                mem[s][j] = held[b].pop((s, j))
+        elif kind == "flag":
+            flag.add((s, b[0]))
+        pc[b] += 1
+    for s in range(nseg_evicting):
+        if not np.array_equal(mem[s][:m], kept[s]):
+            return f"segment {s}: result is not the stable compaction"
+    return None
+
+
+@pytest.mark.parametrize("nseg_evicting,n,m,ctas,rows_y,resident", [
+    (16, 640, 512, 4, 37, 444),      # fewer evicting segments than rows of the grid: some blocks find nothing to do
+    (9, 640, 512, 4, 4, 16),         # every block walks two or three segments
+    (9, 640, 512, 4, 4, 5),          # fewer resident blocks than the grid holds: later blocks start as earlier ones end
+    (7, 200, 150, 8, 3, 9),
+    (5, 133, 100, 8, 2, 1),          # one block at a time: strictly in index order
+])
+def test_blocks_walking_a_list_of_segments_cannot_dead_lock(nseg_evicting, n, m, ctas, rows_y, resident):
+    for seed in range(12):
+        assert simulate_grid(nseg_evicting, n, m, ctas, rows_y, resident, 16, seed) is None
