@@ -639,6 +639,9 @@ def main():
     ap.add_argument("--blas", default="default", choices=["default", "cublas", "cublaslt"],
                     help="which library entry torch uses for the dense GEMMs of the decode step (torch.backends.cuda."
                          "preferred_blas_library); the GEMMs are library code either way")
+    ap.add_argument("--tc-gemm", default="",
+                    help="comma-separated subset of qkvg,o,gu,down: projections of the decode step that run on "
+                         "tkv_skinny_gemm instead of the library GEMM")
     ap.add_argument("--no-evict-window", action="store_true",
                     help="do not advance the cache so that an eviction falls inside the timed windows (profiling runs)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
@@ -700,7 +703,8 @@ def main():
             torch.cuda.empty_cache()
         dec = GreedyDecoder(model, cache, use_graph=not args.no_graph, fused=not args.no_fused,
                             head_shard_group=dist.group.WORLD if sharded else None,
-                            fused_gather=sharded and args.fused_gather)
+                            fused_gather=sharded and args.fused_gather,
+                            tc_gemm=frozenset(t for t in args.tc_gemm.split(",") if t))
         dec.ids.copy_(first)
         clocks = ClockSampler(local)
         clocks.__enter__()             # sampled from before the warm-up; the line reports the timed spans

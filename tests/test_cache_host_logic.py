@@ -167,3 +167,19 @@ def test_caches_are_freed_by_their_last_reference(host_flat_caches, host_cache):
                 views[0]
     finally:
         gc.enable()
+
+
+def test_counter_snapshot_covers_the_row_totals_of_the_flat_classes(host_flat_caches):
+    """A CUDA graph capture runs the host side of a decode step without its kernels and then puts the counters back;
+    for the budget-sharing classes that includes the per-layer row totals compress() triggers on."""
+    for cls in host_flat_caches:
+        c = cls(device="cpu")
+        k = emu.on_device(torch.randn(1, 2, 10, 16))
+        for l in range(2):
+            c.update(k, k.clone(), emu.on_device(torch.zeros(1, 2, 10)), torch.arange(10), l)
+        snap = c.snapshot_counters()
+        before = (c.get_seq_length(), list(c._rows), c.get_total_cached_tokens())
+        c.advance(1)
+        assert c.get_total_cached_tokens() == before[2] + 2 * 2
+        c.restore_counters(snap)
+        assert (c.get_seq_length(), list(c._rows), c.get_total_cached_tokens()) == before

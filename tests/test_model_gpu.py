@@ -276,6 +276,20 @@ def test_hf_generate_through_the_fused_step():
     sampled = model.generate(prompt, do_sample=True, temperature=0.8, top_k=20, past_key_values=cache, **kw)
     assert sampled.shape == (3, plen + new_tokens) and int(sampled.max()) < cfg.vocab_size
     cache.check_status()
+    # launched from Python instead of replayed from a graph
+    model.config.fused_decode_step = "eager"
+    short = model.generate(prompt, do_sample=False, past_key_values=TrimKVCache(device=DEV),
+                           **dict(kw, max_new_tokens=8))
+    _module_path_rates_choices(model, cfg, prompt, short, 8)
+    model.config.fused_decode_step = True
+    # without eviction the slabs grow: the step that would exceed the capacity runs plainly and the graph is recorded again
+    model.config.compress_memory = False
+    grown = TrimKVCache(device=DEV)
+    long = model.generate(prompt, do_sample=False, past_key_values=grown, **dict(kw, max_new_tokens=30))
+    assert grown.get_cache_length(0) == plen + 29
+    grown.check_status()
+    _module_path_rates_choices(model, cfg, prompt, long, 30)
+    model.config.compress_memory = True
     # a forward pass the fused step does not cover takes the module path
     out = model(input_ids=ids[:, -1:], past_key_values=cache, output_hidden_states=True)
     assert out.logits.shape == (3, 1, cfg.vocab_size)

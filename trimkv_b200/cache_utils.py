@@ -152,6 +152,14 @@ class TrimKVCache:
             self.n_seen_tokens[l] += num_tokens
             self._cache_len[l] += num_tokens
 
+    def snapshot_counters(self):
+        """The host-side counters that ``update`` / ``decode_prep`` / ``advance`` move, for ``restore_counters``: a CUDA
+        graph capture of a decode step runs the host side of the step without running its kernels."""
+        return (self._seen_tokens, list(self.n_seen_tokens), list(self._cache_len))
+
+    def restore_counters(self, snap) -> None:
+        self._seen_tokens, self.n_seen_tokens, self._cache_len = snap[0], list(snap[1]), list(snap[2])
+
     # ------------------------------------------------------------------ views
     def _view(self, kind: str, l: int):
         if l >= len(self):
@@ -560,6 +568,13 @@ class BatchedDynamicBudgetTrimKVCache(TrimKVCache):
         super().advance(num_tokens)
         for l in range(len(self._rows)):
             self._rows[l] += self._batch * self._hkv * num_tokens
+
+    def snapshot_counters(self):
+        return super().snapshot_counters() + (list(self._rows),)
+
+    def restore_counters(self, snap) -> None:
+        super().restore_counters(snap)
+        self._rows = list(snap[3])     # compress() triggers on these totals: a captured, unexecuted step must not count
 
     def _attn_kwargs(self, l: int) -> Dict[str, Any]:
         kw = super()._attn_kwargs(l)

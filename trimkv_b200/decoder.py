@@ -84,7 +84,8 @@ class FusedDecodeStep:
                 gu, gu_bias = fuse([mlp.gate_up_proj] if hasattr(mlp, "gate_up_proj") else [mlp.gate_proj, mlp.up_proj])
                 self.layers.append((layer, w, bias, gu, gu_bias))
         self.hq, self.hkv, self.eps = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.rms_norm_eps
-        # tc_gemm: tkv_skinny_gemm for the four per-layer projections instead of the library GEMMs.  Off by default: at 32
+        # tc_gemm: tkv_skinny_gemm for the four per-layer projections instead of the library GEMMs (True, or the subset
+        # of {"qkvg", "o", "gu", "down"} to switch).  Off by default: at 32
         # rows these GEMMs are bound by launch and pipeline-fill latency, and the tensor-core kernel only matches cuBLAS
         # (5-12 us per call either way on B200) while its fp32 partials make the consumers slower.
         # fused_down: the MLP's activation and down projection as one kernel (tkv_skinny_gemm_swiglu) instead of
@@ -105,7 +106,8 @@ class FusedDecodeStep:
         (None, 0) when the shape is outside its envelope (then the caller uses the library GEMM)."""
         m, k = x.shape
         n = w.shape[0]
-        splits = ops.skinny_gemm_splits(m, n, k) if self.use_tc_gemm else 0
+        use = self.use_tc_gemm if isinstance(self.use_tc_gemm, bool) else tag in self.use_tc_gemm
+        splits = ops.skinny_gemm_splits(m, n, k) if use else 0
         if splits == 0:
             return None, 0
         buf = self._partials.get((tag, m))
@@ -166,6 +168,60 @@ class FusedDecodeStep:
         return F.linear(h, self.model.lm_head.weight)
 
 
+class GraphedForwardStep:
+    """The fused decode step behind ``TrimKVForCausalLM.forward`` (``config.fused_decode_step``): static input buffers, two
+    plain calls that size the workspaces, then one CUDA graph replayed per call.  Lives on the cache it serves and refers
+    to it weakly; the caller passes the cache to every call.  The graph is dropped and recorded again when the cache's
+    slabs were re-homed (growth without eviction) and is not used for a step that would exceed the capacity (that step
+    runs plainly, which grows the slabs)."""
+
+    EAGER_CALLS = 2
+
+    def __init__(self, model, cache: TrimKVCache, use_graph: bool = True):
+        self.step = FusedDecodeStep(model, cache)
+        self.model, self.use_graph = model, use_graph
+        dev = model.device
+        self.ids = torch.zeros(cache._batch, 1, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(1, dtype=torch.int64, device=dev)
+        self.calls, self.graph, self.logits, self.key, self.launches_per_replay = 0, None, None, None, 0
+
+    def _slab_key(self, cache):
+        return (cache._slab["k"].data_ptr(), cache._cap, cache._batch) if cache._slab is not None else None
+
+    def release_graph(self) -> None:
+        if self.graph is not None:
+            torch.cuda.synchronize()
+            self.graph.reset()
+            self.graph, self.logits = None, None
+
+    def __call__(self, cache: TrimKVCache, input_ids: torch.Tensor, pos: torch.Tensor) -> torch.Tensor:
+        """input_ids [B,1], pos int64[1] (device) -> logits [B, vocab] (a tensor of the caller's own)."""
+        self.ids.copy_(input_ids)
+        self.pos.copy_(pos)
+        fits = cache._slab is not None and max(cache._cache_len) + 1 <= cache._cap
+        if self.graph is not None and (self.key != self._slab_key(cache) or not fits):
+            self.release_graph()
+            self.calls, cache.static_views = 0, False
+        if (not self.use_graph or not fits or self.calls < self.EAGER_CALLS or torch.cuda.is_current_stream_capturing()):
+            self.calls += 1
+            return self.step(self.ids, self.pos)
+        if self.graph is None:
+            cache.static_views = True        # views of the whole capacity: the recorded launches stay valid as lengths grow
+            snap = cache.snapshot_counters()
+            self.graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count
+            with torch.cuda.graph(self.graph):
+                self.logits = self.step(self.ids, self.pos)
+            self.launches_per_replay = ops.launch_count - before
+            ops.launch_count = before
+            cache.restore_counters(snap)
+            self.key = self._slab_key(cache)
+        self.graph.replay()
+        ops.launch_count += self.launches_per_replay
+        cache.advance(1)
+        return self.logits.clone()
+
+
 class GreedyDecoder:
     """Steps a prefilled (model, cache) pair one token at a time.
 
@@ -206,26 +262,18 @@ class GreedyDecoder:
         self.ids.copy_(self.next_ids)
         self.pos.add_(1)
 
-    def _counters(self):
-        c = self.cache
-        return (c._seen_tokens, list(c.n_seen_tokens), list(c._cache_len))
-
-    def _restore(self, snap):
-        c = self.cache
-        c._seen_tokens, c.n_seen_tokens, c._cache_len = snap[0], list(snap[1]), list(snap[2])
-
     def capture(self):
         """Records one decode step.  Views handed to attention span the full capacity so the recorded
         launch geometry is valid for every later length; the kernels read the live lengths on the device."""
         self.cache.static_views = True
-        snap = self._counters()
+        snap = self.cache.snapshot_counters()
         self.graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
         with torch.cuda.graph(self.graph):
             self._forward()
         self.launches_per_replay = ops.launch_count - before
         ops.launch_count = before
-        self._restore(snap)
+        self.cache.restore_counters(snap)
 
     def release_graph(self) -> None:
         """Destroys the captured decode graph (the next ``step`` captures again).  Needed before a process group whose
@@ -254,10 +302,7 @@ class GreedyDecoder:
             self.cache.advance(1)
         else:
             self._forward()
-        if self.cfg.compress_memory:
-            self.cache.compress(
-                strategy=self.cfg.compress_strategy, memory_size=self.cfg.memory_size, buffer_size=self.cfg.buffer_size,
-                num_layers=self.cfg.num_hidden_layers, num_key_value_heads=self.cfg.num_key_value_heads)
+        self.model.model.compress_after_forward(self.cache)     # the eviction check that ends the model's forward pass
         return self.next_ids
 
 

@@ -416,8 +416,9 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
     def _fused_step_for(self, input_ids, past_key_values, inputs_embeds, kwargs):
         """The fused CUDA decode step for this call, or None.  Opt-in (``config.fused_decode_step = True``): a forward
         pass of one new token per request on a cache that holds the prompt then runs as ten fused launches per layer
-        (``decoder.FusedDecodeStep``) instead of module by module, under HF ``generate`` as under a hand-written loop;
-        same arithmetic up to the summation order of the kernels.  Anything the fused step does not cover (other
+        (``decoder.FusedDecodeStep``) instead of module by module, replayed from a CUDA graph from the third such call
+        on (``"eager"`` instead of True: launched from Python every time), under HF ``generate`` as under a
+        hand-written loop; same arithmetic up to the summation order of the kernels.  Anything the fused step does not cover (other
         shapes or dtypes, ``inputs_embeds``, hidden-state or attention outputs, CPU) takes the module path."""
         if not getattr(self.config, "fused_decode_step", False) or input_ids is None or inputs_embeds is not None:
             return None
@@ -429,12 +430,15 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
         if (not isinstance(cache, TrimKVCache) or cache.get_seq_length() == 0
                 or getattr(cache, "_batch", None) != input_ids.shape[0]):
             return None
-        from .decoder import FusedDecodeStep
+        from .decoder import FusedDecodeStep, GraphedForwardStep
         if self.lm_head.weight.dtype not in (torch.bfloat16, torch.float16) or not FusedDecodeStep.supports(self):
             return None
         step = cache.__dict__.get("_fused_step")
-        if step is None or step.model is not self:
-            step = cache.__dict__["_fused_step"] = FusedDecodeStep(self, cache)
+        graph = self.config.fused_decode_step != "eager"
+        if step is None or step.model is not self or step.use_graph != graph or step.ids.shape[0] != input_ids.shape[0]:
+            if step is not None:
+                step.release_graph()
+            step = cache.__dict__["_fused_step"] = GraphedForwardStep(self, cache, use_graph=graph)
         return step
 
     def forward(self, input_ids=None, attention_mask=None, position_ids=None, past_key_values=None, inputs_embeds=None,
@@ -443,7 +447,7 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
         if step is not None:
             pos = cache_position[-1:] if cache_position is not None else torch.full(
                 (1,), past_key_values.get_seq_length(), device=input_ids.device)
-            logits = step(input_ids, pos.to(torch.int64))
+            logits = step(past_key_values, input_ids, pos.to(torch.int64))
             self.model.compress_after_forward(past_key_values)
             return CausalLMOutputWithPast(logits=logits[:, None, :], past_key_values=past_key_values)
         out = self.model(input_ids=input_ids, attention_mask=attention_mask, position_ids=position_ids,
