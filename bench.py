@@ -449,13 +449,34 @@ def run_micro(args):
 
         res.update({"config": {"workload": args.workload, "batch": wl["batch"], "prompt": wl["prompt"],
                                "M": wl["memory_size"], "B": wl["buffer_size"], "new_tokens": n_new},
-                    "timing": "wall clock of generate(max_new_tokens=8+n) minus generate(max_new_tokens=8), the faster of two calls each, per token"})
+                    "timing": "HF loop: host time stamps of the streamer calls over the last n tokens; fused_decode: wall clock of generate(max_new_tokens=8+n) minus generate(max_new_tokens=8), the faster of two calls each"})
+        class Stamps:
+            """HF streamer that records when each step's tokens reached the host."""
+            def __init__(self):
+                self.t = []
+
+            def put(self, value):
+                self.t.append(time.perf_counter())
+
+            def end(self):
+                pass
+
         for name, kw, flag in (("hf_generate", {}, False), ("hf_generate_fused_step", {}, True),
                                ("fused_decode", {"fused_decode": True}, False)):
             model.config.fused_decode_step = flag           # True: one-token forward passes run as the fused CUDA step
             wall(4, **kw)                                   # warm-up: workspaces, kernel attributes, fused weights
             # every call builds a cache (and, on the fused paths, records a graph), whose cost varies from call to call
             # by more than the tokens in between take: the faster of two calls each
+            if "fused_decode" not in kw:
+                # the HF loop: time stamps of its streamer calls, from the 8th new token on (the graph of the fused step
+                # has been recorded by then); a call's fixed costs (cache, graph) stay out of the figure
+                st = Stamps()
+                total = wall(8 + n_new, streamer=st, **kw)
+                ms = (st.t[-1] - st.t[-1 - n_new]) / n_new * 1e3
+                res[name] = {"ms_per_step": ms, "tok_per_s": wl["batch"] / (ms * 1e-3), "whole_call_s": total}
+                continue
+            # every call builds a cache and records a graph, whose cost varies from call to call by more than the tokens
+            # in between take: the faster of two calls each
             short = min(wall(8, **kw), wall(8, **kw))
             full = min(wall(8 + n_new, **kw), wall(8 + n_new, **kw))
             ms = (full - short) / n_new * 1e3
