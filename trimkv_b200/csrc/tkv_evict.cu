@@ -566,18 +566,26 @@ __global__ void __launch_bounds__(256) compact_gather_kernel(CompactParams p) {
 }
 
 // cu_seqlens[g, 0..group] = exclusive prefix sum of seg_len[g*group ..]; one CTA per group.
-__global__ void __launch_bounds__(256) rebuild_cu_kernel(const int32_t* seg_len, int32_t* cu, int group) {
-  __shared__ int warp_sums[256 / 32 + 1];
+// Four consecutive lengths per thread, so that a group of up to 1024 segments (4096 with the wide block) takes one scan.
+template <int kThreads>
+__global__ void __launch_bounds__(kThreads) rebuild_cu_kernel(const int32_t* seg_len, int32_t* cu, int group) {
+  __shared__ int warp_sums[kThreads / 32 + 1];
   const int g = blockIdx.x;
   const int32_t* len = seg_len + (int64_t)g * group;
   int32_t* out = cu + (int64_t)g * (group + 1);
   int running = 0;
-  for (int base = 0; base < group; base += 256) {
-    const int i = base + threadIdx.x;
-    const int v = i < group ? len[i] : 0;
+  for (int base = 0; base < group; base += 4 * kThreads) {
+    const int i0 = base + 4 * (int)threadIdx.x;
+    int v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v[u] = i0 + u < group ? len[i0 + u] : 0;
     int total;
-    const int excl = block_exclusive_scan<256>(v, warp_sums, &total);
-    if (i < group) out[i] = running + excl;
+    int at = running + block_exclusive_scan<kThreads>(v[0] + v[1] + v[2] + v[3], warp_sums, &total);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (i0 + u < group) out[i0 + u] = at;
+      at += v[u];
+    }
     running += total;
   }
   if (threadIdx.x == 0) out[group] = running;
@@ -587,7 +595,8 @@ static int launch_rebuild(const int32_t* seg_len, int32_t* cu, int nseg, int gro
   if (cu == nullptr || nseg == 0) return TKV_OK;
   if (group <= 0 || nseg % group != 0)
     return fail(TKV_ERR_ARG, "cu_seqlens rebuild: nseg=%d is not a multiple of group=%d", nseg, group);
-  rebuild_cu_kernel<<<nseg / group, 256, 0, st>>>(seg_len, cu, group);
+  if (group > 1024) rebuild_cu_kernel<1024><<<nseg / group, 1024, 0, st>>>(seg_len, cu, group);
+  else rebuild_cu_kernel<256><<<nseg / group, 256, 0, st>>>(seg_len, cu, group);
   return check_launch("tkv_rebuild_cu_seqlens");
 }
 
