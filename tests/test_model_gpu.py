@@ -293,6 +293,11 @@ def test_hf_generate_through_the_fused_step():
     # a forward pass the fused step does not cover takes the module path
     out = model(input_ids=ids[:, -1:], past_key_values=cache, output_hidden_states=True)
     assert out.logits.shape == (3, 1, cfg.vocab_size)
+    with torch.no_grad():
+        assert model._fused_step_for(ids[:, -1:], cache, None, {}) is not None
+        assert model._fused_step_for(ids[:, -2:], cache, None, {}) is None              # two tokens
+    with torch.enable_grad():
+        assert model._fused_step_for(ids[:, -1:], cache, None, {}) is None              # autograd would record nothing
     # a cache that carries a fused step is still freed by its last reference (no cycle for the collector to find)
     import gc
     import weakref

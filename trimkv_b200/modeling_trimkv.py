@@ -419,10 +419,12 @@ class TrimKVForCausalLM(TrimKVPreTrainedModel, GenerationMixin):
         (``decoder.FusedDecodeStep``) instead of module by module, replayed from a CUDA graph from the third such call
         on (``"eager"`` instead of True: launched from Python every time), under HF ``generate`` as under a
         hand-written loop; same arithmetic up to the summation order of the kernels.  Anything the fused step does not cover (other
-        shapes or dtypes, ``inputs_embeds``, hidden-state or attention outputs, CPU) takes the module path."""
+        shapes or dtypes, ``inputs_embeds``, hidden-state or attention outputs, CPU, a call with autograd enabled) takes
+        the module path."""
         if not getattr(self.config, "fused_decode_step", False) or input_ids is None or inputs_embeds is not None:
             return None
-        if input_ids.dim() != 2 or input_ids.shape[1] != 1 or not input_ids.is_cuda or self.training:
+        if (input_ids.dim() != 2 or input_ids.shape[1] != 1 or not input_ids.is_cuda or self.training
+                or torch.is_grad_enabled()):      # the fused kernels record nothing for autograd
             return None
         if kwargs.get("output_attentions") or kwargs.get("output_hidden_states") or kwargs.get("labels") is not None:
             return None
