@@ -110,6 +110,7 @@ CASES = [
     (2, 4224, 128, 4096, 4224, "full", torch.bfloat16, _bf16_logbeta),   # config-2 steady state
     (2, 16512, 128, 16384, 16512, "full", torch.bfloat16, _bf16_logbeta),  # long segments: the 512-thread variant
     (3, 20000, 64, 15000, 15001, "ragged", torch.bfloat16, _coarse_logbeta),
+    (2, 57000, 128, 4096, 57000, "full", torch.bfloat16, _bf16_logbeta),  # the longest segment the selection accepts
 ]
 
 
@@ -188,6 +189,26 @@ def _evict_case(ops, nseg, cap, d, m, trigger, spec, dtype, beta_fn, ctas):
     before = (k.clone(), pos.clone(), ln.clone())
     ops.evict(k, v, beta, pos, ln, cu, nseg, nseg, cap, q_idx, m, max(trigger, m + 1), cap, None, status)
     assert torch.equal(before[0], k) and torch.equal(before[1], pos) and torch.equal(before[2], ln)
+
+
+def test_select_at_the_longest_supported_prompt(ops):
+    """Prompt hand-off at the size limit of the selection (57 000 tokens per segment: the keys fill the shared memory a
+    block may have); one token more is refused on the host."""
+    gen = torch.Generator().manual_seed(13)
+    nseg, n, m = 3, 57000, 4096
+    b = _coarse_logbeta(gen, nseg, n).to(DEV)
+    p = torch.arange(n, dtype=torch.int32, device=DEV)
+    kept = torch.empty(nseg, m, dtype=torch.int32, device=DEV)
+    cnt = torch.empty(nseg, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    ops.evict_select(b, p, None, n, nseg, n + 1, m, m + 128, n, kept, cnt, status)
+    assert ops.read_status(status) == 0
+    want = orc.canonical_topm(orc.retention_scores(b.cpu().numpy(), np.arange(n), n + 1), m)
+    assert np.array_equal(kept.cpu().numpy(), want) and cnt.cpu().tolist() == [m] * nseg
+    b1 = torch.zeros(1, n + 1, device=DEV)
+    with pytest.raises(Exception):
+        ops.evict_select(b1, torch.arange(n + 1, dtype=torch.int32, device=DEV), None, n + 1, 1, n + 2, m, m + 128, n + 1,
+                         kept[:1], cnt[:1], status)
 
 
 def test_evict_grouped_cu_seqlens(ops):
