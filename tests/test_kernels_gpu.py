@@ -379,6 +379,32 @@ def test_decode_attention_ragged_work_list(ops, bsz, hq, hkv, cap):
     assert ops.read_status(status) == 2
 
 
+def test_decode_attention_over_a_very_long_segment(ops):
+    """70 000 and 300 cached tokens side by side (274 chunks for the long one: beyond the 255 the compact work list can
+    address, so the call with a token bound must fall back to the full grid and give the same bits)."""
+    gen = torch.Generator().manual_seed(29)
+    bsz, hq, hkv, d, cap, dtype = 1, 8, 2, 128, 70000, torch.bfloat16
+    lens = [cap, 300]
+    q = torch.randn(bsz, hq, d, generator=gen).to(dtype).to(DEV)
+    k = torch.randn(hkv * cap, d, generator=gen).to(dtype).to(DEV)
+    v = torch.randn(hkv * cap, d, generator=gen).to(dtype).to(DEV)
+    ln = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    status = ops.new_status(DEV)
+    out = torch.full_like(q, float("nan"))
+    ws = torch.empty(ops.decode_attn_workspace_bytes(bsz, hq, hkv, d, cap), dtype=torch.uint8, device=DEV)
+    ops.decode_attn(q, k, v, ln, None, cap, out, ws, hkv, d ** -0.5, cap, status)
+    assert ops.read_status(status) == 0
+    kf = torch.cat([k.view(hkv, cap, d)[s, :lens[s]] for s in range(hkv)]).float().cpu().numpy()
+    vf = torch.cat([v.view(hkv, cap, d)[s, :lens[s]] for s in range(hkv)]).float().cpu().numpy()
+    want = orc.varlen_gqa_attention(q[:, :, None].float().cpu().numpy(), kf, vf, np.concatenate([[0], np.cumsum(lens)]), bsz, hkv)[:, 0]
+    assert np.max(np.abs(out.float().cpu().numpy() - want)) <= 2e-2
+    out2 = torch.full_like(q, float("nan"))
+    wsr = torch.empty(ops.decode_attn_workspace_bytes_ragged(bsz, hq, hkv, d, cap, sum(lens)), dtype=torch.uint8, device=DEV)
+    ops.decode_attn(q, k, v, ln, None, cap, out2, wsr, hkv, d ** -0.5, cap, status, total_len_bound=sum(lens))
+    assert ops.read_status(status) == 0
+    assert torch.equal(out2, out)
+
+
 @pytest.mark.parametrize("dtype,tol", [(torch.bfloat16, 2e-2), (torch.float16, 5e-3)])
 @pytest.mark.parametrize("bsz,hq,hkv,ql,cap", [(2, 16, 8, 3, 700), (1, 8, 4, 8, 300), (2, 16, 4, 7, 1100), (3, 2, 2, 5, 200),
                                                (1, 16, 8, 20, 600), (1, 8, 2, 48, 900), (2, 4, 4, 70, 400), (1, 16, 8, 32, 130)])
