@@ -132,6 +132,8 @@ MULTI_CASES = [
     (3, 2100, 64, 2000, 2001, "ragged", torch.float16, _coarse_logbeta, 7),
     (4, 1064, 128, 1024, 1064, "full", torch.bfloat16, _tail_heavy_logbeta, 4),  # kept rows are a prefix
     (2, 16512, 128, 16384, 16512, "full", torch.bfloat16, _bf16_logbeta, 32),
+    (100, 384, 128, 256, 320, "ragged", torch.bfloat16, _bf16_logbeta, 8),      # more evicting segments than rows of the move grid
+    (700, 160, 64, 128, 129, "ragged", torch.float16, _coarse_logbeta, 2),      # 2 x 296 blocks walk up to 700 segments
 ]
 
 
