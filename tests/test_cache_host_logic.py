@@ -183,3 +183,15 @@ def test_counter_snapshot_covers_the_row_totals_of_the_flat_classes(host_flat_ca
         assert c.get_total_cached_tokens() == before[2] + 2 * 2
         c.restore_counters(snap)
         assert (c.get_seq_length(), list(c._rows), c.get_total_cached_tokens()) == before
+
+
+def test_constructor_hints_refuse_knorm_alpha(host_cache):
+    """The hints make update() reduce the prompt by the "alpha" score; compressing by key norms afterwards is refused
+    instead of silently mixing the two."""
+    c = host_cache(device="cpu", memory_size=4, buffer_size=2, num_layers=1)
+    k = emu.on_device(torch.randn(1, 2, 10, 16))
+    c.update(k, k.clone(), emu.on_device(torch.zeros(1, 2, 10)), torch.arange(10), 0)
+    with pytest.raises(ValueError, match="knorm_alpha"):
+        c.compress(strategy="knorm_alpha", memory_size=4, buffer_size=2)
+    c.compress(strategy="alpha", memory_size=4, buffer_size=2)
+    assert c.get_cache_length(0) == 4

@@ -383,6 +383,13 @@ class TrimKVCache:
         if strategy not in ("alpha", "knorm_alpha"):
             raise ValueError(f"Unknown compression strategy: {strategy}")
         knorm = strategy == "knorm_alpha"
+        if (knorm and type(self) is TrimKVCache and not self.defer_handoff and self._hint_m is not None
+                and self._hint_b is not None and self._hint_layers is not None and not self.sliding_window_size):
+            # With these constructor hints update() has already reduced each layer's prompt to its top rows, by the
+            # "alpha" score: the key norms would come too late.
+            raise ValueError("memory_size / buffer_size / num_layers given to the constructor select the prompt's rows with "
+                             "strategy 'alpha' inside update(); leave them out (or set defer_handoff) to compress with "
+                             "'knorm_alpha'")
         num_layers = len(self) if num_layers is None else num_layers
         if num_layers == 0:
             return
