@@ -1,5 +1,5 @@
 """Seeded random walks of the budget-sharing flat caches (update -> compress every step, both classes, every strategy the
-goldens hold) against the oracle's restatement, at shapes the reference-generated fixtures do not cover: one to four
+goldens hold, the key-norm forms included) against the oracle's restatement, at shapes the reference-generated fixtures do not cover: one to four
 layers, one to five KV heads, budgets from 3 to 70, prompts below and far above the budget.  Needs a B200."""
 import numpy as np
 import pytest
@@ -12,7 +12,10 @@ DEV = "cuda:0"
 
 COMBOS = [("batched", "alpha", False, False), ("batched", "layer_wise_alpha", False, False),
           ("batched", "layer_wise_alpha", True, False), ("batched", "alpha_threshold", False, True),
-          ("single", "alpha", False, False), ("single", "alpha", True, False), ("single", "layer_wise_alpha", False, False)]
+          ("single", "alpha", False, False), ("single", "alpha", True, False), ("single", "layer_wise_alpha", False, False),
+          ("batched", "knorm_alpha", False, False), ("batched", "layer_wise_knorm_alpha", False, False),
+          ("batched", "knorm_alpha_threshold", False, True), ("single", "knorm_alpha", False, False),
+          ("single", "layer_wise_knorm_alpha", False, False)]
 
 
 def _draw(seed):
@@ -29,7 +32,7 @@ def _draw(seed):
     return rng, kind, strategy, floor, thr, L, H, bsz, m, buf, prompt, steps
 
 
-@pytest.mark.parametrize("seed", range(21))
+@pytest.mark.parametrize("seed", range(36))
 def test_random_flat_budget_walk_matches_oracle(seed):
     from trimkv_b200 import BatchedDynamicBudgetTrimKVCache, DynamicBudgetTrimKVCache
     rng, kind, strategy, floor, thr, L, H, bsz, m, buf, prompt, steps = _draw(seed)
@@ -41,10 +44,12 @@ def test_random_flat_budget_walk_matches_oracle(seed):
     cache = (BatchedDynamicBudgetTrimKVCache if kind == "batched" else DynamicBudgetTrimKVCache)(device=DEV)
     ref = orc.OracleFlatBudgetCache(kind == "batched")
     tag = (seed, kind, strategy, floor, thr, L, H, bsz, m, buf, prompt)
+    # keys of varied length (the knorm strategies add log ||k|| to the score); the values are their negatives
+    keys = (torch.randn(L, bsz, H, prompt + steps, d) * (0.2 + 3 * torch.rand(L, bsz, H, prompt + steps, 1))).numpy()
     for t in range(steps + 1):
         lo, hi = (0, prompt) if t == 0 else (prompt + t - 1, prompt + t)
         for l in range(L):
-            k = np.broadcast_to(np.arange(lo, hi, dtype=np.float32)[None, None, :, None], (bsz, H, hi - lo, d)) + 1000 * l
+            k = np.ascontiguousarray(keys[l, :, :, lo:hi])
             ref.update(k.copy(), -k.copy(), logb[l, :, :, lo:hi].numpy(), np.arange(lo, hi), l)
             kt = torch.from_numpy(k.copy()).to(DEV)
             cache.update(kt, -kt, logb[l, :, :, lo:hi].contiguous().to(DEV), torch.arange(lo, hi, device=DEV), l)
@@ -58,7 +63,7 @@ def test_random_flat_budget_walk_matches_oracle(seed):
             for l in range(L):
                 kp, vp, bp, pp = cache.packed(l)
                 assert np.array_equal(pp[:, 0].cpu().numpy(), ref.kv_positions[l][:, 0]), (tag, t, l)
-                assert torch.equal(kp[:, 0], pp[:, 0].float() + 1000.0 * l) and torch.equal(vp, -kp)
+                assert np.array_equal(kp.cpu().numpy(), ref.key_cache[l]) and torch.equal(vp, -kp)
                 assert np.array_equal(bp[:, 0].float().cpu().numpy(), ref.retention_weights[l][:, 0])
                 assert np.array_equal(cache.cu_seqlens_k[l].cpu().numpy(), np.concatenate([[0], np.cumsum(got[l])]))
     cache.check_status()
