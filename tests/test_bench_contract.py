@@ -54,3 +54,27 @@ def test_clock_summary_parses_rows_and_windows():
     window = cs.summary(10.05, 10.15)
     assert window == {"sm_mhz": 1800, "sm_max_mhz": 1965, "reasons": ["sw_power_cap"], "samples": 1}
     assert cs.summary(20.0, 21.0) == {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+
+
+import pytest  # noqa: E402
+
+
+@pytest.mark.gpu
+def test_native_arm_line_on_the_small_workload():
+    """The whole default flow on a small model: one JSON line with the keys the contract names."""
+    out = _run(None, "--workload", "tiny", "--steps", "8", "--warmup", "3", "--cpu-steps", "2")
+    assert out.returncode == 0, out.stderr[-3000:]
+    lines = [l for l in out.stdout.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["metric"] == "decode_tok_per_s" and d["unit"] == "tok/s" and d["n_gpus"] == 1 and d["steps"] == 8
+    assert d["higher_is_better"] is True and d["scaling"] == "weak" and d["data"] == "synthetic" and d["dtype"] == "bf16"
+    assert d["config"]["workload"] == "tiny" and d["value"] > 0 and d["gpu_launches"] > 0
+    r = d["roofline"]
+    assert r["bound"] == "hbm" and r["unit"] == "GB/s" and r["peak"] > 0 and abs(r["frac"] - r["achieved"] / r["peak"]) < 1e-9
+    e = d["e2e"]
+    assert e["value"] > 0 and e["h2d_bytes_per_step"] > 0 and e["d2h_bytes_per_step"] > 0
+    assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["value"] > 0
+    assert d["evict"] is not None and d["evict"]["frac"] > 0          # an eviction falls inside the window
+    assert d["evict_micro"]["frac"] > 0 and d["append"]["frac"] > 0
+    assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons", "samples"}
