@@ -614,18 +614,14 @@ def run_micro(args):
             res["flash_attn_varlen"] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
         res["config"] = {"batch": batch, "hq": hq, "hkv": hkv, "head_dim": D, "dtype": "bf16",
                          "mean_len": float(lens.float().mean()), "buffers": nbuf, "shape": args.attn_shape}
-    ms = sorted(a.elapsed_time(b) / chain for a, b in times)
+    ms = sorted(a.elapsed_time(b) for a, b in times)
     avg = sum(ms) / len(ms)
-    if kind == "append":
-        res["timing"] = (f"{chain} launches back to back in a CUDA graph per sample, L2 flushed before each sample; "
-                         "2 MB per launch: bound by launch latency, not by bandwidth (the decode step appends inside "
-                         "decode_prep_kernel and never runs this launch)")
     res.update({"algorithmic_bytes_per_launch": alg, "avg_ms": avg, "median_ms": ms[len(ms) // 2],
                 "achieved_gbs": alg / (avg * 1e-3) / 1e9, "frac_of_peak": alg / (avg * 1e-3) / 1e9 / peak})
     print(json.dumps(res))
 
 
-def main():
+def parse_args(argv=None):
     ap = argparse.ArgumentParser()
     ap.add_argument("--micro", default=None, choices=["evict", "attn", "append", "steady", "multi", "prefill", "generate"],
                     help="run one kernel microbenchmark instead of the decode benchmark")
@@ -669,7 +665,11 @@ def main():
     ap.add_argument("--no-evict-window", action="store_true",
                     help="do not advance the cache so that an eviction falls inside the timed windows (profiling runs)")
     ap.add_argument("--no-micro", action="store_true", help="skip the kernel-level evict / append phases of the default run")
-    args = ap.parse_args()
+    return ap.parse_args(argv)
+
+
+def main():
+    args = parse_args()
     wl = WORKLOADS[args.workload]
     if args.warmup < 3:
         args.warmup = 3

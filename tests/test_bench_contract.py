@@ -78,3 +78,29 @@ def test_native_arm_line_on_the_small_workload():
     assert d["evict"] is not None and d["evict"]["frac"] > 0          # an eviction falls inside the window
     assert d["evict_micro"]["frac"] > 0 and d["append"]["frac"] > 0
     assert set(d["clocks"]) >= {"sm_mhz", "sm_max_mhz", "reasons", "samples"}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("argv", [
+    ["--micro", "evict", "--nseg", "16", "--M", "256", "--no-cpu-baseline"],
+    ["--micro", "evict", "--nseg", "16", "--M", "256", "--ctas", "4", "--no-cpu-baseline"],
+    ["--micro", "append", "--nseg", "64", "--M", "256", "--no-cpu-baseline"],
+    ["--micro", "steady", "--nseg", "64", "--M", "256", "--ctas", "4"],
+    ["--micro", "attn", "--nseg", "64"],
+    ["--micro", "attn", "--nseg", "64", "--token-bound"],
+    ["--micro", "attn", "--nseg", "64", "--packed"],
+    ["--micro", "attn", "--attn-shape", "config2", "--nseg", "32"],
+    ["--micro", "multi", "--nseg", "16", "--M", "256", "--q-tokens", "16"],
+    ["--micro", "prefill", "--nseg", "8", "--M", "512"],
+])
+def test_every_microbenchmark_runs_and_prints_a_line(argv, capsys):
+    """Small sizes: what is checked is that each microbenchmark of bench.py still runs and prints one JSON line."""
+    sys.path.insert(0, ROOT)
+    import bench
+    bench.run_micro(bench.parse_args(argv + ["--steps", "3", "--warmup", "3"]))
+    lines = [l for l in capsys.readouterr().out.splitlines() if l.startswith("{")]
+    assert len(lines) == 1
+    d = json.loads(lines[0])
+    assert d["micro"] == argv[1]
+    times = [v for k, v in d.items() if k in ("avg_ms", "avg_ms_per_step", "query_resident_ms")]
+    assert times and all(t > 0 for t in times)
